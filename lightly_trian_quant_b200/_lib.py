@@ -1,0 +1,60 @@
+"""ctypes binding of libkf_b200.so (the C-ABI declared in include/kf_b200.h).
+
+The library is the only compute path: if it is missing or fails to load, importing the operators raises
+(there is no CPU or PyTorch fallback).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libkf_b200.so"
+HEADER = PKG.parent / "include" / "kf_b200.h"
+
+KF_FMT = {"mx8": 0, "nv4": 1, "mx4": 2, "bf16": 3}
+KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
+KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV = 1, 2, 4
+
+_lib = None
+
+
+class KfError(RuntimeError):
+    pass
+
+
+def declared_symbols() -> list[str]:
+    """every function name include/kf_b200.h declares."""
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(kf_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise KfError(f"{LIB_PATH} not built: run `python -m lightly_trian_quant_b200.build` (no fallback path exists)")
+        L = C.CDLL(str(LIB_PATH))
+        L.kf_version.restype = C.c_char_p
+        L.kf_last_error_string.restype = C.c_char_p
+        L.kf_sf_bytes.restype = C.c_int64
+        L.kf_sf_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int]
+        vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+        sigs = {
+            "kf_quant_rows": [i32, i32, vp, i64, i32, i32, vp, vp, i32, vp, vp, vp],
+            "kf_ln_quant": [i32, vp, vp, vp, f32, i32, i32, vp, i32, vp, vp, vp, vp],
+            "kf_ln_rows": [vp, vp, vp, f32, i32, i32, i32, vp, vp],
+        }
+        for name, args in sigs.items():
+            fn = getattr(L, name)
+            fn.restype = C.c_int
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = lib().kf_last_error_string().decode()
+        raise KfError(f"{what} failed with status {status}: {msg}")

@@ -1,0 +1,141 @@
+// Shared device/host helpers of the B200 (sm_100a) low-precision ViT path: format conversions, the 128x4 blocked
+// scale-factor addressing, status codes and the last-error string of the C-ABI.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <type_traits>
+
+#include "../../include/kf_b200.h"
+
+namespace kf {
+
+// ---------------------------------------------------------------------------------------------- host side status
+void set_error(const char* fmt, ...);
+int cuda_status(cudaError_t e, const char* what);
+
+#define KF_REQUIRE(cond, ...)            \
+  do {                                   \
+    if (!(cond)) {                       \
+      kf::set_error(__VA_ARGS__);        \
+      return KF_ERR_BAD_ARGUMENT;        \
+    }                                    \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------- scale layout
+// Byte offset of the scale of (row, kb) in the 128x4 blocked layout [ceil(R/128), nkb/4, 32, 4, 4]:
+// one 512-byte atom holds 128 rows x 4 consecutive k-blocks, a 32-bit word the 4 k-block scales of one row.
+__host__ __device__ __forceinline__ size_t sf_offset(int row, int kb, int nkb4 /* k-blocks / 4 */) {
+  return ((size_t)(row >> 7) * nkb4 + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
+}
+
+__host__ __device__ __forceinline__ int fmt_vec(int fmt) { return fmt == KF_FMT_NV4 ? 16 : 32; }
+
+// ---------------------------------------------------------------------------------------------- conversions
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {      // returns (hi << 8) | lo, RN-even, saturating
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+// 8 floats -> 8 e2m1 nibbles packed into 32 bits, element 0 in the lowest nibble (RN-even, saturating at 6).
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float* v) {
+  uint32_t r;
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+      "}"
+      : "=r"(r)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return r;
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+  uint32_t h2;
+  uint16_t b = (uint16_t)byte;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(b));
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFF)));
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+
+// 2^k for k in [-128, 127] including the two subnormal powers below 2^-126.
+__device__ __forceinline__ float pow2_int(int k) {
+  int eb = k + 127;
+  return eb > 0 ? __uint_as_float((uint32_t)eb << 23) : __uint_as_float(0x00400000u >> (-eb));
+}
+
+// ue8m0 byte of a block: biased exponent of fl32(amax/denom) plus one when the mantissa is non-zero (round up to a
+// power of two), clamped.  The division is a true IEEE division unless div_true == 0, in which case amax is
+// multiplied by the fp32 reciprocal (what torch does for tensor / python-scalar on a CUDA device).
+template <int DENOM>
+__device__ __forceinline__ int rceil_byte(float amax, int max_byte, bool div_true) {
+  float r = div_true ? __fdiv_rn(amax, (float)DENOM) : amax * (1.0f / (float)DENOM);
+  uint32_t b = __float_as_uint(r);
+  int e = (b >> 23) & 0xFF;
+  e += (b & 0x7FFFFFu) != 0;
+  return e < max_byte ? e : max_byte;
+}
+
+// ---------------------------------------------------------------------------------------------- block quantisers
+// Each takes NL values held by one lane (NL = 8 or 16) whose block maximum `amax` has already been reduced over the
+// lanes that share the block, and returns the packed codes.  `sf_byte` receives the block's scale byte.
+
+template <int NL>
+__device__ __forceinline__ void quant_mx8(const float (&v)[NL], float amax, bool div_true, uint32_t* out /* NL/4 words */, int& sf_byte) {
+  int byte = rceil_byte<448>(amax, 255, div_true);
+  float inv = pow2_int(127 - (byte < 1 ? 1 : byte));
+#pragma unroll
+  for (int i = 0; i < NL; i += 4) {
+    float a = fminf(fmaxf(v[i] * inv, -448.f), 448.f), b = fminf(fmaxf(v[i + 1] * inv, -448.f), 448.f);
+    float c = fminf(fmaxf(v[i + 2] * inv, -448.f), 448.f), d = fminf(fmaxf(v[i + 3] * inv, -448.f), 448.f);
+    out[i / 4] = cvt_e4m3x4(a, b, c, d);
+  }
+  sf_byte = byte;
+}
+
+template <int NL>
+__device__ __forceinline__ void quant_mx4(const float (&v)[NL], float amax, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
+  int byte = rceil_byte<6>(amax, 254, div_true);
+  float inv = pow2_int(127 - byte);
+  float t[8];
+#pragma unroll
+  for (int i = 0; i < NL; i += 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = v[i + j] * inv;
+    out[i / 8] = cvt_e2m1x8(t);
+  }
+  sf_byte = byte;
+}
+
+template <int NL>
+__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, float ts, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
+  float a6 = div_true ? __fdiv_rn(amax, 6.0f) : amax * (1.0f / 6.0f);
+  float t = fminf(__fdiv_rn(a6, ts), 448.f);
+  uint32_t sb = cvt_e4m3x2(t, 0.f) & 0xFF;
+  float denom = e4m3_to_float(sb) * ts;
+  bool ok = denom > 0.f;
+  float dd = ok ? denom : 1.0f;
+  float tt[8];
+#pragma unroll
+  for (int i = 0; i < NL; i += 8) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tt[j] = ok ? __fdiv_rn(v[i + j], dd) : 0.f;
+    out[i / 8] = cvt_e2m1x8(tt);
+  }
+  sf_byte = (int)sb;
+}
+
+}  // namespace kf

@@ -1,0 +1,358 @@
+// Memory-bound producers of the block-scaled operands: the stand-alone row quantiser (optionally bias + GELU first),
+// LayerNorm fused with quantisation, and LayerNorm to a 16-bit tensor.  All three stream each input element once
+// from HBM with 16-byte loads issued up front, keep the row segment in registers and write codes with 8/16-byte
+// stores and scale factors as whole 32-bit words of the 128x4 blocked layout.
+//
+// Bit rules (identical to the reference's torch quantiser, infer-opt/round10_lowp_probe/impl/quant_ref.py:92-154):
+//   mx8  byte = min(exp(fl32(amax/448)) + (mant != 0), 255);  q = e4m3_rn_sat(clamp(x * 2^(127 - max(byte,1)), +-448))
+//   mx4  byte = min(exp(fl32(amax/6))   + (mant != 0), 254);  q = e2m1_rn_sat(x * 2^(127 - byte))
+//   nv4  sf = e4m3_rn(min((amax/6)/ts, 448));  q = e2m1_rn_sat(x / (float(sf) * ts)), 0 when the scale is 0
+#include "kf_common.cuh"
+
+namespace kf {
+
+// ------------------------------------------------------------------------------------------------ loads
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&v)[16]);
+
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+  float4 a = __ldg(p4), b = __ldg(p4 + 1), c = __ldg(p4 + 2), d = __ldg(p4 + 3);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  v[8] = c.x; v[9] = c.y; v[10] = c.z; v[11] = c.w; v[12] = d.x; v[13] = d.y; v[14] = d.z; v[15] = d.w;
+}
+
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[16]) {
+  const uint4* p4 = reinterpret_cast<const uint4*>(p);
+  uint4 a = __ldg(p4), b = __ldg(p4 + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* p, float (&v)[16]) {
+  const uint4* p4 = reinterpret_cast<const uint4*>(p);
+  uint4 a = __ldg(p4), b = __ldg(p4 + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// Gathers the scale bytes of 4 consecutive k-blocks (held by lanes lane0, lane0+STEP, ...) into one word on lane0.
+template <int STEP>
+__device__ __forceinline__ uint32_t gather_sf_word(int byte, int lane) {
+  int base = lane & ~(4 * STEP - 1);
+  uint32_t b0 = __shfl_sync(0xffffffffu, byte, base);
+  uint32_t b1 = __shfl_sync(0xffffffffu, byte, base + STEP);
+  uint32_t b2 = __shfl_sync(0xffffffffu, byte, base + 2 * STEP);
+  uint32_t b3 = __shfl_sync(0xffffffffu, byte, base + 3 * STEP);
+  return (b0 & 0xFF) | ((b1 & 0xFF) << 8) | ((b2 & 0xFF) << 16) | ((b3 & 0xFF) << 24);
+}
+
+// ------------------------------------------------------------------------------------------------ row quantiser
+// One thread = 16 consecutive elements of one row.  mx8 / mx4: two adjacent lanes share a 1x32 block, eight lanes one
+// scale word; nv4: one lane = one 1x16 block, four lanes one scale word.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int M, int K, const float* __restrict__ ts_ptr,
+                                                         const float* __restrict__ bias, int flags, uint8_t* __restrict__ q,
+                                                         uint8_t* __restrict__ sf, int64_t items_valid, int64_t items_total) {
+  const int lane = threadIdx.x & 31;
+  const int per_row = K >> 4;
+  int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool in_pad = w < items_total;          // inside the padded row range (scale bytes must be written)
+  const bool valid = w < items_valid;           // a real row
+  int row = (int)(w / per_row), c16 = (int)(w - (int64_t)row * per_row);
+  float v[16];
+  if (valid) {
+    load16<T>(x + (int64_t)row * ldx + c16 * 16, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  }
+  float ts = 1.f;
+  if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
+  if (flags & KF_Q_GELU) {
+    if (valid) {
+      const float4* b4 = reinterpret_cast<const float4*>(bias + c16 * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 bb = __ldg(b4 + i);
+        v[4 * i] = gelu_erf(v[4 * i] + bb.x);
+        v[4 * i + 1] = gelu_erf(v[4 * i + 1] + bb.y);
+        v[4 * i + 2] = gelu_erf(v[4 * i + 2] + bb.z);
+        v[4 * i + 3] = gelu_erf(v[4 * i + 3] + bb.w);
+      }
+    }
+  }
+  if (flags & KF_Q_ROUND_BF16) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = bf16_round(v[i]);
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const bool div_true = !(flags & KF_Q_RECIP_DIV);
+  int byte;
+  if (FMT == KF_FMT_MX8) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    uint32_t o[4];
+    quant_mx8<16>(v, amax, div_true, o, byte);
+    if (valid) *reinterpret_cast<uint4*>(q + (int64_t)row * K + c16 * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+  } else if (FMT == KF_FMT_MX4) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    uint32_t o[2];
+    quant_mx4<16>(v, amax, div_true, o, byte);
+    if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * (K >> 1) + c16 * 8) = make_uint2(o[0], o[1]);
+  } else {
+    uint32_t o[2];
+    quant_nv4<16>(v, amax, ts, div_true, o, byte);
+    if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * (K >> 1) + c16 * 8) = make_uint2(o[0], o[1]);
+  }
+  if (!valid) byte = 0;
+  constexpr int STEP = (FMT == KF_FMT_NV4) ? 1 : 2;                 // lanes per k-block
+  uint32_t word = gather_sf_word<STEP>(byte, lane);
+  if (in_pad && (lane & (4 * STEP - 1)) == 0) {
+    int kb = (FMT == KF_FMT_NV4) ? c16 : (c16 >> 1);
+    int nkb4 = (FMT == KF_FMT_NV4) ? (K >> 6) : (K >> 7);
+    *reinterpret_cast<uint32_t*>(sf + sf_offset(row, kb, nkb4)) = word;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ LayerNorm (+ quant)
+// One warp per row; lane l holds the 8 consecutive elements [i*256 + l*8, +8) for i < NV (d = NV*256).
+template <int NV>
+__device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                       int lane, bool valid, float (&v)[NV][8]) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (valid) {
+      const float4* p = reinterpret_cast<const float4*>(xr + i * 256 + lane * 8);
+      float4 a = __ldg(p), c = __ldg(p + 1);
+      v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+  constexpr float inv_d = 1.0f / (NV * 256);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[i][j];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  const float mean = s * inv_d;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float c = v[i][j] - mean;
+      ss = fmaf(c, c, ss);
+    }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rstd = rsqrtf(ss * inv_d + eps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const float4* wp = reinterpret_cast<const float4*>(w + i * 256 + lane * 8);
+    const float4* bp = reinterpret_cast<const float4*>(b + i * 256 + lane * 8);
+    float4 w0 = __ldg(wp), w1 = __ldg(wp + 1), b0 = __ldg(bp), b1 = __ldg(bp + 1);
+    float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * ww[j] + bb[j];
+  }
+}
+
+template <int NV, int FMT>
+__global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                                       int M, int rows_pad, const float* __restrict__ ts_ptr, int flags, uint8_t* __restrict__ q,
+                                                       uint8_t* __restrict__ sf, float* __restrict__ y_dbg) {
+  constexpr int D = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows_pad) return;
+  const bool valid = row < M;
+  float v[NV][8];
+  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, valid, v);
+  float ts = 1.f;
+  if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
+  const bool div_true = !(flags & KF_Q_RECIP_DIV);
+  const bool rb = flags & KF_Q_ROUND_BF16;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (rb) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = bf16_round(v[i][j]);
+    }
+    if (y_dbg && valid) {
+      float4* yp = reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + i * 256 + lane * 8);
+      yp[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      yp[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if (FMT != KF_FMT_NV4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int byte;
+    const int col = i * 256 + lane * 8;
+    if (FMT == KF_FMT_MX8) {
+      uint32_t o[2];
+      quant_mx8<8>(v[i], amax, div_true, o, byte);
+      if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * D + col) = make_uint2(o[0], o[1]);
+    } else if (FMT == KF_FMT_MX4) {
+      uint32_t o[1];
+      quant_mx4<8>(v[i], amax, div_true, o, byte);
+      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = o[0];
+    } else {
+      uint32_t o[1];
+      quant_nv4<8>(v[i], amax, ts, div_true, o, byte);
+      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = o[0];
+    }
+    if (!valid) byte = 0;
+    constexpr int STEP = (FMT == KF_FMT_NV4) ? 2 : 4;               // lanes per k-block
+    uint32_t word = gather_sf_word<STEP>(byte, lane);
+    if ((lane & (4 * STEP - 1)) == 0) {
+      int kb = col / ((FMT == KF_FMT_NV4) ? 16 : 32);
+      constexpr int nkb4 = (FMT == KF_FMT_NV4) ? (D >> 6) : (D >> 7);
+      *reinterpret_cast<uint32_t*>(sf + sf_offset(row, kb, nkb4)) = word;
+    }
+  }
+}
+
+template <int NV, typename TO>
+__global__ void __launch_bounds__(128) ln_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                                      int M, TO* __restrict__ y) {
+  constexpr int D = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  float v[NV][8];
+  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, true, v);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if constexpr (sizeof(TO) == 2 && std::is_same<TO, __nv_bfloat16>::value) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[i][2 * j], v[i][2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[i][2 * j], v[i][2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(y + (int64_t)row * D + i * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host launchers
+template <typename T>
+static int launch_quant_rows(int fmt, const void* x, int64_t ldx, int M, int K, const float* ts, const float* bias, int flags, void* q, void* sf,
+                             cudaStream_t st) {
+  int64_t per_row = K / 16;
+  int64_t valid = (int64_t)M * per_row, total = (int64_t)((M + 127) / 128 * 128) * per_row;
+  unsigned grid = (unsigned)((total + 255) / 256);
+  const T* xp = static_cast<const T*>(x);
+  uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
+  if (fmt == KF_FMT_MX8) quant_rows_kernel<T, KF_FMT_MX8><<<grid, 256, 0, st>>>(xp, ldx, M, K, ts, bias, flags, qp, sp, valid, total);
+  else if (fmt == KF_FMT_NV4) quant_rows_kernel<T, KF_FMT_NV4><<<grid, 256, 0, st>>>(xp, ldx, M, K, ts, bias, flags, qp, sp, valid, total);
+  else quant_rows_kernel<T, KF_FMT_MX4><<<grid, 256, 0, st>>>(xp, ldx, M, K, ts, bias, flags, qp, sp, valid, total);
+  return cuda_status(cudaGetLastError(), "kf_quant_rows launch");
+}
+
+template <int NV>
+static int launch_ln_quant(int fmt, const float* x, const float* w, const float* b, float eps, int M, const float* ts, int flags, void* q, void* sf,
+                           float* y_dbg, cudaStream_t st) {
+  int rows_pad = (M + 127) / 128 * 128;
+  unsigned grid = (unsigned)((rows_pad + 3) / 4);
+  uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
+  if (fmt == KF_FMT_MX8) ln_quant_kernel<NV, KF_FMT_MX8><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
+  else if (fmt == KF_FMT_NV4) ln_quant_kernel<NV, KF_FMT_NV4><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
+  else ln_quant_kernel<NV, KF_FMT_MX4><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
+  return cuda_status(cudaGetLastError(), "kf_ln_quant launch");
+}
+
+template <int NV>
+static int launch_ln_rows(const float* x, const float* w, const float* b, float eps, int M, int out_dtype, void* y, cudaStream_t st) {
+  unsigned grid = (unsigned)((M + 3) / 4);
+  if (out_dtype == KF_BF16) ln_rows_kernel<NV, __nv_bfloat16><<<grid, 128, 0, st>>>(x, w, b, eps, M, static_cast<__nv_bfloat16*>(y));
+  else ln_rows_kernel<NV, __half><<<grid, 128, 0, st>>>(x, w, b, eps, M, static_cast<__half*>(y));
+  return cuda_status(cudaGetLastError(), "kf_ln_rows launch");
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int kf_quant_rows(int fmt, int in_dtype, const void* x, int64_t ldx, int M, int K, const float* ts, const float* bias, int flags, void* q,
+                             void* sf, void* stream) {
+  KF_REQUIRE(fmt == KF_FMT_MX8 || fmt == KF_FMT_NV4 || fmt == KF_FMT_MX4, "kf_quant_rows: unknown format %d", fmt);
+  KF_REQUIRE(in_dtype == KF_F32 || in_dtype == KF_BF16 || in_dtype == KF_F16, "kf_quant_rows: unknown input dtype %d", in_dtype);
+  KF_REQUIRE(M >= 0 && K > 0 && K % 128 == 0, "kf_quant_rows: K=%d must be a positive multiple of 128 (M=%d)", K, M);
+  if (M == 0) return KF_OK;
+  KF_REQUIRE(x && q && sf, "kf_quant_rows: null tensor pointer");
+  KF_REQUIRE(ldx >= K && ldx % 8 == 0, "kf_quant_rows: row stride %lld must be >= K and a multiple of 8", (long long)ldx);
+  KF_REQUIRE(aligned16(x) && aligned16(q) && aligned16(sf), "kf_quant_rows: tensors must be 16-byte aligned");
+  KF_REQUIRE(fmt != KF_FMT_NV4 || ts, "kf_quant_rows: nv4 needs the per-tensor scale pointer");
+  KF_REQUIRE(!(flags & KF_Q_GELU) || (bias && aligned16(bias)), "kf_quant_rows: KF_Q_GELU needs a 16-byte aligned bias");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (in_dtype == KF_F32) return launch_quant_rows<float>(fmt, x, ldx, M, K, ts, bias, flags, q, sf, st);
+  if (in_dtype == KF_BF16) return launch_quant_rows<__nv_bfloat16>(fmt, x, ldx, M, K, ts, bias, flags, q, sf, st);
+  return launch_quant_rows<__half>(fmt, x, ldx, M, K, ts, bias, flags, q, sf, st);
+}
+
+extern "C" int kf_ln_quant(int fmt, const float* x, const float* w, const float* b, float eps, int M, int d, const float* ts, int flags, void* q,
+                           void* sf, float* y_dbg, void* stream) {
+  KF_REQUIRE(fmt == KF_FMT_MX8 || fmt == KF_FMT_NV4 || fmt == KF_FMT_MX4, "kf_ln_quant: unknown format %d", fmt);
+  KF_REQUIRE(M >= 0 && d > 0 && d % 256 == 0 && d <= 2048, "kf_ln_quant: d=%d must be a multiple of 256 up to 2048", d);
+  if (M == 0) return KF_OK;
+  KF_REQUIRE(x && w && b && q && sf, "kf_ln_quant: null tensor pointer");
+  KF_REQUIRE(aligned16(x) && aligned16(w) && aligned16(b) && aligned16(q) && aligned16(sf) && aligned16(y_dbg), "kf_ln_quant: tensors must be 16-byte aligned");
+  KF_REQUIRE(fmt != KF_FMT_NV4 || ts, "kf_ln_quant: nv4 needs the per-tensor scale pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (d / 256) {
+    case 1: return launch_ln_quant<1>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 2: return launch_ln_quant<2>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 3: return launch_ln_quant<3>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 4: return launch_ln_quant<4>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 5: return launch_ln_quant<5>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 6: return launch_ln_quant<6>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    case 7: return launch_ln_quant<7>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+    default: return launch_ln_quant<8>(fmt, x, w, b, eps, M, ts, flags, q, sf, y_dbg, st);
+  }
+}
+
+extern "C" int kf_ln_rows(const float* x, const float* w, const float* b, float eps, int M, int d, int out_dtype, void* y, void* stream) {
+  KF_REQUIRE(out_dtype == KF_BF16 || out_dtype == KF_F16, "kf_ln_rows: output dtype must be bf16 or f16");
+  KF_REQUIRE(M >= 0 && d > 0 && d % 256 == 0 && d <= 2048, "kf_ln_rows: d=%d must be a multiple of 256 up to 2048", d);
+  if (M == 0) return KF_OK;
+  KF_REQUIRE(x && w && b && y, "kf_ln_rows: null tensor pointer");
+  KF_REQUIRE(aligned16(x) && aligned16(w) && aligned16(b) && aligned16(y), "kf_ln_rows: tensors must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (d / 256) {
+    case 1: return launch_ln_rows<1>(x, w, b, eps, M, out_dtype, y, st);
+    case 2: return launch_ln_rows<2>(x, w, b, eps, M, out_dtype, y, st);
+    case 3: return launch_ln_rows<3>(x, w, b, eps, M, out_dtype, y, st);
+    case 4: return launch_ln_rows<4>(x, w, b, eps, M, out_dtype, y, st);
+    case 5: return launch_ln_rows<5>(x, w, b, eps, M, out_dtype, y, st);
+    case 6: return launch_ln_rows<6>(x, w, b, eps, M, out_dtype, y, st);
+    case 7: return launch_ln_rows<7>(x, w, b, eps, M, out_dtype, y, st);
+    default: return launch_ln_rows<8>(x, w, b, eps, M, out_dtype, y, st);
+  }
+}
