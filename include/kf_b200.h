@@ -45,6 +45,15 @@ extern "C" {
 #define KF_Q_ROUND_BF16 2  /* round the (LN / GELU) value to bf16 before quantising                  */
 #define KF_Q_RECIP_DIV 4   /* amax/448, amax/6 as multiply by the fp32 reciprocal (torch-on-CUDA rule) */
 
+/* GEMM epilogues */
+#define KF_EPI_PLAIN 0 /* C = act(acc*ts + bias)                      f32 | bf16 | f16 [M,N]         */
+#define KF_EPI_RES 1   /* C = R + gamma * (acc*ts + bias)             f32 [M,N]                      */
+#define KF_EPI_ROPE 2  /* bias + RoPE on q,k + relayout               bf16 | f16 [3,B,Ntok,H,64]     */
+#define KF_EPI_QUANT 3 /* gelu(acc*ts + bias) quantised to out_fmt    codes [M,N] + blocked scales   */
+
+/* GEMM flags (share the flag word with KF_Q_ROUND_BF16 / KF_Q_RECIP_DIV, which act on the QUANT epilogue) */
+#define KF_G_GELU 8 /* PLAIN: apply gelu_erf after the bias */
+
 /* Library version and the SM architecture the kernels were built for ("sm_100a"). */
 KF_API const char* kf_version(void);
 
@@ -77,6 +86,47 @@ KF_API int kf_ln_quant(int fmt, const float* x, const float* w, const float* b, 
  * (infer-opt/round12_lowp_stack/impl/ln16.cu). */
 KF_API int kf_ln_rows(const float* x, const float* w, const float* b, float eps, int M, int d, int out_dtype, void* y,
                void* stream);
+
+/* Parameter block of kf_gemm_bs.  All pointers are device pointers; unused ones are NULL.
+ * Replaces the by-value Params blobs of the reference GEMMs: "=12Q8i" (infer-opt/round13_mxfp8_full/impl/mgx.py:24,96-102;
+ * mgx_core.cu:43-48) and "=14Q10i" (infer-opt/round14_fp4_full/impl/fp4gb.py:15,74-82; fp4g_core.cu:36-42). */
+typedef struct kf_gemm_params {
+  int fmt;       /* operand format of A and W: KF_FMT_MX8 | NV4 | MX4 | BF16                                 */
+  int epi;       /* KF_EPI_*                                                                                   */
+  int M, N, K;   /* C[M,N] = A[M,K] * W[N,K]^T; N % 128 == 0; K % 128 (mx8) | 256 (nv4, mx4) | 64 (bf16) == 0 */
+  int out_dtype; /* KF_F32 | KF_BF16 | KF_F16 for PLAIN; KF_BF16 | KF_F16 for ROPE                             */
+  int flags;     /* KF_G_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV                                                 */
+  int Ntok, prefix, H; /* ROPE: tokens per image, tokens that are not rotated (queries, cls, registers), heads */
+  int out_fmt;   /* QUANT: KF_FMT_MX8 | NV4 | MX4                                                              */
+  const void* A;   /* codes [M, K] (mx8), [M, K/2] (nv4, mx4) or bf16 [M, K], rows contiguous                  */
+  const void* SFA; /* blocked scales of A (NULL for bf16)                                                      */
+  const void* W;   /* codes / bf16 [N, K]                                                                      */
+  const void* SFW; /* blocked scales of W                                                                      */
+  const float* ts_a; /* nv4 per-tensor scale of A (NULL = 1)                                                   */
+  const float* ts_w; /* nv4 per-tensor scale of W (NULL = 1); the accumulator is multiplied by ts_a*ts_w       */
+  const float* bias;  /* fp32 [N] or NULL                                                                      */
+  const float* gamma; /* RES: fp32 [N] LayerScale                                                              */
+  const float* R;     /* RES: fp32 [M, N] residual stream (may alias C)                                        */
+  const float* sin;   /* ROPE: fp32 [Ntok - prefix, 64]                                                        */
+  const float* cos;   /* ROPE: fp32 [Ntok - prefix, 64]                                                        */
+  void* C;            /* PLAIN / RES / ROPE output                                                             */
+  void* Qo;           /* QUANT: output codes [M, N] (mx8) or [M, N/2]                                          */
+  void* SFo;          /* QUANT: output blocked scales of an [M, N] operand                                     */
+  const float* tso;   /* QUANT to nv4: static per-tensor scale of the output                                   */
+} kf_gemm_params;
+
+/* Block-scaled GEMM on tcgen05 with a fused epilogue.
+ * Replaces gemm_kernel + qkv_rope / gemm_res / gemm_gelu_q / gemm_plain
+ * (infer-opt/round13_mxfp8_full/impl/mgx_core.cu:118-444, mgx.py:130-167), the FP4 gemm_kernel
+ * (infer-opt/round14_fp4_full/impl/fp4g_core.cu:153-470, fp4gb.py:74-82), torch._scaled_mm at
+ * infer-opt/round13_mxfp8_full/impl/mx13.py:87-88 and the QuACK GEMMs behind FP4Linear.fwd_*
+ * (infer-opt/round14_fp4_full/impl/fp4util.py:137-159). */
+KF_API int kf_gemm_bs(const kf_gemm_params* p, void* stream);
+
+/* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
+ * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
+ * No counterpart in the reference (its mbarrier waits spin without a bound: infer-opt/round12_lowp_stack/impl/attn16o.cu:77-79). */
+KF_API int kf_check_device_error(void);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,19 @@ KF_FMT = {"mx8": 0, "nv4": 1, "mx4": 2, "bf16": 3}
 KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
 KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV = 1, 2, 4
 
+KF_EPI = {"plain": 0, "res": 1, "rope": 2, "quant": 3}
+KF_G_GELU = 8
+
+
+class GemmParams(C.Structure):
+    """mirror of kf_gemm_params (include/kf_b200.h)."""
+    _fields_ = [("fmt", C.c_int), ("epi", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("out_dtype", C.c_int),
+                ("flags", C.c_int), ("Ntok", C.c_int), ("prefix", C.c_int), ("H", C.c_int), ("out_fmt", C.c_int),
+                ("A", C.c_void_p), ("SFA", C.c_void_p), ("W", C.c_void_p), ("SFW", C.c_void_p), ("ts_a", C.c_void_p),
+                ("ts_w", C.c_void_p), ("bias", C.c_void_p), ("gamma", C.c_void_p), ("R", C.c_void_p), ("sin", C.c_void_p),
+                ("cos", C.c_void_p), ("C", C.c_void_p), ("Qo", C.c_void_p), ("SFo", C.c_void_p), ("tso", C.c_void_p)]
+
+
 _lib = None
 
 
@@ -45,6 +58,8 @@ def lib() -> C.CDLL:
             "kf_quant_rows": [i32, i32, vp, i64, i32, i32, vp, vp, i32, vp, vp, vp],
             "kf_ln_quant": [i32, vp, vp, vp, f32, i32, i32, vp, i32, vp, vp, vp, vp],
             "kf_ln_rows": [vp, vp, vp, f32, i32, i32, i32, vp, vp],
+            "kf_gemm_bs": [C.POINTER(GemmParams), vp],
+            "kf_check_device_error": [],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)

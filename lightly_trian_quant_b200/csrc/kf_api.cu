@@ -2,7 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 
-#include "kf_common.cuh"
+#include "kf_sm100.cuh"
 
 namespace kf {
 
@@ -21,7 +21,33 @@ int cuda_status(cudaError_t e, const char* what) {
   return (int)e;
 }
 
+__device__ unsigned int g_dev_error[4];
+
+unsigned int* dev_error_ptr() {
+  static unsigned int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev < 64 && cached[dev]) return cached[dev];
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_dev_error) != cudaSuccess) return nullptr;
+  if (dev < 64) cached[dev] = static_cast<unsigned int*>(p);
+  return static_cast<unsigned int*>(p);
+}
+
 }  // namespace kf
+
+extern "C" int kf_check_device_error(void) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return kf::cuda_status(e, "cudaDeviceSynchronize");
+  unsigned int h[4] = {0, 0, 0, 0};
+  e = cudaMemcpyFromSymbol(h, kf::g_dev_error, sizeof(h));
+  if (e != cudaSuccess) return kf::cuda_status(e, "cudaMemcpyFromSymbol");
+  if (h[0] == 0) return KF_OK;
+  unsigned int z[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(kf::g_dev_error, z, sizeof(z));
+  kf::set_error("a bounded device wait ran out: code %u at wait site %u in block %u", h[0], h[1], h[2]);
+  return KF_ERR_DEVICE_WAIT;
+}
 
 extern "C" const char* kf_version(void) { return "kf_b200 0.1 sm_100a"; }
 

@@ -1,0 +1,527 @@
+// Block-scaled GEMM  C[M,N] = A[M,K] * W[N,K]^T  on the sm_100a tensor cores (tcgen05.mma, fp32 accumulators in
+// TMEM) with the epilogues of the ViT block fused in.
+//
+//   operands   K-major codes: e4m3 bytes (mx8), packed e2m1 nibbles (nv4 / mx4) or plain bf16; scale factors in
+//              the 128x4 blocked layout, one 512-byte atom per 128 rows x 4 k-blocks
+//   tile       128 x 128 output tile per CTA step, 128 bytes of K per pipeline stage (one TMA swizzle atom per row)
+//   pipeline   warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy), warp 1 = MMA issuer
+//              (tcgen05.cp scale atoms smem -> TMEM, 4 MMAs of 32 K-bytes per stage), warps 2..5 = epilogue
+//              (tcgen05.ld, one accumulator row per thread); two accumulator stages in TMEM so the epilogue of tile
+//              i overlaps the main loop of tile i+1; persistent CTAs, one per SM, static round-robin over tiles
+//   epilogues  PLAIN  out = act(acc*ts + bias)                       -> f32 | bf16 | f16 [M,N]
+//              RES    out = R + gamma * (acc*ts + bias)              -> f32 [M,N]         (proj, fc2)
+//              ROPE   bias + rotary embedding of q,k + relayout      -> bf16 | f16 [3,B,Ntok,H,64]   (qkv)
+//              QUANT  gelu(acc*ts + bias) quantised again            -> codes [M,N] + blocked scales (fc1 -> fc2)
+//
+// Replaces (reference checkout paths): infer-opt/round13_mxfp8_full/impl/mgx_core.cu:118-444 (MXFP8, mma.sync) and
+// infer-opt/round14_fp4_full/impl/fp4g_core.cu:153-470 (NVFP4 / MXFP4, mma.sync); epilogue math per
+// mgx_core.cu:308-426 and fp4g_core.cu:309-382.
+#include <mutex>
+
+#include "kf_sm100.cuh"
+
+namespace kf {
+
+constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
+constexpr int BM = 128, BN = 128, BKB = 128;          // tile rows, tile columns, K bytes per stage
+constexpr int STAGES = 6;
+constexpr int TILE_BYTES = (BM + BN) * BKB;            // 32 KB of operands per stage
+constexpr int SF_STAGE_BYTES = 4096;                   // up to 4 atoms for A and 4 for W per stage
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_SF_COL = 256;                       // accumulators: columns [0,256); scale factors from 256
+constexpr size_t GEMM_SMEM = 1024 + (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + 256;
+
+struct GemmArgs {
+  const uint8_t *sfa, *sfw;
+  const float *ts_a, *ts_w, *bias, *gamma, *R, *sin, *cos, *tso;
+  void* C;
+  uint8_t *Qo, *SFo;
+  int M, N, K;
+  int Ntok, prefix, H, d;
+  int out_dtype, flags, out_fmt;
+  int m_tiles, n_tiles, k_tiles, nkb4;
+  unsigned int* err;
+};
+
+template <int KIND>
+struct KindTraits;
+template <>
+struct KindTraits<KIND_MX8> { static constexpr int ATOMS = 1; };   // 128 elements per stage = 4 k-blocks of 32
+template <>
+struct KindTraits<KIND_NV4> { static constexpr int ATOMS = 4; };   // 256 elements per stage = 16 k-blocks of 16
+template <>
+struct KindTraits<KIND_MX4> { static constexpr int ATOMS = 2; };   // 256 elements per stage = 8 k-blocks of 32
+template <>
+struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
+
+// ------------------------------------------------------------------------------------------------ epilogue pieces
+__device__ __forceinline__ void store_row32(void* base, int out_dtype, const float (&v)[32]) {
+  if (out_dtype == KF_F32) {
+    float4* p = reinterpret_cast<float4*>(base);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (out_dtype == KF_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint4* p = reinterpret_cast<uint4*>(base);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  }
+}
+
+__device__ __forceinline__ void load32(const float* p, float (&v)[32]) {
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float4 t = __ldg(p4 + i);
+    v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+  }
+}
+
+// acc*ts + bias for 32 consecutive columns starting at n0
+__device__ __forceinline__ void scale_bias(const uint32_t (&r)[32], float ts, const float* bias, int n0, float (&v)[32]) {
+  if (bias) {
+    float b[32];
+    load32(bias + n0, b);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(r[i]), ts, b[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ts;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ the kernel
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
+  constexpr int ATOMS = KindTraits<KIND>::ATOMS;
+  constexpr bool SCALED = KIND != KIND_BF16;
+  constexpr uint32_t TX_BYTES = TILE_BYTES + 2 * ATOMS * 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sfs + (size_t)STAGES * SF_STAGE_BYTES);
+  uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 4);
+    mbar_init(&tempty[1], 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const WaitCtx ctx{abort_flag, g.err};
+  const int total_tiles = g.m_tiles * g.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
+        for (int kt = 0; kt < g.k_tiles; ++kt) {
+          if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) { ok = false; break; }
+          mbar_expect_tx(&full[s], TX_BYTES);
+          uint8_t* ta = tiles + (size_t)s * TILE_BYTES;
+          tma_load_2d(ta, &tmA, kt * BKB, m_blk * BM, &full[s]);
+          tma_load_2d(ta + BM * BKB, &tmW, kt * BKB, n_blk * BN, &full[s]);
+          if (SCALED) {
+            uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
+            bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
+            bulk_load_1d(sa + 2048, g.sfw + ((size_t)n_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC = KIND == KIND_BF16 ? idesc_f16(1, BN)
+                                 : KIND == KIND_MX8 ? idesc_bs(0, 1, BN)
+                                 : KIND == KIND_NV4 ? idesc_bs(1, 0, BN)
+                                                    : idesc_bs(1, 1, BN);
+      uint32_t s = 0, ph = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+        const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(&tempty[as], aph ^ 1, ctx, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kt = 0; kt < g.k_tiles; ++kt) {
+          if (!mbar_wait(&full[s], ph, ctx, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * TILE_BYTES);
+          const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + BM * BKB);
+          const uint32_t sf_t = tmem_base + TMEM_SF_COL + (kt & 1) * 32;     // scale factors of A, then of W at +16
+          if (SCALED) {
+            const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
+#pragma unroll
+            for (int a = 0; a < ATOMS; ++a) {
+              tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
+              tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + 2048 + a * 512));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {                                       // 32 K-bytes per MMA
+            const uint32_t acc = (kt | j) != 0;
+            const uint64_t ad = adesc + 2 * j, bd = bdesc + 2 * j;
+            if (KIND == KIND_BF16) {
+              mma_f16(d_tmem, ad, bd, IDESC, acc);
+            } else if (KIND == KIND_MX8) {      // one scale per row per MMA: byte j of the atom's 32-bit word
+              mma_mxf8(d_tmem, ad, bd, idesc_with_sf_id(IDESC, j, j), acc, sf_t, sf_t + 16);
+            } else if (KIND == KIND_NV4) {      // four scales per row per MMA: atom j
+              mma_nvf4(d_tmem, ad, bd, IDESC, acc, sf_t + 4 * j, sf_t + 16 + 4 * j);
+            } else {                            // two scales per row per MMA: half-word (j & 1) of atom j / 2
+              mma_mxf4(d_tmem, ad, bd, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), acc, sf_t + 4 * (j >> 1), sf_t + 16 + 4 * (j >> 1));
+            }
+          }
+          tc_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) tc_commit(&tfull[as]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    float ts = 1.f;
+    if (g.ts_a) ts *= __ldg(g.ts_a);
+    if (g.ts_w) ts *= __ldg(g.ts_w);
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
+      const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
+      const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
+      if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
+      tc_fence_after();
+      const int m = m_blk * BM + row_in_tile;
+      const bool row_ok = m < g.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
+      uint32_t r[32];
+      float v[32];
+
+      if (EPI == KF_EPI_PLAIN) {
+        const int esz = g.out_dtype == KF_F32 ? 4 : 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = n_blk * BN + c * 32;
+          scale_bias(r, ts, g.bias, n0, v);
+          if (g.flags & KF_G_GELU) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+          }
+          if (row_ok) store_row32(static_cast<uint8_t*>(g.C) + ((size_t)m * g.N + n0) * esz, g.out_dtype, v);
+        }
+      } else if (EPI == KF_EPI_RES) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = n_blk * BN + c * 32;
+          scale_bias(r, ts, g.bias, n0, v);
+          if (row_ok) {
+            float gm[32], rr[32];
+            load32(g.gamma + n0, gm);
+            load32(g.R + (size_t)m * g.N + n0, rr);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf(gm[i], v[i], rr[i]);
+            store_row32(static_cast<float*>(g.C) + (size_t)m * g.N + n0, KF_F32, v);
+          }
+        }
+      } else if (EPI == KF_EPI_ROPE) {
+        const int b = m / g.Ntok, t = m - b * g.Ntok;
+        const int nbatch = g.M / g.Ntok;
+#pragma unroll 1
+        for (int hc = 0; hc < BN / 64; ++hc) {
+          uint32_t r2[32];
+          float hi[32];
+          tmem_ld32(taddr + hc * 64, r);
+          tmem_ld32(taddr + hc * 64 + 32, r2);
+          tmem_ld_wait();
+          const int n0 = n_blk * BN + hc * 64;
+          scale_bias(r, ts, g.bias, n0, v);
+          scale_bias(r2, ts, g.bias, n0 + 32, hi);
+          const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
+          if (row_ok) {
+            if (which < 2 && t >= g.prefix) {
+              const float* sp = g.sin + (size_t)(t - g.prefix) * 64;
+              const float* cp = g.cos + (size_t)(t - g.prefix) * 64;
+              float s_lo[32], c_lo[32];
+              load32(sp, s_lo);
+              load32(cp, c_lo);
+              float lo2[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) lo2[i] = v[i] * c_lo[i] - hi[i] * s_lo[i];
+              load32(sp + 32, s_lo);
+              load32(cp + 32, c_lo);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                hi[i] = hi[i] * c_lo[i] + v[i] * s_lo[i];
+                v[i] = lo2[i];
+              }
+            }
+            uint8_t* dst = static_cast<uint8_t*>(g.C) + ((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 * 2;
+            store_row32(dst, g.out_dtype, v);
+            store_row32(dst + 64, g.out_dtype, hi);
+          }
+        }
+      } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
+        const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
+        const bool rb = g.flags & KF_Q_ROUND_BF16;
+        float tso = 1.f;
+        if (g.out_fmt == KF_FMT_NV4) tso = __ldg(g.tso);
+        uint32_t sfw0 = 0, sfw1 = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = n_blk * BN + c * 32;
+          scale_bias(r, ts, g.bias, n0, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v[i] = gelu_erf(v[i]);
+            if (rb) v[i] = bf16_round(v[i]);
+          }
+          const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
+          const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
+          float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            am0 = fmaxf(am0, fabsf(v[i]));
+            am1 = fmaxf(am1, fabsf(v[16 + i]));
+          }
+          int by0, by1;
+          if (g.out_fmt == KF_FMT_MX8) {
+            uint32_t o[8];
+            const float am = fmaxf(am0, am1);
+            quant_mx8<16>(va, am, div_true, o, by0);
+            quant_mx8<16>(vb, am, div_true, o + 4, by0);
+            if (row_ok) {
+              uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
+              p[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              p[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+            sfw0 |= (uint32_t)(row_ok ? by0 : 0) << (8 * c);
+          } else if (g.out_fmt == KF_FMT_MX4) {
+            uint32_t o[4];
+            const float am = fmaxf(am0, am1);
+            quant_mx4<16>(va, am, div_true, o, by0);
+            quant_mx4<16>(vb, am, div_true, o + 2, by0);
+            if (row_ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+            sfw0 |= (uint32_t)(row_ok ? by0 : 0) << (8 * c);
+          } else {
+            uint32_t o[4];
+            quant_nv4<16>(va, am0, tso, div_true, o, by0);
+            quant_nv4<16>(vb, am1, tso, div_true, o + 2, by1);
+            if (row_ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+            const uint32_t two = row_ok ? ((uint32_t)by0 | ((uint32_t)by1 << 8)) : 0u;
+            if (c < 2) sfw0 |= two << (16 * c);
+            else sfw1 |= two << (16 * (c - 2));
+          }
+        }
+        // scale words of this row for the tile's 128 columns (rows beyond M inside the last tile get zeros)
+        if (g.out_fmt == KF_FMT_NV4) {
+          uint32_t* p = reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 8, g.N >> 6));
+          p[0] = sfw0;
+          *reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 8 + 4, g.N >> 6)) = sfw1;
+        } else {
+          *reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 4, g.N >> 7)) = sfw0;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[as]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {                 // a wait ran out: give copies still in flight time to land before the CTA exits
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tmap_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return KF_ERR_UNSUPPORTED;
+  }
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p rows %llu row_bytes %llu)", (int)r, base, (unsigned long long)rows,
+              (unsigned long long)row_bytes);
+    return KF_ERR_BAD_ARGUMENT;
+  }
+  return KF_OK;
+}
+
+int device_sm_count(int* sms) {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+  if (dev < 64 && cached[dev]) {
+    *sms = cached[dev];
+    return KF_OK;
+  }
+  int n = 0;
+  e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaDeviceGetAttribute");
+  if (dev < 64) cached[dev] = n;
+  *sms = n;
+  return KF_OK;
+}
+
+template <int KIND, int EPI>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g, int grid, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
+    if (dev < 64) attr_set[dev] = true;
+  }
+  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmW, g);
+  return cuda_status(cudaGetLastError(), "kf_gemm_bs launch");
+}
+
+template <int KIND>
+static int launch_gemm_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g, int grid, cudaStream_t st) {
+  switch (epi) {
+    case KF_EPI_PLAIN: return launch_gemm<KIND, KF_EPI_PLAIN>(tmA, tmW, g, grid, st);
+    case KF_EPI_RES: return launch_gemm<KIND, KF_EPI_RES>(tmA, tmW, g, grid, st);
+    case KF_EPI_ROPE: return launch_gemm<KIND, KF_EPI_ROPE>(tmA, tmW, g, grid, st);
+    default: return launch_gemm<KIND, KF_EPI_QUANT>(tmA, tmW, g, grid, st);
+  }
+}
+
+static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
+  KF_REQUIRE(p != nullptr, "kf_gemm_bs: null parameter block");
+  const int fmt = p->fmt, epi = p->epi;
+  KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_gemm_bs: unknown operand format %d", fmt);
+  KF_REQUIRE(epi >= KF_EPI_PLAIN && epi <= KF_EPI_QUANT, "kf_gemm_bs: unknown epilogue %d", epi);
+  KF_REQUIRE(p->M >= 0 && p->N > 0 && p->K > 0, "kf_gemm_bs: bad shape M=%d N=%d K=%d", p->M, p->N, p->K);
+  KF_REQUIRE(p->N % BN == 0, "kf_gemm_bs: N=%d must be a multiple of %d", p->N, BN);
+  const int kelems = fmt == KF_FMT_MX8 ? 128 : (fmt == KF_FMT_BF16 ? 64 : 256);   // K elements per 128-byte stage
+  KF_REQUIRE(p->K % kelems == 0, "kf_gemm_bs: K=%d must be a multiple of %d for this format", p->K, kelems);
+  if (p->M == 0) return KF_OK;
+  KF_REQUIRE(p->A && p->W && al16(p->A) && al16(p->W), "kf_gemm_bs: A and W must be non-null and 16-byte aligned");
+  if (fmt != KF_FMT_BF16) KF_REQUIRE(p->SFA && p->SFW && al16(p->SFA) && al16(p->SFW), "kf_gemm_bs: scale tensors must be non-null and 16-byte aligned");
+  KF_REQUIRE(!p->bias || al16(p->bias), "kf_gemm_bs: bias must be 16-byte aligned");
+  if (epi == KF_EPI_PLAIN) {
+    KF_REQUIRE(p->C && al16(p->C), "kf_gemm_bs: PLAIN needs a 16-byte aligned output C");
+    KF_REQUIRE(p->out_dtype == KF_F32 || p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: bad out_dtype %d", p->out_dtype);
+  } else if (epi == KF_EPI_RES) {
+    KF_REQUIRE(p->C && p->R && p->gamma && al16(p->C) && al16(p->R) && al16(p->gamma), "kf_gemm_bs: RES needs 16-byte aligned C, R and gamma");
+  } else if (epi == KF_EPI_ROPE) {
+    KF_REQUIRE(p->C && al16(p->C) && p->sin && p->cos && al16(p->sin) && al16(p->cos), "kf_gemm_bs: ROPE needs 16-byte aligned C, sin and cos");
+    KF_REQUIRE(p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: ROPE output must be bf16 or f16");
+    KF_REQUIRE(p->H > 0 && p->N == 3 * p->H * 64, "kf_gemm_bs: ROPE needs N = 3*H*64 (N=%d, H=%d)", p->N, p->H);
+    KF_REQUIRE(p->Ntok > 0 && p->M % p->Ntok == 0 && p->prefix >= 0 && p->prefix <= p->Ntok, "kf_gemm_bs: ROPE needs M %% Ntok == 0 and 0 <= prefix <= Ntok");
+  } else {
+    KF_REQUIRE(p->out_fmt == KF_FMT_MX8 || p->out_fmt == KF_FMT_NV4 || p->out_fmt == KF_FMT_MX4, "kf_gemm_bs: bad quantise-out format %d", p->out_fmt);
+    KF_REQUIRE(p->Qo && p->SFo && al16(p->Qo) && al16(p->SFo), "kf_gemm_bs: QUANT needs 16-byte aligned Qo and SFo");
+    KF_REQUIRE(p->out_fmt != KF_FMT_NV4 || p->tso, "kf_gemm_bs: nv4 quantise-out needs the per-tensor scale tso");
+  }
+  const uint64_t kbytes = fmt == KF_FMT_MX8 ? (uint64_t)p->K : (fmt == KF_FMT_BF16 ? 2ull * p->K : (uint64_t)p->K / 2);
+  CUtensorMap tmA, tmW;
+  int st = make_tmap_2d_bytes(&tmA, p->A, (uint64_t)p->M, kbytes, kbytes, BM);
+  if (st != KF_OK) return st;
+  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, BN);
+  if (st != KF_OK) return st;
+  GemmArgs g{};
+  g.sfa = static_cast<const uint8_t*>(p->SFA);
+  g.sfw = static_cast<const uint8_t*>(p->SFW);
+  g.ts_a = p->ts_a; g.ts_w = p->ts_w; g.bias = p->bias; g.gamma = p->gamma; g.R = p->R; g.sin = p->sin; g.cos = p->cos; g.tso = p->tso;
+  g.C = p->C; g.Qo = static_cast<uint8_t*>(p->Qo); g.SFo = static_cast<uint8_t*>(p->SFo);
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.Ntok = p->Ntok; g.prefix = p->prefix; g.H = p->H; g.d = p->H * 64;
+  g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
+  g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = p->N / BN; g.k_tiles = (int)(kbytes / BKB);
+  g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
+  g.err = dev_error_ptr();
+  KF_REQUIRE(g.err != nullptr, "kf_gemm_bs: device error word unavailable");
+  int sms = 0;
+  st = device_sm_count(&sms);
+  if (st != KF_OK) return st;
+  const int total = g.m_tiles * g.n_tiles;
+  const int grid = total < sms ? total : sms;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  switch (fmt) {
+    case KF_FMT_MX8: return launch_gemm_epi<KIND_MX8>(epi, tmA, tmW, g, grid, cs);
+    case KF_FMT_NV4: return launch_gemm_epi<KIND_NV4>(epi, tmA, tmW, g, grid, cs);
+    case KF_FMT_MX4: return launch_gemm_epi<KIND_MX4>(epi, tmA, tmW, g, grid, cs);
+    default: return launch_gemm_epi<KIND_BF16>(epi, tmA, tmW, g, grid, cs);
+  }
+}

@@ -18,7 +18,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import KF_DT, KF_FMT, KF_Q_GELU, KF_Q_RECIP_DIV, KF_Q_ROUND_BF16, KfError, check
+from ._lib import KF_DT, KF_EPI, KF_FMT, KF_G_GELU, KF_Q_GELU, KF_Q_RECIP_DIV, KF_Q_ROUND_BF16, GemmParams, KfError, check
 
 VEC = {"mx8": 32, "nv4": 16, "mx4": 32}
 _DT = {torch.float32: KF_DT["f32"], torch.bfloat16: KF_DT["bf16"], torch.float16: KF_DT["f16"]}
@@ -142,3 +142,120 @@ def ln_rows(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, dtype
 
 
 ln_bf16 = ln_rows
+
+
+# ------------------------------------------------------------------------------------------------ weights and GEMMs
+def check_device_error() -> None:
+    """synchronises and raises if a kernel's bounded wait ran out (no reference counterpart)."""
+    check(_lib.lib().kf_check_device_error(), "kf_check_device_error")
+
+
+class QWeight:
+    """Weight [N, K] (nn.Linear layout) quantised once along K with 1-D block scales; fmt "bf16" keeps a bf16 copy.
+    nv4: exact per-tensor scale ts = amax/(6*448) computed once on the host cores (IEEE division).
+    Counterparts: MXW (infer-opt/round13_mxfp8_full/impl/mx13.py:74-84), Lin / FP4Linear weights
+    (infer-opt/round14_fp4_full/impl/stack14b.py:55-66, fp4util.py:114-131)."""
+
+    def __init__(self, W: torch.Tensor, fmt: str, ts: Optional[torch.Tensor] = None):
+        _need_cuda(W)
+        self.N, self.K = W.shape
+        self.fmt = fmt
+        if fmt == "bf16":
+            self.q = W.to(torch.bfloat16).contiguous()
+            self.sf = None
+            self.ts = None
+            return
+        Wf = W.float().contiguous()
+        buf = ActBuf(self.N, self.K, fmt, device=W.device)
+        if fmt == "nv4":
+            if ts is None:
+                import numpy as np
+
+                amax = np.float32(Wf.abs().amax().item())
+                ts = torch.tensor([amax / np.float32(2688.0) if amax > 0 else 1.0], dtype=torch.float32)
+            buf.ts.copy_(ts.reshape(1))
+        quant_rows(Wf, buf)
+        self.q, self.sf, self.ts = buf.q, buf.sf, buf.ts
+
+
+MXW = QWeight
+
+
+def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
+          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0):
+    p = GemmParams()
+    if isinstance(a, ActBuf):
+        if a.fmt != W.fmt or a.K != W.K:
+            raise KfError(f"gemm: operand mismatch A {a.fmt} K={a.K} vs W {W.fmt} K={W.K}")
+        M = a.M
+        p.A, p.SFA, p.ts_a = a.q.data_ptr(), a.sf.data_ptr(), _ptr(a.ts)
+    else:
+        if W.fmt != "bf16" or a.dtype != torch.bfloat16 or a.dim() != 2 or not a.is_contiguous() or a.shape[1] != W.K:
+            raise KfError("gemm: a plain tensor operand must be contiguous bf16 [M, K] with a bf16 weight")
+        _need_cuda(a)
+        M = a.shape[0]
+        p.A = a.data_ptr()
+    p.fmt, p.epi, p.M, p.N, p.K = KF_FMT[W.fmt], KF_EPI[epi], M, W.N, W.K
+    p.W, p.SFW, p.ts_w = W.q.data_ptr(), _ptr(W.sf), _ptr(W.ts)
+    p.out_dtype = _DT[out_dtype]
+    p.flags = (KF_G_GELU if gelu else 0) | (KF_Q_ROUND_BF16 if round_bf16 else 0) | (KF_Q_RECIP_DIV if recip_div else 0)
+    p.Ntok, p.prefix, p.H = Ntok, prefix, H
+    _need_cuda(bias, gamma, R, C, sin, cos)
+    p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
+    if out is not None:
+        p.out_fmt, p.Qo, p.SFo, p.tso = KF_FMT[out.fmt], out.q.data_ptr(), out.sf.data_ptr(), _ptr(out.ts)
+    check(_lib.lib().kf_gemm_bs(p, _stream()), "kf_gemm_bs")
+
+
+def _f32c(t, n, what):
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n):
+        raise KfError(f"gemm: {what} must be contiguous fp32 with {n} elements")
+
+
+def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[M, N] = act(a @ W^T (* ts) + bias) in bf16 / f16 / f32 (mm, gemm_plain, fwd_bias, fwd_gelu, fwd_plain)."""
+    M = a.M if isinstance(a, ActBuf) else a.shape[0]
+    _f32c(bias, W.N, "bias")
+    if out is None:
+        out = torch.empty(M, W.N, dtype=out_dtype, device=W.q.device)
+    _gemm(a, W, "plain", bias=bias, C=out, out_dtype=out.dtype, gelu=gelu)
+    return out
+
+
+mm = gemm_plain
+
+
+def gemm_res(a, W: QWeight, bias, gamma, res: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 [M, N] = res + gamma * (a @ W^T (* ts) + bias)   (proj / fc2; gemm_res, fwd_res)."""
+    M = a.M if isinstance(a, ActBuf) else a.shape[0]
+    _f32c(bias, W.N, "bias")
+    _f32c(gamma, W.N, "gamma")
+    _f32c(res, M * W.N, "res")
+    if out is None:
+        out = torch.empty_like(res)
+    _gemm(a, W, "res", bias=bias, gamma=gamma, R=res, C=out, out_dtype=torch.float32)
+    return out
+
+
+def qkv_rope(a, W: QWeight, bias, sin, cos, Ntok: int, prefix: int, H: int, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """a [M=B*Ntok, d] -> physical [3, B, Ntok, H, 64] (bias + RoPE in fp32 on q and k of tokens >= prefix)."""
+    M = a.M if isinstance(a, ActBuf) else a.shape[0]
+    _f32c(bias, W.N, "bias")
+    if sin.dtype != torch.float32 or cos.dtype != torch.float32 or not sin.is_contiguous() or not cos.is_contiguous() \
+            or sin.shape[-1] != 64 or sin.shape[0] < Ntok - prefix or cos.shape != sin.shape:
+        raise KfError("qkv_rope: sin / cos must be contiguous fp32 [>= Ntok - prefix, 64]")
+    if M % Ntok:
+        raise KfError("qkv_rope: M must be a multiple of Ntok")
+    out = torch.empty(3, M // Ntok, Ntok, H, 64, dtype=out_dtype, device=W.q.device)
+    _gemm(a, W, "rope", bias=bias, sin=sin, cos=cos, C=out, out_dtype=out_dtype, Ntok=Ntok, prefix=prefix, H=H)
+    return out
+
+
+def gemm_gelu_q(a, W: QWeight, bias, out: ActBuf, *, round_bf16: bool = False, recip_div: bool = False) -> ActBuf:
+    """out = quantise(gelu(a @ W^T (* ts) + bias)) in out.fmt: fc1 writes fc2's operand and blocked scales directly."""
+    M = a.M if isinstance(a, ActBuf) else a.shape[0]
+    _f32c(bias, W.N, "bias")
+    if (out.M, out.K) != (M, W.N):
+        raise KfError(f"gemm_gelu_q: out must be [{M}, {W.N}], got [{out.M}, {out.K}]")
+    _gemm(a, W, "quant", bias=bias, out=out, round_bf16=round_bf16, recip_div=recip_div)
+    return out

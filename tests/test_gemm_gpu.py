@@ -1,0 +1,196 @@
+"""GPU parity of the tcgen05 block-scaled GEMM (through the C-ABI) against the dequantise-then-matmul oracle.
+
+Tolerances: fp32 output vs the float64 product of the dequantised operands: rel. Frobenius <= 2e-5 (fp32 accumulation);
+16-bit outputs: <= 2e-3 (the bound the task states; bf16 output rounding alone is about 1.7e-3)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm_oracle as go
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+
+FMTS = ["mx8", "nv4", "mx4"]
+
+
+def _ops():
+    from lightly_trian_quant_b200 import ops
+
+    return ops
+
+
+def _mk_x(M, K, seed, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    ch = torch.randperm(K, generator=g)[: max(1, K // 100)]
+    x[:, ch] *= 20
+    return x.to(dtype)
+
+
+def _mk_w(N, K, seed, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(N, K, generator=g) * std).to(torch.bfloat16)
+
+
+def _quant_pair(x, w, fmt):
+    """quantise activation and weight on the GPU; return the device containers and their dequantised fp32 values."""
+    ops = _ops()
+    M, K = x.shape
+    N = w.shape[0]
+    if fmt == "bf16":
+        return x.cuda().contiguous(), ops.QWeight(w.cuda(), "bf16"), x.float().numpy(), w.float().numpy()
+    a = ops.ActBuf(M, K, fmt, device="cuda")
+    if fmt == "nv4":
+        a.ts.copy_(torch.from_numpy(qo.nv4_ts(x.float().numpy())))
+    ops.quant_rows(x.cuda(), a)
+    W = ops.QWeight(w.cuda(), fmt)
+    torch.cuda.synchronize()
+    ts_a = a.ts.cpu().numpy() if a.ts is not None else None
+    ts_w = W.ts.cpu().numpy() if W.ts is not None else None
+    ad = go.dequant_operand(a.q.cpu().numpy(), a.sf.cpu().numpy(), ts_a, fmt, M, K)
+    wd = go.dequant_operand(W.q.cpu().numpy(), W.sf.cpu().numpy(), ts_w, fmt, N, K)
+    return a, W, ad, wd
+
+
+@pytest.mark.parametrize("fmt", FMTS + ["bf16"])
+@pytest.mark.parametrize("shape", [(128, 128, 256), (128, 256, 512), (200, 128, 1024), (1, 384, 768)])
+def test_gemm_plain_small_f32(fmt, shape):
+    ops = _ops()
+    M, N, K = shape
+    x, w = _mk_x(M, K, 1), _mk_w(N, K, 2, std=0.05)
+    a, W, ad, wd = _quant_pair(x, w, fmt)
+    y = ops.gemm_plain(a, W, out_dtype=torch.float32)
+    ops.check_device_error()
+    ref = go.matmul_ref(ad, wd)
+    assert go.rel_fro(y.cpu().numpy(), ref) < 2e-5
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_gemm_c1_fc1_bias(fmt):
+    """BASELINE config 1: X bf16 [1605,1024] (1 % channels x20), W [4096,1024] ~ N(0,0.02), bias: bf16 out within 2e-3."""
+    ops = _ops()
+    gc = torch.Generator().manual_seed(0)
+    X = torch.randn(1605, 1024, generator=gc)
+    ch = torch.randperm(1024, generator=gc)[:10]
+    X[:, ch] *= 20
+    W_ = (torch.randn(4096, 1024, generator=gc) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn(4096, generator=gc) * 0.02).to(torch.bfloat16).float()
+    a, W, ad, wd = _quant_pair(X.to(torch.bfloat16), W_, fmt)
+    ref = go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)
+    y32 = ops.gemm_plain(a, W, bias.cuda(), out_dtype=torch.float32)
+    y16 = ops.gemm_plain(a, W, bias.cuda(), out_dtype=torch.bfloat16)
+    ops.check_device_error()
+    assert go.rel_fro(y32.cpu().numpy(), ref) < 2e-5
+    assert go.rel_fro(y16.float().cpu().numpy(), ref) < 2e-3
+    # operands are the oracle's bytes: the same slice as the golden fixture
+    q, s, _ = qo.quantize(X.to(torch.bfloat16).float().numpy(), fmt, a.ts.cpu().numpy() if a.ts is not None else None)
+    assert np.array_equal(a.q.cpu().numpy(), q)
+
+
+@pytest.mark.parametrize("fmt", FMTS + ["bf16"])
+def test_gemm_res(fmt):
+    ops = _ops()
+    M, N, K = 333, 256, 1024
+    x, w = _mk_x(M, K, 3), _mk_w(N, K, 4)
+    g = torch.Generator().manual_seed(5)
+    bias = torch.randn(N, generator=g) * 0.1
+    gamma = torch.rand(N, generator=g)
+    R = torch.randn(M, N, generator=g) * 3
+    a, W, ad, wd = _quant_pair(x, w, fmt)
+    out = ops.gemm_res(a, W, bias.cuda(), gamma.cuda(), R.cuda())
+    ops.check_device_error()
+    ref = go.epi_res(go.matmul_ref(ad, wd), bias.numpy(), gamma.numpy(), R.numpy())
+    assert go.rel_fro(out.cpu().numpy(), ref) < 2e-6
+    # in place on the residual stream
+    Rc = R.cuda()
+    ops.gemm_res(a, W, bias.cuda(), gamma.cuda(), Rc, out=Rc)
+    assert torch.equal(Rc, out)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_gemm_qkv_rope(fmt, out_dtype):
+    ops = _ops()
+    B, Ntok, prefix, H = 2, 133, 5, 4
+    d = H * 64
+    M = B * Ntok
+    x, w = _mk_x(M, d, 6), _mk_w(3 * d, d, 7, std=0.05)
+    g = torch.Generator().manual_seed(8)
+    bias = torch.randn(3 * d, generator=g) * 0.1
+    sin = torch.randn(Ntok - prefix, 64, generator=g)
+    cos = torch.randn(Ntok - prefix, 64, generator=g)
+    a, W, ad, wd = _quant_pair(x, w, fmt)
+    out = ops.qkv_rope(a, W, bias.cuda(), sin.cuda(), cos.cuda(), Ntok, prefix, H, out_dtype=out_dtype)
+    ops.check_device_error()
+    assert out.shape == (3, B, Ntok, H, 64)
+    y = go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)
+    ref = go.epi_rope(y, sin.numpy(), cos.numpy(), Ntok, prefix, H)
+    tol = 2.5e-3 if out_dtype == torch.bfloat16 else 4e-4
+    assert go.rel_fro(out.float().cpu().numpy(), ref) < tol
+    # prefix rows and v are not rotated
+    ref_v = y.reshape(B, Ntok, 3, H, 64)[:, :, 2]
+    assert go.rel_fro(out[2].float().cpu().numpy(), ref_v) < tol
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("round_bf16", [False, True])
+def test_gemm_fc1_gelu_quant_out(fmt, round_bf16):
+    """fc1 with bias + GELU + quantise-out: the written operand must be the oracle quantisation of the kernel's own
+    pre-quantisation values up to the ulp noise of accumulation order; compared through the dequantised operand."""
+    ops = _ops()
+    M, N, K = 300, 512, 1024
+    x, w = _mk_x(M, K, 9), _mk_w(N, K, 10, std=0.03)
+    g = torch.Generator().manual_seed(11)
+    bias = torch.randn(N, generator=g) * 0.1
+    a, W, ad, wd = _quant_pair(x, w, fmt)
+    pre = go.gelu_erf(go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)).astype(np.float32)
+    if round_bf16:
+        pre = qo.bf16_round(pre)
+    out = ops.ActBuf(M, N, fmt, device="cuda")
+    out.q.fill_(0xAA)
+    out.sf.fill_(0xAA)
+    tso = None
+    if fmt == "nv4":
+        tso = qo.nv4_ts(pre) * np.float32(2.0)
+        out.ts.copy_(torch.from_numpy(tso))
+    ops.gemm_gelu_q(a, W, bias.cuda(), out, round_bf16=round_bf16)
+    ops.check_device_error()
+    eq, es, _ = qo.quantize(pre, fmt, tso)
+    esb = qo.to_blocked(es).reshape(-1)
+    q = out.q.cpu().numpy()
+    sf = out.sf.cpu().numpy()
+    assert (sf == esb).mean() > 0.995
+    assert (q == eq).mean() > (0.97 if fmt == "mx8" else 0.985)
+    got = go.dequant_operand(q, sf, tso, fmt, M, N)
+    exp = qo.dequant(eq, es, tso, fmt)
+    qerr = go.rel_fro(exp, pre)                       # the quantisation error itself
+    assert go.rel_fro(got, pre) < 1.05 * qerr + 1e-6  # the kernel's operand is as good a quantisation of the same values
+    # padded scale rows are zero
+    blocked = sf.reshape(-(-M // 128), -1, 32, 4, 4)
+    full = qo.from_blocked(blocked, -(-M // 128) * 128, N // qo.VEC[fmt])
+    assert not full[M:].any()
+
+
+@pytest.mark.parametrize("fmt", ["nv4", "mx8"])
+@pytest.mark.parametrize("kind", ["qkv", "proj", "fc1", "fc2"])
+def test_gemm_vitl_shapes_batch8(fmt, kind):
+    """config 2 shapes at M = 1605*8: a 512-row window of the output is checked against the oracle."""
+    ops = _ops()
+    K, N = {"qkv": (1024, 3072), "proj": (1024, 1024), "fc1": (1024, 4096), "fc2": (4096, 1024)}[kind]
+    M = 1605 * 8
+    x, w = _mk_x(M, K, 12), _mk_w(N, K, 13)
+    a, W, _, wd = _quant_pair(x, w, fmt)
+    y = ops.gemm_plain(a, W, out_dtype=torch.float32)
+    ops.check_device_error()
+    rows = slice(M - 512, M)
+    ts_a = a.ts.cpu().numpy() if a.ts is not None else None
+    nb = K // qo.VEC[fmt]
+    s2 = qo.from_blocked(a.sf.cpu().numpy().reshape(-(-M // 128), nb // 4, 32, 4, 4), M, nb)
+    ad = qo.dequant(a.q.cpu().numpy()[rows], s2[rows], ts_a, fmt)
+    assert go.rel_fro(y[rows].cpu().numpy(), go.matmul_ref(ad, wd)) < 2e-5
+    # linearity / row independence: the first 128 rows alone give the same values
+    a1 = ops.ActBuf(128, K, fmt, device="cuda", ts=a.ts)
+    ops.quant_rows(x[:128].cuda(), a1)
+    y1 = ops.gemm_plain(a1, W, out_dtype=torch.float32)
+    assert torch.equal(y1, y[:128])
