@@ -123,6 +123,12 @@ typedef struct kf_gemm_params {
  * (infer-opt/round14_fp4_full/impl/fp4util.py:137-159). */
 KF_API int kf_gemm_bs(const kf_gemm_params* p, void* stream);
 
+/* FlashAttention-style forward, head dimension 64, no mask: qkv [3, B, N, H, 64] (bf16 | f16, RoPE already applied,
+ * the layout KF_EPI_ROPE writes) -> O [B, N, H*64] of the same type; softmax scale 1/8, fp32 statistics and
+ * accumulators.  `pre` is the reference's power-of-two Q pre-scale for fp16 accumulation; it is neutral here.
+ * Replaces attn16_fwd / a16::fwd_kernel (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404). */
+KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream);
+
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
  * No counterpart in the reference (its mbarrier waits spin without a bound: infer-opt/round12_lowp_stack/impl/attn16o.cu:77-79). */

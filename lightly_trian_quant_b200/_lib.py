@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
             "kf_ln_rows": [vp, vp, vp, f32, i32, i32, i32, vp, vp],
             "kf_gemm_bs": [C.POINTER(GemmParams), vp],
             "kf_check_device_error": [],
+            "kf_attn_fwd": [i32, vp, vp, i32, i32, i32, f32, vp],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)

@@ -1,0 +1,322 @@
+// FlashAttention-style forward on the sm_100a tensor cores (tcgen05.mma kind::f16, fp32 S and O in TMEM), head
+// dimension 64, no mask, RoPE already applied by the qkv epilogue.
+//
+//   input    qkv [3, B, N, H, 64] bf16 | f16 (the physical layout the qkv GEMM epilogue writes)
+//   output   O [B, N, H*64] bf16 | f16 (the proj GEMM's A operand before quantisation)
+//   CTA      128 query rows of one (batch, head); key tiles of 128; two CTAs share an SM so one CTA's softmax
+//            overlaps the other's MMAs
+//   roles    warps 0..3: softmax (one query row per thread: tcgen05.ld S, running max / sum in fp32, P -> 16-bit ->
+//            swizzled smem, O_tile accumulation with the rescale factor in registers);
+//            warp 4: TMA producer (Q once, K / V double buffered, 4-D tensor maps so rows past N read zero);
+//            warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16;  O_tile = P V: 8 MMAs of K=16, V as the MN-major operand)
+//   numerics softmax scale 1/8 folded into exp2; running max never reset; m, l, O in fp32; P rounded to the input
+//            16-bit type; every mbarrier wait is bounded.
+//
+// Replaces a16::fwd_kernel / attn16_fwd (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404; mma.sync m16n8k16 +
+// TMA on sm_120).  The power-of-two Q pre-scale `pre` of the reference protects its fp16 accumulators
+// (attn16o.cu:184-194); with fp32 accumulation it is mathematically neutral and is accepted but not applied.
+#include "kf_sm100.cuh"
+
+namespace kf {
+
+constexpr int AT_BM = 128, AT_BN = 128, AT_D = 64;
+constexpr int AT_THREADS = 192;
+constexpr int AT_TILE = AT_BM * AT_D * 2;             // 16 KB: one [128 x 64] 16-bit tile
+constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_TILE, AT_OFF_V = 3 * AT_TILE, AT_OFF_P = 5 * AT_TILE, AT_OFF_BAR = 7 * AT_TILE;
+constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
+constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128;
+
+struct AttnArgs {
+  void* O;
+  int B, N, H;
+  int f16;          // 0 = bf16, 1 = f16
+  float scale_log2; // softmax scale * log2(e)
+  unsigned int* err;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
+  if (f16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const AttnArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AT_OFF_BAR);
+  uint64_t *q_full = bars, *k_full = bars + 1, *v_full = bars + 3, *kv_empty = bars + 5, *s_full = bars + 7, *p_full = bars + 8, *o_full = bars + 9;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tiles = (a.N + AT_BM - 1) / AT_BM;
+  const int qt = blockIdx.x % q_tiles;
+  const int bh = blockIdx.x / q_tiles;
+  const int h = bh % a.H, b = bh / a.H;
+  const int n_kt = (a.N + AT_BN - 1) / AT_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;   // the swizzled tiles need a 1024-byte aligned base
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_holder, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const WaitCtx ctx{abort_flag, a.err};
+  const bool bad_align = *abort_flag != 0;
+  if (bad_align && threadIdx.x == 0 && atomicCAS(&a.err[0], 0u, 99u) == 0u) {
+    a.err[1] = 100;
+    a.err[2] = blockIdx.x;
+  }
+
+  if (bad_align) {
+    // nothing was issued; fall through to the teardown
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      mbar_expect_tx(q_full, AT_TILE);
+      tma_load_4d(smem + AT_OFF_Q, &tmQ, 0, h, qt * AT_BM, b, q_full);
+      for (int j = 0; j < n_kt; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, ctx, 11)) break;
+        mbar_expect_tx(&k_full[st], AT_TILE);
+        tma_load_4d(smem + AT_OFF_K + st * AT_TILE, &tmK, 0, h, j * AT_BN, b, &k_full[st]);
+        mbar_expect_tx(&v_full[st], AT_TILE);
+        tma_load_4d(smem + AT_OFF_V + st * AT_TILE, &tmV, 0, h, j * AT_BN, b, &v_full[st]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t fmt = a.f16 ? 0u : 1u;
+      const uint32_t idesc_s = idesc_f16(fmt, AT_BN);
+      const uint32_t idesc_o = idesc_f16(fmt, AT_D) | (1u << 16);          // B (= V) is MN-major
+      const uint64_t qdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_Q));
+      const uint64_t pdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_P));
+      const uint32_t t_s = tmem_base + AT_COL_S, t_o = tmem_base + AT_COL_O;
+      bool ok = mbar_wait(q_full, 0, ctx, 12);
+      if (ok) ok = mbar_wait(&k_full[0], 0, ctx, 13);
+      if (ok) {
+        tc_fence_after();
+        const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K));
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
+        tc_commit(s_full);
+      }
+      for (int j = 0; j < n_kt && ok; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(p_full, j & 1, ctx, 14)) break;
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1, ctx, 15)) break;
+        tc_fence_after();
+        const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_TILE));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // A: 16 keys = 32 bytes inside key atom kk/4 of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
+          const uint64_t ad = pdesc + (uint64_t)((kk >> 2) * (AT_TILE >> 4) + (kk & 3) * 2);
+          const uint64_t bd = vdesc + (uint64_t)(kk * (2048 >> 4));
+          mma_f16(t_o, ad, bd, idesc_o, kk != 0);
+        }
+        tc_commit(o_full);
+        tc_commit(&kv_empty[st]);
+        if (j + 1 < n_kt) {
+          const int sn = (j + 1) & 1;
+          if (!mbar_wait(&k_full[sn], ((j + 1) >> 1) & 1, ctx, 16)) break;
+          tc_fence_after();
+          const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + sn * AT_TILE));
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
+          tc_commit(s_full);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax: thread = query row
+    const int row = warp * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const float sc = a.scale_log2;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    uint8_t* prow = smem + AT_OFF_P + row * 128;
+    const int sw = row & 7;
+    bool ok = true;
+    for (int j = 0; j < n_kt; ++j) {
+      if (!mbar_wait(s_full, j & 1, ctx, 17)) { ok = false; break; }
+      tc_fence_after();
+      const int kbase = j * AT_BN;
+      const bool tail = kbase + AT_BN > a.N;
+      uint32_t r[32];
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(t_lane + AT_COL_S + c * 32, r);
+        tmem_ld_wait();
+        if (tail) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kbase + c * 32 + i < a.N) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = ex2((m_run - m_new) * sc);
+      const float mneg = -m_new * sc;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld32(t_lane + AT_COL_S + c * 32, r);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = ex2(fmaf(__uint_as_float(r[i]), sc, mneg));
+          if (tail && kbase + c * 32 + i >= a.N) e = 0.f;
+          p[i] = e;
+          sum += e;
+        }
+        // 32 keys = 64 bytes = four 16-byte chunks of this row inside key atom c/2, XOR-swizzled by the row
+        uint8_t* atom = prow + (c >> 1) * AT_TILE;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int chunk = ((c & 1) * 4 + i) ^ sw;
+          *reinterpret_cast<uint4*>(atom + chunk * 16) =
+              make_uint4(pack16(p[8 * i], p[8 * i + 1], a.f16), pack16(p[8 * i + 2], p[8 * i + 3], a.f16),
+                         pack16(p[8 * i + 4], p[8 * i + 5], a.f16), pack16(p[8 * i + 6], p[8 * i + 7], a.f16));
+        }
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+      if (!mbar_wait(o_full, j & 1, ctx, 18)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r2[32];
+      tmem_ld32(t_lane + AT_COL_O, r);
+      tmem_ld32(t_lane + AT_COL_O + 32, r2);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        o[i] = fmaf(o[i], alpha, __uint_as_float(r[i]));
+        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(r2[i]));
+      }
+      tc_fence_before();
+    }
+    const int n = qt * AT_BM + row;
+    if (ok && n < a.N) {
+      const float inv = 1.0f / l_run;
+      uint32_t w[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) w[i] = pack16(o[2 * i] * inv, o[2 * i + 1] * inv, a.f16);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.O) + (((size_t)b * a.N + n) * a.H + h) * (AT_D * 2));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && !bad_align) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
+// 4-D tensor map over one of q / k / v: dims (64, H, N, B) of 16-bit elements, box (64, 1, 128, 1), 128-byte swizzle;
+// rows past N are out of bounds in their own dimension and read as zero.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_tmap_qkv(CUtensorMap* map, const void* base, int B, int N, int H) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return KF_ERR_UNSUPPORTED;
+  }
+  EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(p);
+  cuuint64_t dims[4] = {64, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
+  cuuint64_t strides[3] = {128, (cuuint64_t)H * 128, (cuuint64_t)N * H * 128};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (qkv) failed with CUresult %d", (int)r);
+    return KF_ERR_BAD_ARGUMENT;
+  }
+  return KF_OK;
+}
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream) {
+  (void)pre;
+  KF_REQUIRE(dtype == KF_BF16 || dtype == KF_F16, "kf_attn_fwd: dtype must be bf16 or f16");
+  KF_REQUIRE(B >= 0 && N > 0 && H > 0, "kf_attn_fwd: bad shape B=%d N=%d H=%d", B, N, H);
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(qkv && O && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(O) & 15) == 0,
+             "kf_attn_fwd: qkv and O must be non-null and 16-byte aligned");
+  const size_t plane = (size_t)B * N * H * 64 * 2;
+  const uint8_t* base = static_cast<const uint8_t*>(qkv);
+  CUtensorMap tq, tk, tv;
+  int st = make_tmap_qkv(&tq, base, B, N, H);
+  if (st != KF_OK) return st;
+  st = make_tmap_qkv(&tk, base + plane, B, N, H);
+  if (st != KF_OK) return st;
+  st = make_tmap_qkv(&tv, base + 2 * plane, B, N, H);
+  if (st != KF_OK) return st;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(attn_fwd_kernel)");
+    if (dev < 64) attr_set[dev] = true;
+  }
+  AttnArgs a{};
+  a.O = O; a.B = B; a.N = N; a.H = H; a.f16 = dtype == KF_F16;
+  a.scale_log2 = 0.125f * 1.4426950408889634f;
+  a.err = dev_error_ptr();
+  KF_REQUIRE(a.err != nullptr, "kf_attn_fwd: device error word unavailable");
+  const int q_tiles = (N + AT_BM - 1) / AT_BM;
+  attn_fwd_kernel<<<B * H * q_tiles, AT_THREADS, AT_SMEM, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, a);
+  return cuda_status(cudaGetLastError(), "kf_attn_fwd launch");
+}

@@ -259,3 +259,20 @@ def gemm_gelu_q(a, W: QWeight, bias, out: ActBuf, *, round_bf16: bool = False, r
         raise KfError(f"gemm_gelu_q: out must be [{M}, {W.N}], got [{out.M}, {out.K}]")
     _gemm(a, W, "quant", bias=bias, out=out, round_bf16=round_bf16, recip_div=recip_div)
     return out
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def attn_fwd(qkv: torch.Tensor, pre: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """qkv contiguous [3, B, N, H, 64] bf16 | f16 (RoPE applied) -> O [B, N, H*64] of the same dtype.
+    Counterpart: attn16_fwd(qkv, kind, pre) (infer-opt/round12_lowp_stack/impl/attn16o.cu:389-404)."""
+    _need_cuda(qkv)
+    if qkv.dim() != 5 or qkv.shape[0] != 3 or qkv.shape[4] != 64 or not qkv.is_contiguous() or qkv.dtype not in (torch.bfloat16, torch.float16):
+        raise KfError("attn_fwd: qkv must be contiguous [3, B, N, H, 64] bf16 or f16")
+    _, B, N, H, _ = qkv.shape
+    if out is None:
+        out = torch.empty(B, N, H * 64, dtype=qkv.dtype, device=qkv.device)
+    check(_lib.lib().kf_attn_fwd(_DT[qkv.dtype], qkv.data_ptr(), out.data_ptr(), B, N, H, float(pre), _stream()), "kf_attn_fwd")
+    return out
+
+
+attn16_fwd = attn_fwd
