@@ -52,7 +52,8 @@ extern "C" {
 #define KF_EPI_QUANT 3 /* gelu(acc*ts + bias) quantised to out_fmt    codes [M,N] + blocked scales   */
 
 /* GEMM flags (share the flag word with KF_Q_ROUND_BF16 / KF_Q_RECIP_DIV, which act on the QUANT epilogue) */
-#define KF_G_GELU 8 /* PLAIN: apply gelu_erf after the bias */
+#define KF_G_GELU 8        /* PLAIN: apply gelu_erf after the bias */
+#define KF_G_ROUND_BF16 16 /* PLAIN: round the value to bf16 before storing (matters for an f32 output) */
 
 /* Library version and the SM architecture the kernels were built for ("sm_100a"). */
 KF_API const char* kf_version(void);
@@ -113,6 +114,9 @@ typedef struct kf_gemm_params {
   void* Qo;           /* QUANT: output codes [M, N] (mx8) or [M, N/2]                                          */
   void* SFo;          /* QUANT: output blocked scales of an [M, N] operand                                     */
   const float* tso;   /* QUANT to nv4: static per-tensor scale of the output                                   */
+  /* PLAIN only: output row of GEMM row m is (m / group) * stride + offset + m % group; group 0 = identity.
+   * Lets the patch-embed GEMM write straight into the token stream behind each image's cls / register rows. */
+  int out_row_group, out_row_stride, out_row_offset;
 } kf_gemm_params;
 
 /* Block-scaled GEMM on tcgen05 with a fused epilogue.
@@ -122,6 +126,38 @@ typedef struct kf_gemm_params {
  * infer-opt/round13_mxfp8_full/impl/mx13.py:87-88 and the QuACK GEMMs behind FP4Linear.fwd_*
  * (infer-opt/round14_fp4_full/impl/fp4util.py:137-159). */
 KF_API int kf_gemm_bs(const kf_gemm_params* p, void* stream);
+
+/* Final LayerNorm of the fp32 token stream x [B, Ntok, d] with the row gather of the EoMT head: query rows
+ * (t < Q) -> qb bf16 [B*Q, d], patch rows (t >= Q + npre) -> xb bf16 [B*(Ntok-Q-npre), d].
+ * Replaces the LN + gather part of tail_ln (infer-opt/round11_attn_tier0/impl/head_ext11.cu:252-320). */
+KF_API int kf_ln_tail(const float* x, const float* w, const float* b, float eps, int B, int Ntok, int Q, int npre, int d,
+                      void* qb, void* xb, void* stream);
+
+/* Patch gathering for the patch-embed GEMM: x bf16 [B, 3, S, S] -> bf16 [B*(S/16)^2, 768], k = c*256 + py*16 + px.
+ * Replaces the implicit im2col of patch_gemm_kernel (infer-opt/round11_attn_tier0/impl/patch_embed.cu:76-194). */
+KF_API int kf_im2col_patch16(const void* x, void* out, int B, int S, void* stream);
+
+/* ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] (ConvTranspose2d k2 s2 as a GEMM, column (dy*2+dx)*C + c) -> bias + GELU +
+ * pixel shuffle + depthwise 3x3 (dww fp32 [9, C], tap-major, zero padding) + LayerNorm2D -> out bf16 [B, 2Hs, 2Ws, C].
+ * Replaces dw_ln (infer-opt/round11_attn_tier0/impl/head_ext11.cu:72-250) = ScaleBlock.forward after conv1
+ * (src/lightly_train/_task_models/dinov3_eomt_semantic_segmentation/scale_block.py:39-44). */
+KF_API int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B,
+                    int Hs, int Ws, int C, float eps, void* stream);
+
+/* Per-pixel semantic scores: scores[b,c,p] = sum_q sigmoid(mask_logits[b,q,p]) * softmax(class_logits[b,q,:])[c]
+ * (fp32 [B, ncls+1, HW], optional) and labels[b,p] = argmax over the ncls real classes (uint8, optional).
+ * mask_logits bf16 [B, Q, HW], class_logits bf16 [B, Q, ncls+1].
+ * Replaces to_per_pixel_logits_semantic + argmax (src/lightly_train/_task_models/dinov3_eomt_semantic_segmentation/
+ * task_model.py:583-594; scripts/infer_dinov3_eomt_head_video.py:90-94). */
+KF_API int kf_semantic(const void* mask_logits, const void* class_logits, int B, int Q, int ncls, int HW, float* scores,
+                       uint8_t* labels, void* stream);
+
+/* Frame pre-processing: uint8 [B, Hi, Wi, 3] -> bf16 [B, 3, So, So], bilinear with antialiasing, then
+ * (v/255 - mean[c]) / std[c]; mean3 / std3 are HOST arrays of three floats.
+ * Replaces prep_kernel (infer-opt/round7_head_postprocess/impl/postfuse_ext.cu:30-72) / base_prep
+ * (infer-opt/common/model_factory.py:99). */
+KF_API int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, int Wi, int So, const float* mean3,
+                          const float* std3, void* stream);
 
 /* FlashAttention-style forward, head dimension 64, no mask: qkv [3, B, N, H, 64] (bf16 | f16, RoPE already applied,
  * the layout KF_EPI_ROPE writes) -> O [B, N, H*64] of the same type; softmax scale 1/8, fp32 statistics and

@@ -18,7 +18,7 @@ KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
 KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV = 1, 2, 4
 
 KF_EPI = {"plain": 0, "res": 1, "rope": 2, "quant": 3}
-KF_G_GELU = 8
+KF_G_GELU, KF_G_ROUND_BF16 = 8, 16
 
 
 class GemmParams(C.Structure):
@@ -27,7 +27,8 @@ class GemmParams(C.Structure):
                 ("flags", C.c_int), ("Ntok", C.c_int), ("prefix", C.c_int), ("H", C.c_int), ("out_fmt", C.c_int),
                 ("A", C.c_void_p), ("SFA", C.c_void_p), ("W", C.c_void_p), ("SFW", C.c_void_p), ("ts_a", C.c_void_p),
                 ("ts_w", C.c_void_p), ("bias", C.c_void_p), ("gamma", C.c_void_p), ("R", C.c_void_p), ("sin", C.c_void_p),
-                ("cos", C.c_void_p), ("C", C.c_void_p), ("Qo", C.c_void_p), ("SFo", C.c_void_p), ("tso", C.c_void_p)]
+                ("cos", C.c_void_p), ("C", C.c_void_p), ("Qo", C.c_void_p), ("SFo", C.c_void_p), ("tso", C.c_void_p),
+                ("out_row_group", C.c_int), ("out_row_stride", C.c_int), ("out_row_offset", C.c_int)]
 
 
 _lib = None
@@ -61,6 +62,11 @@ def lib() -> C.CDLL:
             "kf_gemm_bs": [C.POINTER(GemmParams), vp],
             "kf_check_device_error": [],
             "kf_attn_fwd": [i32, vp, vp, i32, i32, i32, f32, vp],
+            "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp],
+            "kf_im2col_patch16": [vp, vp, i32, i32, vp],
+            "kf_dw_ln": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
+            "kf_semantic": [vp, vp, i32, i32, i32, i32, vp, vp, vp],
+            "kf_resize_norm": [vp, vp, i32, i32, i32, i32, C.POINTER(C.c_float), C.POINTER(C.c_float), vp],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)

@@ -41,6 +41,7 @@ struct GemmArgs {
   int Ntok, prefix, H, d;
   int out_dtype, flags, out_fmt;
   int m_tiles, n_tiles, k_tiles, nkb4;
+  int row_group, row_stride, row_offset;   // PLAIN: output row = (m / group) * stride + offset + m % group (group 0: identity)
   unsigned int* err;
 };
 
@@ -237,6 +238,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       if (EPI == KF_EPI_PLAIN) {
         const int esz = g.out_dtype == KF_F32 ? 4 : 2;
+        const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           tmem_ld32(taddr + c * 32, r);
@@ -247,7 +249,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
           }
-          if (row_ok) store_row32(static_cast<uint8_t*>(g.C) + ((size_t)m * g.N + n0) * esz, g.out_dtype, v);
+          if (g.flags & KF_G_ROUND_BF16) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]);
+          }
+          if (row_ok) store_row32(static_cast<uint8_t*>(g.C) + ((size_t)orow * g.N + n0) * esz, g.out_dtype, v);
         }
       } else if (EPI == KF_EPI_RES) {
 #pragma unroll 1
@@ -481,6 +487,8 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   KF_REQUIRE(!p->bias || al16(p->bias), "kf_gemm_bs: bias must be 16-byte aligned");
   if (epi == KF_EPI_PLAIN) {
     KF_REQUIRE(p->C && al16(p->C), "kf_gemm_bs: PLAIN needs a 16-byte aligned output C");
+    KF_REQUIRE(p->out_row_group >= 0 && (p->out_row_group == 0 || (p->out_row_stride >= p->out_row_group && p->out_row_offset >= 0)),
+               "kf_gemm_bs: bad output row mapping group=%d stride=%d offset=%d", p->out_row_group, p->out_row_stride, p->out_row_offset);
     KF_REQUIRE(p->out_dtype == KF_F32 || p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: bad out_dtype %d", p->out_dtype);
   } else if (epi == KF_EPI_RES) {
     KF_REQUIRE(p->C && p->R && p->gamma && al16(p->C) && al16(p->R) && al16(p->gamma), "kf_gemm_bs: RES needs 16-byte aligned C, R and gamma");
@@ -510,6 +518,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
   g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = p->N / BN; g.k_tiles = (int)(kbytes / BKB);
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
+  g.row_group = p->out_row_group; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
   g.err = dev_error_ptr();
   KF_REQUIRE(g.err != nullptr, "kf_gemm_bs: device error word unavailable");
   int sms = 0;

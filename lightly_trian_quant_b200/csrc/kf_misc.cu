@@ -1,0 +1,254 @@
+// Memory-bound kernels around the transformer blocks of the DINOv3 + EoMT path: patch gathering for the patch-embed
+// GEMM, the ScaleBlock tail (bias + GELU + pixel shuffle + depthwise 3x3 + LayerNorm2D), the per-pixel semantic
+// scores / argmax, and frame resize + normalisation.
+#include "kf_common.cuh"
+
+namespace kf {
+
+// ------------------------------------------------------------------------------------------------ patch gathering
+// x [B, 3, S, S] bf16 -> rows [B*g*g, 768] bf16 with k = c*256 + py*16 + px: the K-major A operand of the patch-embed
+// GEMM against the Conv2d weight [d, 3, 16, 16] viewed as [d, 768].  One thread moves 16 pixels (32 bytes) of one
+// patch row.
+__global__ void __launch_bounds__(256) im2col16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int B, int S) {
+  const int g = S >> 4;
+  const int64_t total = (int64_t)B * g * g * 48;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int seg = (int)(i % 48);
+  const int64_t patch = i / 48;
+  const int c = seg >> 4, py = seg & 15;
+  const int gx = (int)(patch % g), gy = (int)((patch / g) % g), b = (int)(patch / ((int64_t)g * g));
+  const uint4* src = reinterpret_cast<const uint4*>(x + (((int64_t)b * 3 + c) * S + gy * 16 + py) * S + gx * 16);
+  uint4* dst = reinterpret_cast<uint4*>(out + patch * 768 + seg * 16);
+  uint4 a = __ldg(src), d = __ldg(src + 1);
+  dst[0] = a;
+  dst[1] = d;
+}
+
+// ------------------------------------------------------------------------------------------------ ScaleBlock tail
+// g [B*Hs*Ws, 4C] bf16 is the ConvTranspose2d(k=2, s=2) GEMM output with column (dy*2+dx)*C + c.  For each output
+// pixel (Y, X) = (2y+dy, 2x+dx):  a = bf16(gelu(g + bias[c]));  o = bf16(sum over the 3x3 taps of a * dww[tap][c])
+// with zero padding, fp32 accumulation in tap order;  out = bf16(LayerNorm over c of o) in NHWC.
+// One CTA = 4 x 8 output pixels; the activations of the 6 x 10 halo are staged through shared memory 256 channels at
+// a time, the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics.
+constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 256;
+
+__global__ void __launch_bounds__(256, 2)
+dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias, const float* __restrict__ dww, const float* __restrict__ lnw,
+             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps) {
+  extern __shared__ __align__(16) uint8_t dsm[];
+  __nv_bfloat162* act = reinterpret_cast<__nv_bfloat162*>(dsm);                               // [60][128] channel pairs
+  __nv_bfloat162* res = reinterpret_cast<__nv_bfloat162*>(dsm + DW_HW * DW_CH * 2);           // [32][C/2]
+  const int t = threadIdx.x;
+  const int Ho = 2 * Hs, Wo = 2 * Ws;
+  const int X0 = blockIdx.x * DW_TW, Y0 = blockIdx.y * DW_TH, b = blockIdx.z;
+  const int cp = t & 127, half = t >> 7;
+  const int C2 = C >> 1;
+
+  for (int ch = 0; ch < C; ch += DW_CH) {
+    const int c0 = ch + cp * 2;
+    const float b0 = __ldg(bias + c0), b1 = __ldg(bias + c0 + 1);
+#pragma unroll 2
+    for (int px = half; px < DW_HW; px += 2) {
+      const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
+      const int Y = Y0 + hy - 1, X = X0 + hx - 1;
+      __nv_bfloat162 v = __floats2bfloat162_rn(0.f, 0.f);
+      if (Y >= 0 && Y < Ho && X >= 0 && X < Wo) {
+        const int64_t row = ((int64_t)b * Hs + (Y >> 1)) * Ws + (X >> 1);
+        const __nv_bfloat162 raw = *reinterpret_cast<const __nv_bfloat162*>(g + row * 4 * C + ((Y & 1) * 2 + (X & 1)) * C + c0);
+        const float2 f = __bfloat1622float2(raw);
+        v = __floats2bfloat162_rn(gelu_erf(f.x + b0), gelu_erf(f.y + b1));
+      }
+      act[px * 128 + cp] = v;
+    }
+    float w0[9], w1[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) {
+      w0[k] = __ldg(dww + k * C + c0);
+      w1[k] = __ldg(dww + k * C + c0 + 1);
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int px = half; px < DW_TH * DW_TW; px += 2) {
+      const int oy = px / DW_TW, ox = px - oy * DW_TW;
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+          const float2 f = __bfloat1622float2(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 128 + cp]);
+          a0 = fmaf(f.x, w0[ky * 3 + kx], a0);
+          a1 = fmaf(f.y, w1[ky * 3 + kx], a1);
+        }
+      res[px * C2 + (ch >> 1) + cp] = __floats2bfloat162_rn(a0, a1);
+    }
+    __syncthreads();
+  }
+
+  // LayerNorm over the channels of each pixel: 8 warps x 4 pixels
+  const int warp = t >> 5, lane = t & 31;
+  const float invC = 1.0f / (float)C;
+  for (int px = warp; px < DW_TH * DW_TW; px += 8) {
+    const int oy = px / DW_TW, ox = px - oy * DW_TW;
+    const int Y = Y0 + oy, X = X0 + ox;
+    const __nv_bfloat162* r = res + px * C2;
+    float s = 0.f;
+    for (int i = lane; i < C2; i += 32) {
+      const float2 f = __bfloat1622float2(r[i]);
+      s += f.x + f.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s * invC;
+    float ss = 0.f;
+    for (int i = lane; i < C2; i += 32) {
+      const float2 f = __bfloat1622float2(r[i]);
+      ss = fmaf(f.x - mean, f.x - mean, ss);
+      ss = fmaf(f.y - mean, f.y - mean, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss * invC + eps);
+    if (Y < Ho && X < Wo) {
+      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (((int64_t)b * Ho + Y) * Wo + X) * C);
+      for (int i = lane; i < C2; i += 32) {
+        const float2 f = __bfloat1622float2(r[i]);
+        const float2 w = __ldg(reinterpret_cast<const float2*>(lnw) + i), bb = __ldg(reinterpret_cast<const float2*>(lnb) + i);
+        dst[i] = __floats2bfloat162_rn((f.x - mean) * rstd * w.x + bb.x, (f.y - mean) * rstd * w.y + bb.y);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ semantic scores
+// scores[b, c, p] = sum_q sigmoid(mask_logits[b, q, p]) * softmax(class_logits[b, q, :])[c]   (all ncls+1 classes kept),
+// labels[b, p] = argmax over the ncls real classes.  One thread per pixel; the class probabilities sit in shared memory.
+__global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __restrict__ ml, const __nv_bfloat16* __restrict__ cl, int Q, int ncls1,
+                                                       int HW, float* __restrict__ scores, uint8_t* __restrict__ labels) {
+  extern __shared__ float prob[];                     // [Q][ncls1]
+  const int b = blockIdx.y;
+  for (int q = threadIdx.x; q < Q; q += blockDim.x) {
+    float v[8], mx = -INFINITY, s = 0.f;
+    for (int c = 0; c < ncls1; ++c) {
+      v[c] = __bfloat162float(cl[((int64_t)b * Q + q) * ncls1 + c]);
+      mx = fmaxf(mx, v[c]);
+    }
+    for (int c = 0; c < ncls1; ++c) {
+      v[c] = expf(v[c] - mx);
+      s += v[c];
+    }
+    for (int c = 0; c < ncls1; ++c) prob[q * ncls1 + c] = v[c] / s;
+  }
+  __syncthreads();
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= HW) return;
+  float acc[8];
+  for (int c = 0; c < ncls1; ++c) acc[c] = 0.f;
+  const __nv_bfloat16* m = ml + (int64_t)b * Q * HW + p;
+  for (int q = 0; q < Q; ++q) {
+    const float x = __bfloat162float(m[(int64_t)q * HW]);
+    const float sg = 1.0f / (1.0f + expf(-x));
+    for (int c = 0; c < ncls1; ++c) acc[c] = fmaf(sg, prob[q * ncls1 + c], acc[c]);
+  }
+  int best = 0;
+  for (int c = 0; c < ncls1; ++c) {
+    if (scores) scores[((int64_t)b * ncls1 + c) * HW + p] = acc[c];
+    if (c < ncls1 - 1 && acc[c] > acc[best]) best = c;
+  }
+  if (labels) labels[(int64_t)b * HW + p] = (uint8_t)best;
+}
+
+// ------------------------------------------------------------------------------------------------ resize + normalise
+// frames uint8 [B, Hi, Wi, 3] (HWC) -> bf16 [B, 3, So, So]: separable triangle filter with support scaled by the
+// down-sampling factor (bilinear with antialiasing, align_corners = false), then (v/255 - mean[c]) / std[c].
+__global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restrict__ src, __nv_bfloat16* __restrict__ dst, int Hi, int Wi, int So,
+                                                          float m0, float m1, float m2, float s0, float s1, float s2) {
+  const int ox = blockIdx.x * blockDim.x + threadIdx.x, oy = blockIdx.y, b = blockIdx.z;
+  if (ox >= So) return;
+  const float sy = (float)Hi / So, sx = (float)Wi / So;
+  const float supy = fmaxf(sy, 1.f), supx = fmaxf(sx, 1.f);
+  const float cy = (oy + 0.5f) * sy, cx = (ox + 0.5f) * sx;
+  const int y0 = max((int)(cy - supy + 0.5f), 0), y1 = min((int)(cy + supy + 0.5f), Hi);
+  const int x0 = max((int)(cx - supx + 0.5f), 0), x1 = min((int)(cx + supx + 0.5f), Wi);
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, wsum = 0.f;
+  float wxs = 0.f;
+  for (int x = x0; x < x1; ++x) wxs += fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) / supx));
+  for (int y = y0; y < y1; ++y) {
+    const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) / supy));
+    const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi) * 3;
+    float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+    for (int x = x0; x < x1; ++x) {
+      const float wx = fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) / supx));
+      r0 = fmaf(wx, (float)row[x * 3], r0);
+      r1 = fmaf(wx, (float)row[x * 3 + 1], r1);
+      r2 = fmaf(wx, (float)row[x * 3 + 2], r2);
+    }
+    acc0 = fmaf(wy, r0, acc0);
+    acc1 = fmaf(wy, r1, acc1);
+    acc2 = fmaf(wy, r2, acc2);
+    wsum += wy;
+  }
+  const float inv = 1.0f / (wsum * wxs * 255.f);
+  const int64_t plane = (int64_t)So * So;
+  __nv_bfloat16* o = dst + (int64_t)b * 3 * plane + (int64_t)oy * So + ox;
+  o[0] = __float2bfloat16_rn((acc0 * inv - m0) / s0);
+  o[plane] = __float2bfloat16_rn((acc1 * inv - m1) / s1);
+  o[2 * plane] = __float2bfloat16_rn((acc2 * inv - m2) / s2);
+}
+
+static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int kf_im2col_patch16(const void* x, void* out, int B, int S, void* stream) {
+  KF_REQUIRE(B >= 0 && S > 0 && S % 16 == 0, "kf_im2col_patch16: image side %d must be a positive multiple of 16", S);
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(x && out && al16(x) && al16(out), "kf_im2col_patch16: tensors must be non-null and 16-byte aligned");
+  const int64_t total = (int64_t)B * (S / 16) * (S / 16) * 48;
+  im2col16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                                                static_cast<__nv_bfloat16*>(out), B, S);
+  return cuda_status(cudaGetLastError(), "kf_im2col_patch16 launch");
+}
+
+extern "C" int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B, int Hs, int Ws, int C,
+                        float eps, void* stream) {
+  KF_REQUIRE(B >= 0 && Hs > 0 && Ws > 0, "kf_dw_ln: bad shape B=%d Hs=%d Ws=%d", B, Hs, Ws);
+  KF_REQUIRE(C > 0 && C % 256 == 0 && C <= 1024, "kf_dw_ln: C=%d must be a multiple of 256 up to 1024", C);
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(g && bias && dww && lnw && lnb && out && al16(g) && al16(out) && al16(lnw) && al16(lnb), "kf_dw_ln: tensors must be non-null and 16-byte aligned");
+  const size_t smem = (size_t)DW_HW * DW_CH * 2 + (size_t)DW_TH * DW_TW * C * 2;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(dw_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)DW_HW * DW_CH * 2 + DW_TH * DW_TW * 1024 * 2));
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dw_ln_kernel)");
+    if (dev < 64) attr_set[dev] = true;
+  }
+  dim3 grid((2 * Ws + DW_TW - 1) / DW_TW, (2 * Hs + DW_TH - 1) / DW_TH, B);
+  dw_ln_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(g), bias, dww, lnw, lnb,
+                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps);
+  return cuda_status(cudaGetLastError(), "kf_dw_ln launch");
+}
+
+extern "C" int kf_semantic(const void* mask_logits, const void* class_logits, int B, int Q, int ncls, int HW, float* scores, uint8_t* labels, void* stream) {
+  KF_REQUIRE(B >= 0 && Q > 0 && HW > 0 && ncls >= 1 && ncls <= 7, "kf_semantic: bad shape B=%d Q=%d ncls=%d HW=%d", B, Q, ncls, HW);
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(mask_logits && class_logits && (scores || labels), "kf_semantic: null tensor pointer");
+  dim3 grid((HW + 255) / 256, B);
+  semantic_kernel<<<grid, 256, (size_t)Q * (ncls + 1) * 4, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(mask_logits), static_cast<const __nv_bfloat16*>(class_logits), Q, ncls + 1, HW, scores, labels);
+  return cuda_status(cudaGetLastError(), "kf_semantic launch");
+}
+
+extern "C" int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, int Wi, int So, const float* mean3, const float* std3, void* stream) {
+  KF_REQUIRE(B >= 0 && Hi > 0 && Wi > 0 && So > 0, "kf_resize_norm: bad shape");
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(frames && out && mean3 && std3, "kf_resize_norm: null pointer (mean3 / std3 are host arrays of 3 floats)");
+  dim3 grid((So + 255) / 256, So, B);
+  resize_norm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(frames, static_cast<__nv_bfloat16*>(out), Hi, Wi, So, mean3[0], mean3[1], mean3[2],
+                                                                          std3[0], std3[1], std3[2]);
+  return cuda_status(cudaGetLastError(), "kf_resize_norm launch");
+}

@@ -259,6 +259,34 @@ __global__ void __launch_bounds__(128) ln_rows_kernel(const float* __restrict__ 
   }
 }
 
+// Final LayerNorm of the token stream [B, Ntok, D] with the row gather of the EoMT head: the first Q rows of every
+// image (queries) go to qb [B*Q, D], rows >= Q + npre (patch tokens) go to xb [B*(Ntok-Q-npre), D], the cls / register
+// rows in between are skipped.
+template <int NV>
+__global__ void __launch_bounds__(128) ln_tail_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                                      int M, int Ntok, int Q, int npre, __nv_bfloat16* __restrict__ qb, __nv_bfloat16* __restrict__ xb) {
+  constexpr int D = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const int img = row / Ntok, t = row - img * Ntok;
+  if (t >= Q && t < Q + npre) return;
+  float v[NV][8];
+  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, true, v);
+  const int P = Ntok - Q - npre;
+  __nv_bfloat16* y = t < Q ? qb + ((int64_t)img * Q + t) * D : xb + ((int64_t)img * P + (t - Q - npre)) * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[i][2 * j], v[i][2 * j + 1]);
+      o[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(y + i * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host launchers
 template <typename T>
 static int launch_quant_rows(int fmt, const void* x, int64_t ldx, int M, int K, const float* ts, const float* bias, int flags, void* q, void* sf,
@@ -292,6 +320,12 @@ static int launch_ln_rows(const float* x, const float* w, const float* b, float 
   if (out_dtype == KF_BF16) ln_rows_kernel<NV, __nv_bfloat16><<<grid, 128, 0, st>>>(x, w, b, eps, M, static_cast<__nv_bfloat16*>(y));
   else ln_rows_kernel<NV, __half><<<grid, 128, 0, st>>>(x, w, b, eps, M, static_cast<__half*>(y));
   return cuda_status(cudaGetLastError(), "kf_ln_rows launch");
+}
+
+template <int NV>
+static int launch_ln_tail(const float* x, const float* w, const float* b, float eps, int M, int Ntok, int Q, int npre, void* qb, void* xb, cudaStream_t st) {
+  ln_tail_kernel<NV><<<(unsigned)((M + 3) / 4), 128, 0, st>>>(x, w, b, eps, M, Ntok, Q, npre, static_cast<__nv_bfloat16*>(qb), static_cast<__nv_bfloat16*>(xb));
+  return cuda_status(cudaGetLastError(), "kf_ln_tail launch");
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -354,5 +388,26 @@ extern "C" int kf_ln_rows(const float* x, const float* w, const float* b, float 
     case 6: return launch_ln_rows<6>(x, w, b, eps, M, out_dtype, y, st);
     case 7: return launch_ln_rows<7>(x, w, b, eps, M, out_dtype, y, st);
     default: return launch_ln_rows<8>(x, w, b, eps, M, out_dtype, y, st);
+  }
+}
+
+extern "C" int kf_ln_tail(const float* x, const float* w, const float* b, float eps, int B, int Ntok, int Q, int npre, int d, void* qb, void* xb,
+                          void* stream) {
+  KF_REQUIRE(B >= 0 && Ntok > 0 && Q >= 0 && npre >= 0 && Q + npre <= Ntok, "kf_ln_tail: bad token counts Ntok=%d Q=%d npre=%d", Ntok, Q, npre);
+  KF_REQUIRE(d > 0 && d % 256 == 0 && d <= 2048, "kf_ln_tail: d=%d must be a multiple of 256 up to 2048", d);
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(x && w && b && xb && (qb || Q == 0), "kf_ln_tail: null tensor pointer");
+  KF_REQUIRE(aligned16(x) && aligned16(w) && aligned16(b) && aligned16(qb) && aligned16(xb), "kf_ln_tail: tensors must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = B * Ntok;
+  switch (d / 256) {
+    case 1: return launch_ln_tail<1>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 2: return launch_ln_tail<2>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 3: return launch_ln_tail<3>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 4: return launch_ln_tail<4>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 5: return launch_ln_tail<5>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 6: return launch_ln_tail<6>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 7: return launch_ln_tail<7>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    default: return launch_ln_tail<8>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
   }
 }

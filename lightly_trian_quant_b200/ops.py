@@ -276,3 +276,89 @@ def attn_fwd(qkv: torch.Tensor, pre: float = 1.0, out: Optional[torch.Tensor] = 
 
 
 attn16_fwd = attn_fwd
+
+
+# ------------------------------------------------------------------------------------------------ patch embed / head / pre / post
+def gemm_tokens(a: torch.Tensor, W: QWeight, bias, out: torch.Tensor, rows_per_image: int, tokens_per_image: int, row_offset: int,
+                round_bf16: bool = False) -> torch.Tensor:
+    """patch-embed GEMM: a bf16 [B*P, K] @ W^T + bias written as fp32 rows row_offset.. of every image of the token
+    stream out [B, tokens_per_image, N] (counterpart: PatchEmbedGemm, infer-opt/round11_attn_tier0/impl/patch_embed.py:34-53)."""
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KfError("gemm_tokens: out must be contiguous fp32")
+    p = GemmParams()
+    p.fmt, p.epi, p.M, p.N, p.K = KF_FMT["bf16"], KF_EPI["plain"], a.shape[0], W.N, W.K
+    p.A, p.W, p.bias, p.C = a.data_ptr(), W.q.data_ptr(), _ptr(bias), out.data_ptr()
+    p.out_dtype = KF_DT["f32"]
+    p.flags = _lib.KF_G_ROUND_BF16 if round_bf16 else 0
+    p.out_row_group, p.out_row_stride, p.out_row_offset = rows_per_image, tokens_per_image, row_offset
+    check(_lib.lib().kf_gemm_bs(p, _stream()), "kf_gemm_bs")
+    return out
+
+
+def im2col_patch16(x: torch.Tensor) -> torch.Tensor:
+    """x bf16 [B, 3, S, S] -> bf16 [B*(S/16)^2, 768]."""
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16 or x.dim() != 4 or x.shape[1] != 3 or x.shape[2] != x.shape[3] or not x.is_contiguous():
+        raise KfError("im2col_patch16: x must be contiguous bf16 [B, 3, S, S]")
+    B, _, S, _ = x.shape
+    out = torch.empty(B * (S // 16) ** 2, 768, dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().kf_im2col_patch16(x.data_ptr(), out.data_ptr(), B, S, _stream()), "kf_im2col_patch16")
+    return out
+
+
+def ln_tail(x: torch.Tensor, w, b, eps: float, Q: int, npre: int):
+    """final LayerNorm + gather: x fp32 [B, Ntok, d] -> (queries bf16 [B*Q, d], patches bf16 [B*(Ntok-Q-npre), d])."""
+    _need_cuda(x, w, b)
+    B, Ntok, d = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KfError("ln_tail: x must be contiguous fp32")
+    qb = torch.empty(B * Q, d, dtype=torch.bfloat16, device=x.device)
+    xb = torch.empty(B * (Ntok - Q - npre), d, dtype=torch.bfloat16, device=x.device)
+    check(_lib.lib().kf_ln_tail(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), B, Ntok, Q, npre, d, qb.data_ptr(), xb.data_ptr(), _stream()),
+          "kf_ln_tail")
+    return qb, xb
+
+
+def dw_ln(g: torch.Tensor, bias, dww, lnw, lnb, B: int, Hs: int, Ws: int, eps: float) -> torch.Tensor:
+    """ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] -> bf16 [B, 2Hs, 2Ws, C] (dw_ln_launch, head11.py:60-67)."""
+    _need_cuda(g, bias, dww, lnw, lnb)
+    C = g.shape[1] // 4
+    if g.dtype != torch.bfloat16 or not g.is_contiguous() or g.shape[0] != B * Hs * Ws or dww.shape != (9, C):
+        raise KfError("dw_ln: g must be contiguous bf16 [B*Hs*Ws, 4C] and dww fp32 [9, C]")
+    out = torch.empty(B, 2 * Hs, 2 * Ws, C, dtype=torch.bfloat16, device=g.device)
+    check(_lib.lib().kf_dw_ln(g.data_ptr(), bias.data_ptr(), dww.data_ptr(), lnw.data_ptr(), lnb.data_ptr(), out.data_ptr(), B, Hs, Ws, C,
+                              float(eps), _stream()), "kf_dw_ln")
+    return out
+
+
+def semantic(mask_logits: torch.Tensor, class_logits: torch.Tensor, want_scores: bool = False):
+    """mask_logits bf16 [B, Q, h, w], class_logits bf16 [B, Q, ncls+1] -> (labels uint8 [B, h, w], scores fp32 [B, ncls+1, h, w] | None)."""
+    _need_cuda(mask_logits, class_logits)
+    B, Q, h, w = mask_logits.shape
+    ncls1 = class_logits.shape[-1]
+    if mask_logits.dtype != torch.bfloat16 or class_logits.dtype != torch.bfloat16 or not mask_logits.is_contiguous() or not class_logits.is_contiguous():
+        raise KfError("semantic: logits must be contiguous bf16")
+    labels = torch.empty(B, h, w, dtype=torch.uint8, device=mask_logits.device)
+    scores = torch.empty(B, ncls1, h, w, dtype=torch.float32, device=mask_logits.device) if want_scores else None
+    check(_lib.lib().kf_semantic(mask_logits.data_ptr(), class_logits.data_ptr(), B, Q, ncls1 - 1, h * w, _ptr(scores), labels.data_ptr(), _stream()),
+          "kf_semantic")
+    return labels, scores
+
+
+IMAGENET_MEAN = (0.485, 0.456, 0.406)
+IMAGENET_STD = (0.229, 0.224, 0.225)
+
+
+def resize_norm(frames: torch.Tensor, size: int, mean=IMAGENET_MEAN, std=IMAGENET_STD, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """frames uint8 [B, Hi, Wi, 3] -> bf16 [B, 3, size, size] (antialiased bilinear + normalisation)."""
+    import ctypes as C
+
+    _need_cuda(frames)
+    if frames.dtype != torch.uint8 or frames.dim() != 4 or frames.shape[3] != 3 or not frames.is_contiguous():
+        raise KfError("resize_norm: frames must be contiguous uint8 [B, H, W, 3]")
+    B, Hi, Wi, _ = frames.shape
+    if out is None:
+        out = torch.empty(B, 3, size, size, dtype=torch.bfloat16, device=frames.device)
+    m, s = (C.c_float * 3)(*mean), (C.c_float * 3)(*std)
+    check(_lib.lib().kf_resize_norm(frames.data_ptr(), out.data_ptr(), B, Hi, Wi, size, m, s, _stream()), "kf_resize_norm")
+    return out

@@ -1,0 +1,155 @@
+"""GPU parity of the pieces around the blocks and of the whole model_fn against the CPU oracles.
+
+End-to-end gate: cosine of the mask logits >= 0.9999 against the emulated model at the same format (stress init, static
+NVFP4 scales read back from the GPU model and passed to the oracle)."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import gemm_oracle as go
+from oracle import model_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+
+
+def _mods():
+    from lightly_trian_quant_b200 import modeldef, ops, stack
+
+    return modeldef, ops, stack
+
+
+TINY = dict(dim=256, depth=4, heads=4, ffn=1024, num_queries=32, num_joint_blocks=2)
+
+
+def test_patch_embed_matches_conv():
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.EoMTConfig(**TINY)
+    model = modeldef.build_model(cfg, 0, "stress", "cuda")
+    x = torch.rand(2, 3, 96, 96, generator=torch.Generator().manual_seed(0)).to(BF)
+    pe = stack.PatchEmbed(model.backbone, round_bf16=False)
+    t = pe(x.cuda())
+    ops.check_device_error()
+    bb = model.backbone.cpu()
+    ref = F.conv2d(x.float(), bb.patch_embed.proj.weight.to(BF).float(), bb.patch_embed.proj.bias.to(BF).float(), stride=16)
+    ref = ref.permute(0, 2, 3, 1).reshape(2, 36, cfg.dim)
+    assert t.shape == (2, 41, cfg.dim)
+    assert go.rel_fro(t[:, 5:].cpu().numpy(), ref.numpy()) < 2e-5
+    assert torch.equal(t[:, :1].cpu(), bb.cls_token.expand(2, -1, -1)) and torch.equal(t[:, 1:5].cpu(), bb.storage_tokens.expand(2, -1, -1))
+
+
+def test_ln_tail_gather():
+    modeldef, ops, stack = _mods()
+    g = torch.Generator().manual_seed(1)
+    B, Ntok, Q, npre, d = 3, 50, 7, 5, 512
+    x = torch.randn(B, Ntok, d, generator=g) * 3
+    w, b = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.1
+    qb, xb = ops.ln_tail(x.cuda(), w.cuda(), b.cuda(), 1e-5, Q, npre)
+    ref = F.layer_norm(x, (d,), w, b, 1e-5)
+    assert (qb.float().cpu() - ref[:, :Q].reshape(-1, d).to(BF).float()).abs().max() < 0.05
+    assert go.rel_fro(qb.float().cpu().numpy(), ref[:, :Q].reshape(-1, d).numpy()) < 4e-3
+    assert go.rel_fro(xb.float().cpu().numpy(), ref[:, Q + npre:].reshape(-1, d).numpy()) < 4e-3
+
+
+@pytest.mark.parametrize("C", [256, 1024])
+def test_dw_ln_scale_block_tail(C):
+    modeldef, ops, stack = _mods()
+    g = torch.Generator().manual_seed(2)
+    B, Hs, Ws = 2, 6, 8
+    gm = (torch.randn(B * Hs * Ws, 4 * C, generator=g) * 1.5).to(BF)
+    bias = (torch.randn(C, generator=g) * 0.1).to(BF).float()
+    dww = (torch.randn(C, 9, generator=g) * 0.3).to(BF).float()
+    lw, lb = torch.rand(C, generator=g) + 0.5, torch.randn(C, generator=g) * 0.1
+    out = ops.dw_ln(gm.cuda(), bias.cuda(), dww.t().contiguous().cuda(), lw.cuda(), lb.cuda(), B, Hs, Ws, 1e-6)
+    assert out.shape == (B, 2 * Hs, 2 * Ws, C)
+    a = gm.float().reshape(B, Hs, Ws, 2, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(B, 2 * Hs, 2 * Ws, C)
+    a = F.gelu(a + bias).to(BF).float()
+    o = F.conv2d(a.permute(0, 3, 1, 2), dww.reshape(C, 1, 3, 3), padding=1, groups=C).to(BF).float().permute(0, 2, 3, 1)
+    ref = F.layer_norm(o, (C,), lw, lb, 1e-6)
+    assert go.rel_fro(out.float().cpu().numpy(), ref.numpy()) < 6e-3
+
+
+def test_semantic_scores_and_labels():
+    modeldef, ops, stack = _mods()
+    g = torch.Generator().manual_seed(3)
+    B, Q, h, w = 2, 50, 20, 24
+    ml = (torch.randn(B, Q, h, w, generator=g) * 3).to(BF)
+    cl = (torch.randn(B, Q, 3, generator=g) * 2).to(BF)
+    labels, scores = ops.semantic(ml.cuda(), cl.cuda(), want_scores=True)
+    ref = torch.einsum("bqhw,bqc->bchw", ml.float().sigmoid(), cl.float().softmax(-1))
+    assert go.rel_fro(scores.cpu().numpy(), ref.numpy()) < 1e-5
+    exp = ref[:, :2].argmax(1)
+    margin = (ref[:, 0] - ref[:, 1]).abs() > 1e-4
+    assert torch.equal(labels.cpu().long()[margin], exp[margin])
+
+
+def test_resize_norm_matches_antialiased_bilinear():
+    modeldef, ops, stack = _mods()
+    g = torch.Generator().manual_seed(4)
+    fr = torch.randint(0, 256, (2, 144, 190, 3), generator=g, dtype=torch.uint8)
+    out = ops.resize_norm(fr.cuda(), 64)
+    x = fr.permute(0, 3, 1, 2).float() / 255.0
+    ref = F.interpolate(x, size=(64, 64), mode="bilinear", antialias=True, align_corners=False)
+    mean = torch.tensor(ops.IMAGENET_MEAN).view(1, 3, 1, 1)
+    std = torch.tensor(ops.IMAGENET_STD).view(1, 3, 1, 1)
+    ref = (ref - mean) / std
+    assert (out.float().cpu() - ref).abs().max() < 0.03       # bf16 output rounding at |v| <= 2.7
+
+
+def _collect_ts(model_fn):
+    layers, _, head = model_fn._keepalive[0], model_fn._keepalive[1], model_fn._keepalive[2]
+    ts = {}
+    for i, L in enumerate(layers):
+        for site in ("ln1", "o", "ln2", "g"):
+            t = getattr(L, "ts_" + site)
+            if t is not None:
+                ts[(i, site)] = t.cpu().numpy()
+    for j, st in enumerate(head.stages):
+        if st["ts"] is not None:
+            ts[("head", j)] = st["ts"].cpu().numpy()
+    return ts
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "mx8", "nv4", "mx4"])
+@pytest.mark.parametrize("init", ["stress", "upstream"])
+def test_tiny_model_end_to_end(fmt, init):
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.EoMTConfig(**TINY)
+    model = modeldef.build_model(cfg, 0, init, "cpu")
+    x = torch.rand(2, 3, 64, 64, generator=torch.Generator().manual_seed(5)).to(BF)
+    gmodel = modeldef.build_model(cfg, 0, init, "cuda")
+    fn, _ = stack.make_variant("tiny", gmodel, f"b200_{fmt}+s64")
+    ml, cl = fn(x.cuda())
+    ml2, cl2 = fn(x.cuda())                       # second call: static scales, must be bitwise identical
+    ops.check_device_error()
+    assert torch.equal(ml, ml2) and torch.equal(cl, cl2)
+    assert ml.shape == (2, 32, 16, 16) and cl.shape == (2, 32, 3) and torch.isfinite(ml.float()).all()
+    emu = mo.EmuModel(model, fmt, ts=_collect_ts(fn))
+    ml_ref, cl_ref = emu(x.float())
+    c_ml, c_cl = mo.cosine(ml.float().cpu(), ml_ref), mo.cosine(cl.float().cpu(), cl_ref)
+    assert c_ml >= 0.9999, (c_ml, c_cl)
+    assert c_cl >= 0.9999, (c_ml, c_cl)
+
+
+def test_cuda_graph_replay_is_bitwise_eager():
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.EoMTConfig(**TINY)
+    gmodel = modeldef.build_model(cfg, 0, "stress", "cuda")
+    fn, _ = stack.make_variant("tiny", gmodel, "b200_nv4+s64")
+    x = torch.rand(2, 3, 64, 64, generator=torch.Generator().manual_seed(6)).to(BF).cuda()
+    eager = fn(x)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn(x)
+    torch.cuda.current_stream().wait_stream(s)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        out = fn(x)
+    gr.replay()
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    assert torch.equal(out[0], eager[0]) and torch.equal(out[1], eager[1])
