@@ -165,6 +165,12 @@ KF_API int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, int W
  * Replaces attn16_fwd / a16::fwd_kernel (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404). */
 KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream);
 
+/* Tensor-core instruction-rate probe: every SM issues `iters` x 4 tcgen05.mma (M=128, N=n, 32 K-bytes each) of the
+ * given operand format on shared-memory-resident operands; *flops_per_launch receives the FLOPs one launch performs.
+ * The caller times the launch to obtain the FP8 / FP4 / bf16 instruction-rate ceiling of the part.
+ * Counterpart: the mma.sync probe infer-opt/round10_lowp_probe/peak_extra.cu. */
+KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, double* flops_per_launch, void* stream);
+
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
  * No counterpart in the reference (its mbarrier waits spin without a bound: infer-opt/round12_lowp_stack/impl/attn16o.cu:77-79). */

@@ -1,0 +1,97 @@
+// Instruction-rate probe of the sm_100a tensor core: every SM issues tcgen05.mma back to back on operands that stay
+// in shared memory (zero-filled, no TMA traffic) and accumulators that stay in TMEM.  The host times the launch; the
+// resulting FLOP rate is the ceiling a GEMM main loop of the same instruction shape can reach on this part at the
+// clocks it actually runs at, which is the denominator used for the FP8 / FP4 roofline fractions.
+// Same idea as the reference's register-resident mma.sync probe (infer-opt/round10_lowp_probe/peak_extra.cu).
+#include "kf_sm100.cuh"
+
+namespace kf {
+
+constexpr int PK_SMEM = 1024 + 16384 + 32768 + 4096 + 64;
+
+template <int KIND, int N>
+__global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* err) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t *a = smem, *b = smem + 16384, *sf = smem + 16384 + 32768;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sf + 4096);
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bar + 1);
+  volatile uint32_t* abort_flag = holder + 1;
+  for (int i = threadIdx.x; i < (16384 + 32768 + 4096) / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  fence_proxy_async_smem();
+  if (threadIdx.x < 32) {
+    tmem_alloc(holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *holder;
+  const WaitCtx ctx{abort_flag, err};
+  if (threadIdx.x == 0) {
+    constexpr uint32_t IDESC = KIND == KF_FMT_BF16 ? idesc_f16(1, N) : KIND == KF_FMT_MX8 ? idesc_bs(0, 1, N) : KIND == KF_FMT_NV4 ? idesc_bs(1, 0, N) : idesc_bs(1, 1, N);
+    const uint64_t ad = smem_desc_sw128(smem_u32(a)), bd = smem_desc_sw128(smem_u32(b));
+    const uint32_t sft = tmem + 256 + (N > 128 ? 128 : 0);
+    if (KIND != KF_FMT_BF16) {
+      for (int i = 0; i < 8; ++i) tc_cp_sf(sft + 4 * i, smem_desc_sf(smem_u32(sf) + i * 512));
+    }
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t d = tmem + ((N <= 128) ? (it & 1) * N : 0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (KIND == KF_FMT_BF16) mma_f16(d, ad + 2 * j, bd + 2 * j, IDESC, 1);
+        else if (KIND == KF_FMT_MX8) mma_mxf8(d, ad + 2 * j, bd + 2 * j, idesc_with_sf_id(IDESC, j, j), 1, sft, sft + 16);
+        else if (KIND == KF_FMT_NV4) mma_nvf4(d, ad + 2 * j, bd + 2 * j, IDESC, 1, sft, sft + 16);
+        else mma_mxf4(d, ad + 2 * j, bd + 2 * j, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), 1, sft, sft + 16);
+      }
+    }
+    tc_commit(bar);
+    mbar_wait(bar, 0, ctx, 50);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int KIND>
+static int launch_peak(int n, int iters, int sms, unsigned int* err, cudaStream_t st) {
+  auto go = [&](auto kern) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(peak_kernel)");
+    kern<<<sms, 128, PK_SMEM, st>>>(iters, err);
+    return cuda_status(cudaGetLastError(), "kf_tensor_peak_probe launch");
+  };
+  return n == 256 ? go(peak_kernel<KIND, 256>) : go(peak_kernel<KIND, 128>);
+}
+
+}  // namespace kf
+
+using namespace kf;
+
+extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, double* flops_per_launch, void* stream) {
+  KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_tensor_peak_probe: unknown format %d", fmt);
+  KF_REQUIRE(n == 128 || n == 256, "kf_tensor_peak_probe: n must be 128 or 256");
+  KF_REQUIRE(iters > 0 && iters <= (1 << 22), "kf_tensor_peak_probe: iters out of range");
+  int sms = 0;
+  int st = device_sm_count(&sms);
+  if (st != KF_OK) return st;
+  unsigned int* err = dev_error_ptr();
+  KF_REQUIRE(err != nullptr, "kf_tensor_peak_probe: device error word unavailable");
+  const double k_per_mma = fmt == KF_FMT_MX8 ? 32.0 : (fmt == KF_FMT_BF16 ? 16.0 : 64.0);
+  if (flops_per_launch) *flops_per_launch = 2.0 * 128.0 * n * k_per_mma * 4.0 * iters * sms;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  switch (fmt) {
+    case KF_FMT_MX8: return launch_peak<KF_FMT_MX8>(n, iters, sms, err, cs);
+    case KF_FMT_NV4: return launch_peak<KF_FMT_NV4>(n, iters, sms, err, cs);
+    case KF_FMT_MX4: return launch_peak<KF_FMT_MX4>(n, iters, sms, err, cs);
+    default: return launch_peak<KF_FMT_BF16>(n, iters, sms, err, cs);
+  }
+}

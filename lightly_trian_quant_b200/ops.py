@@ -21,6 +21,29 @@ from . import _lib
 from ._lib import KF_DT, KF_EPI, KF_FMT, KF_G_GELU, KF_Q_GELU, KF_Q_RECIP_DIV, KF_Q_ROUND_BF16, GemmParams, KfError, check
 
 VEC = {"mx8": 32, "nv4": 16, "mx4": 32}
+
+# Launch accounting used by the benchmark: LAUNCHES counts every kernel launched through this module; when TIMING is
+# a dict every launch is bracketed by CUDA events on the launching stream under its kernel-class name and BYTES
+# accumulates the algorithmic bytes of the memory-bound classes.
+LAUNCHES = 0
+TIMING = None
+BYTES: dict = {}
+
+
+def _run(name: str, call, nbytes: int = 0) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
+    if TIMING is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        st = call()
+        e1.record()
+        TIMING.setdefault(name, []).append((e0, e1))
+        if nbytes:
+            BYTES[name] = BYTES.get(name, 0) + nbytes
+    else:
+        st = call()
+    check(st, name)
 _DT = {torch.float32: KF_DT["f32"], torch.bfloat16: KF_DT["bf16"], torch.float16: KF_DT["f16"]}
 
 
@@ -92,9 +115,9 @@ def quant_rows(x: torch.Tensor, out: ActBuf, *, bias: Optional[torch.Tensor] = N
         raise KfError(f"quant_rows: x must be [M={out.M}, K={out.K}] with a contiguous last dim, got {tuple(x.shape)}")
     if x.dtype not in _DT:
         raise KfError(f"quant_rows: unsupported dtype {x.dtype}")
-    st = _lib.lib().kf_quant_rows(KF_FMT[out.fmt], _DT[x.dtype], x.data_ptr(), x.stride(0), out.M, out.K, _ptr(out.ts),
-                                  _ptr(bias), _flags(gelu, round_bf16, recip_div), out.q.data_ptr(), out.sf.data_ptr(), _stream())
-    check(st, "kf_quant_rows")
+    _run("quant_rows", lambda: _lib.lib().kf_quant_rows(KF_FMT[out.fmt], _DT[x.dtype], x.data_ptr(), x.stride(0), out.M, out.K, _ptr(out.ts),
+                                                        _ptr(bias), _flags(gelu, round_bf16, recip_div), out.q.data_ptr(), out.sf.data_ptr(), _stream()),
+         x.numel() * x.element_size() + out.q.numel() + out.sf.numel())
     return out
 
 
@@ -114,9 +137,9 @@ def ln_quant(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out:
     M = x.numel() // d
     if x.dtype != torch.float32 or not x.is_contiguous() or (M, d) != (out.M, out.K):
         raise KfError(f"ln_quant: x must be contiguous fp32 [M={out.M}, d={out.K}], got {tuple(x.shape)} {x.dtype}")
-    st = _lib.lib().kf_ln_quant(KF_FMT[out.fmt], x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), M, d, _ptr(out.ts),
-                                _flags(False, round_bf16, recip_div), out.q.data_ptr(), out.sf.data_ptr(), _ptr(y_dbg), _stream())
-    check(st, "kf_ln_quant")
+    _run("ln_quant", lambda: _lib.lib().kf_ln_quant(KF_FMT[out.fmt], x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), M, d, _ptr(out.ts),
+                                                    _flags(False, round_bf16, recip_div), out.q.data_ptr(), out.sf.data_ptr(), _ptr(y_dbg), _stream()),
+         x.numel() * 4 + out.q.numel() + out.sf.numel())
     return out
 
 
@@ -136,8 +159,7 @@ def ln_rows(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, dtype
     if x.dtype != torch.float32 or not x.is_contiguous():
         raise KfError("ln_rows: x must be contiguous fp32")
     y = torch.empty(x.shape, dtype=dtype, device=x.device)
-    st = _lib.lib().kf_ln_rows(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), M, d, _DT[dtype], y.data_ptr(), _stream())
-    check(st, "kf_ln_rows")
+    _run("ln_rows", lambda: _lib.lib().kf_ln_rows(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), M, d, _DT[dtype], y.data_ptr(), _stream()))
     return y
 
 
@@ -182,7 +204,7 @@ MXW = QWeight
 
 
 def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
-          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0):
+          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block"):
     p = GemmParams()
     if isinstance(a, ActBuf):
         if a.fmt != W.fmt or a.K != W.K:
@@ -204,7 +226,7 @@ def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin
     p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
     if out is not None:
         p.out_fmt, p.Qo, p.SFo, p.tso = KF_FMT[out.fmt], out.q.data_ptr(), out.sf.data_ptr(), _ptr(out.ts)
-    check(_lib.lib().kf_gemm_bs(p, _stream()), "kf_gemm_bs")
+    _run(f"gemm_{tag}_{W.fmt}", lambda: _lib.lib().kf_gemm_bs(p, _stream()))
 
 
 def _f32c(t, n, what):
@@ -212,13 +234,14 @@ def _f32c(t, n, what):
         raise KfError(f"gemm: {what} must be contiguous fp32 with {n} elements")
 
 
-def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.bfloat16, out: Optional[torch.Tensor] = None,
+               tag: str = "block") -> torch.Tensor:
     """[M, N] = act(a @ W^T (* ts) + bias) in bf16 / f16 / f32 (mm, gemm_plain, fwd_bias, fwd_gelu, fwd_plain)."""
     M = a.M if isinstance(a, ActBuf) else a.shape[0]
     _f32c(bias, W.N, "bias")
     if out is None:
         out = torch.empty(M, W.N, dtype=out_dtype, device=W.q.device)
-    _gemm(a, W, "plain", bias=bias, C=out, out_dtype=out.dtype, gelu=gelu)
+    _gemm(a, W, "plain", bias=bias, C=out, out_dtype=out.dtype, gelu=gelu, tag=tag)
     return out
 
 
@@ -271,7 +294,7 @@ def attn_fwd(qkv: torch.Tensor, pre: float = 1.0, out: Optional[torch.Tensor] = 
     _, B, N, H, _ = qkv.shape
     if out is None:
         out = torch.empty(B, N, H * 64, dtype=qkv.dtype, device=qkv.device)
-    check(_lib.lib().kf_attn_fwd(_DT[qkv.dtype], qkv.data_ptr(), out.data_ptr(), B, N, H, float(pre), _stream()), "kf_attn_fwd")
+    _run("attn_fwd", lambda: _lib.lib().kf_attn_fwd(_DT[qkv.dtype], qkv.data_ptr(), out.data_ptr(), B, N, H, float(pre), _stream()))
     return out
 
 
@@ -291,7 +314,7 @@ def gemm_tokens(a: torch.Tensor, W: QWeight, bias, out: torch.Tensor, rows_per_i
     p.out_dtype = KF_DT["f32"]
     p.flags = _lib.KF_G_ROUND_BF16 if round_bf16 else 0
     p.out_row_group, p.out_row_stride, p.out_row_offset = rows_per_image, tokens_per_image, row_offset
-    check(_lib.lib().kf_gemm_bs(p, _stream()), "kf_gemm_bs")
+    _run("gemm_patch_bf16", lambda: _lib.lib().kf_gemm_bs(p, _stream()))
     return out
 
 
@@ -302,7 +325,7 @@ def im2col_patch16(x: torch.Tensor) -> torch.Tensor:
         raise KfError("im2col_patch16: x must be contiguous bf16 [B, 3, S, S]")
     B, _, S, _ = x.shape
     out = torch.empty(B * (S // 16) ** 2, 768, dtype=torch.bfloat16, device=x.device)
-    check(_lib.lib().kf_im2col_patch16(x.data_ptr(), out.data_ptr(), B, S, _stream()), "kf_im2col_patch16")
+    _run("im2col_patch16", lambda: _lib.lib().kf_im2col_patch16(x.data_ptr(), out.data_ptr(), B, S, _stream()))
     return out
 
 
@@ -314,8 +337,8 @@ def ln_tail(x: torch.Tensor, w, b, eps: float, Q: int, npre: int):
         raise KfError("ln_tail: x must be contiguous fp32")
     qb = torch.empty(B * Q, d, dtype=torch.bfloat16, device=x.device)
     xb = torch.empty(B * (Ntok - Q - npre), d, dtype=torch.bfloat16, device=x.device)
-    check(_lib.lib().kf_ln_tail(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), B, Ntok, Q, npre, d, qb.data_ptr(), xb.data_ptr(), _stream()),
-          "kf_ln_tail")
+    _run("ln_tail", lambda: _lib.lib().kf_ln_tail(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), B, Ntok, Q, npre, d, qb.data_ptr(), xb.data_ptr(),
+                                                  _stream()))
     return qb, xb
 
 
@@ -326,8 +349,8 @@ def dw_ln(g: torch.Tensor, bias, dww, lnw, lnb, B: int, Hs: int, Ws: int, eps: f
     if g.dtype != torch.bfloat16 or not g.is_contiguous() or g.shape[0] != B * Hs * Ws or dww.shape != (9, C):
         raise KfError("dw_ln: g must be contiguous bf16 [B*Hs*Ws, 4C] and dww fp32 [9, C]")
     out = torch.empty(B, 2 * Hs, 2 * Ws, C, dtype=torch.bfloat16, device=g.device)
-    check(_lib.lib().kf_dw_ln(g.data_ptr(), bias.data_ptr(), dww.data_ptr(), lnw.data_ptr(), lnb.data_ptr(), out.data_ptr(), B, Hs, Ws, C,
-                              float(eps), _stream()), "kf_dw_ln")
+    _run("dw_ln", lambda: _lib.lib().kf_dw_ln(g.data_ptr(), bias.data_ptr(), dww.data_ptr(), lnw.data_ptr(), lnb.data_ptr(), out.data_ptr(), B, Hs, Ws, C,
+                                              float(eps), _stream()))
     return out
 
 
@@ -340,8 +363,8 @@ def semantic(mask_logits: torch.Tensor, class_logits: torch.Tensor, want_scores:
         raise KfError("semantic: logits must be contiguous bf16")
     labels = torch.empty(B, h, w, dtype=torch.uint8, device=mask_logits.device)
     scores = torch.empty(B, ncls1, h, w, dtype=torch.float32, device=mask_logits.device) if want_scores else None
-    check(_lib.lib().kf_semantic(mask_logits.data_ptr(), class_logits.data_ptr(), B, Q, ncls1 - 1, h * w, _ptr(scores), labels.data_ptr(), _stream()),
-          "kf_semantic")
+    _run("semantic", lambda: _lib.lib().kf_semantic(mask_logits.data_ptr(), class_logits.data_ptr(), B, Q, ncls1 - 1, h * w, _ptr(scores),
+                                                    labels.data_ptr(), _stream()))
     return labels, scores
 
 
@@ -360,5 +383,22 @@ def resize_norm(frames: torch.Tensor, size: int, mean=IMAGENET_MEAN, std=IMAGENE
     if out is None:
         out = torch.empty(B, 3, size, size, dtype=torch.bfloat16, device=frames.device)
     m, s = (C.c_float * 3)(*mean), (C.c_float * 3)(*std)
-    check(_lib.lib().kf_resize_norm(frames.data_ptr(), out.data_ptr(), B, Hi, Wi, size, m, s, _stream()), "kf_resize_norm")
+    _run("resize_norm", lambda: _lib.lib().kf_resize_norm(frames.data_ptr(), out.data_ptr(), B, Hi, Wi, size, m, s, _stream()))
     return out
+
+
+def tensor_peak_tflops(fmt: str, n: int = 256, iters: int = 4096, reps: int = 5) -> float:
+    """measured tcgen05 instruction-rate ceiling (TFLOP/s) for operand format fmt at M=128, N=n (best of reps)."""
+    import ctypes as C
+
+    fl = C.c_double(0.0)
+    L = _lib.lib()
+    best = 0.0
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(L.kf_tensor_peak_probe(KF_FMT[fmt], n, iters, C.byref(fl), _stream()), "kf_tensor_peak_probe")
+        e1.record()
+        e1.synchronize()
+        best = max(best, fl.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best

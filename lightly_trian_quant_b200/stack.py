@@ -201,27 +201,27 @@ class Head:
         B, Ntok, C = t.shape
         Q, (Hs, Ws) = self.Q, grid
         qb, xb = ops.ln_tail(t, self.ln_w, self.ln_b, self.ln_eps, Q, self.npre)
-        cl = ops.gemm_plain(qb, self.Wcls, self.bcls)[:, : self.ncls1].reshape(B, Q, self.ncls1).contiguous()
+        cl = ops.gemm_plain(qb, self.Wcls, self.bcls, tag="head")[:, : self.ncls1].reshape(B, Q, self.ncls1).contiguous()
         z = xb
         for st in self.stages:
             if self.fmt == "bf16":
-                g = ops.gemm_plain(z, st["W"])
+                g = ops.gemm_plain(z, st["W"], tag="head")
             else:
                 if self.calib.on and self.fmt == "nv4":
                     set_ts(st["ts"], z)
                 a = _with_ts(ops.act_buf(z.shape[0], C, self.fmt, z.device, 2), st["ts"])
                 ops.quant_rows(z, a)
-                g = ops.gemm_plain(a, st["W"])
+                g = ops.gemm_plain(a, st["W"], tag="head")
             u = ops.dw_ln(g, st["bias"], st["dww"], st["g"], st["b"], B, Hs, Ws, st["eps"])
             z = u.view(B * 4 * Hs * Ws, C)
             Hs, Ws = 2 * Hs, 2 * Ws
         h = qb
         for i, (W, b) in enumerate(self.mh):
-            h = ops.gemm_plain(h, W, b, gelu=i < len(self.mh) - 1)
+            h = ops.gemm_plain(h, W, b, gelu=i < len(self.mh) - 1, tag="head")
         ml = torch.empty(B, Q, Hs * Ws, dtype=BF, device=t.device)
         uv = u.view(B, Hs * Ws, C)
         for i in range(B):
-            ops.gemm_plain(h[i * Q:(i + 1) * Q], ops.QWeight(uv[i], "bf16"), out=ml[i])
+            ops.gemm_plain(h[i * Q:(i + 1) * Q], ops.QWeight(uv[i], "bf16"), out=ml[i], tag="mask")
         return ml.view(B, Q, Hs, Ws), cl
 
 
