@@ -60,6 +60,20 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(const float* v) {
   return r;
 }
 
+// 4 floats -> 4 e2m1 nibbles in the low 16 bits, element 0 in the lowest nibble.
+__device__ __forceinline__ uint32_t cvt_e2m1x4(const float* v) {
+  uint16_t r;
+  asm("{\n\t"
+      ".reg .b8 b0, b1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "mov.b16 %0, {b0, b1};\n\t"
+      "}"
+      : "=h"(r)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]));
+  return r;
+}
+
 __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   uint32_t h2;
   uint16_t b = (uint16_t)byte;
@@ -110,12 +124,17 @@ template <int NL>
 __device__ __forceinline__ void quant_mx4(const float (&v)[NL], float amax, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
   int byte = rceil_byte<6>(amax, 254, div_true);
   float inv = pow2_int(127 - byte);
-  float t[8];
+  if constexpr (NL == 4) {
+    float t[4] = {v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv};
+    out[0] = cvt_e2m1x4(t);                     // 16 bits
+  } else {
+    float t[8];
 #pragma unroll
-  for (int i = 0; i < NL; i += 8) {
+    for (int i = 0; i < NL; i += 8) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = v[i + j] * inv;
-    out[i / 8] = cvt_e2m1x8(t);
+      for (int j = 0; j < 8; ++j) t[j] = v[i + j] * inv;
+      out[i / 8] = cvt_e2m1x8(t);
+    }
   }
   sf_byte = byte;
 }
@@ -128,12 +147,19 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, floa
   float denom = e4m3_to_float(sb) * ts;
   bool ok = denom > 0.f;
   float dd = ok ? denom : 1.0f;
-  float tt[8];
+  if constexpr (NL == 4) {
+    float tt[4];
 #pragma unroll
-  for (int i = 0; i < NL; i += 8) {
+    for (int j = 0; j < 4; ++j) tt[j] = ok ? __fdiv_rn(v[j], dd) : 0.f;
+    out[0] = cvt_e2m1x4(tt);                    // 16 bits
+  } else {
+    float tt[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) tt[j] = ok ? __fdiv_rn(v[i + j], dd) : 0.f;
-    out[i / 8] = cvt_e2m1x8(tt);
+    for (int i = 0; i < NL; i += 8) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tt[j] = ok ? __fdiv_rn(v[i + j], dd) : 0.f;
+      out[i / 8] = cvt_e2m1x8(tt);
+    }
   }
   sf_byte = (int)sb;
 }

@@ -5,9 +5,12 @@
 //              the 128x4 blocked layout, one 512-byte atom per 128 rows x 4 k-blocks
 //   tile       128 x 128 output tile per CTA step, 128 bytes of K per pipeline stage (one TMA swizzle atom per row)
 //   pipeline   warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy), warp 1 = MMA issuer
-//              (tcgen05.cp scale atoms smem -> TMEM, 4 MMAs of 32 K-bytes per stage), warps 2..5 = epilogue
-//              (tcgen05.ld, one accumulator row per thread); two accumulator stages in TMEM so the epilogue of tile
-//              i overlaps the main loop of tile i+1; persistent CTAs, one per SM, static round-robin over tiles
+//              (tcgen05.cp scale atoms smem -> TMEM, 4 MMAs of 32 K-bytes per stage), warps 2..17 = epilogue: the
+//              fused epilogues are bound by CUDA-core issue and memory latency, not by TMEM bandwidth, so 16 warps
+//              each take one (32-row TMEM quarter, 32-column chunk) piece of the tile: tcgen05.ld one accumulator row
+//              per thread, hand TMEM back at once, restage through warp-private swizzled shared memory so every
+//              global load / store is coalesced; two accumulator stages in TMEM so the epilogue of tile i overlaps
+//              the main loop of tile i+1; persistent CTAs, one per SM, static round-robin over tiles
 //   epilogues  PLAIN  out = act(acc*ts + bias)                       -> f32 | bf16 | f16 [M,N]
 //              RES    out = R + gamma * (acc*ts + bias)              -> f32 [M,N]         (proj, fc2)
 //              ROPE   bias + rotary embedding of q,k + relayout      -> bf16 | f16 [3,B,Ntok,H,64]   (qkv)
@@ -24,13 +27,15 @@ namespace kf {
 
 constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
 constexpr int BM = 128, BN = 128, BKB = 128;          // tile rows, tile columns, K bytes per stage
-constexpr int STAGES = 6;
+constexpr int STAGES = 4;
 constexpr int TILE_BYTES = (BM + BN) * BKB;            // 32 KB of operands per stage
 constexpr int SF_STAGE_BYTES = 4096;                   // up to 4 atoms for A and 4 for W per stage
-constexpr int GEMM_THREADS = 192;
+constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
+constexpr int EPI_WARPS = 16;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;                       // accumulators: columns [0,256); scale factors from 256
-constexpr size_t GEMM_SMEM = 1024 + (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + 256;
+constexpr size_t GEMM_SMEM = 1024 + (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
 
 struct GemmArgs {
   const uint8_t *sfa, *sfw;
@@ -57,49 +62,37 @@ template <>
 struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
 
 // ------------------------------------------------------------------------------------------------ epilogue pieces
-__device__ __forceinline__ void store_row32(void* base, int out_dtype, const float (&v)[32]) {
-  if (out_dtype == KF_F32) {
-    float4* p = reinterpret_cast<float4*>(base);
+// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns); global memory wants a warp to touch
+// consecutive addresses.  Each epilogue warp therefore restages its 32 x 32 chunk through a private shared-memory
+// tile (128 bytes per row, 16-byte pieces XOR-swizzled by the row so both directions are bank-conflict free) and
+// continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4 columns 4*(l&7).. of row 4*i + (l>>3), so a
+// warp instruction covers 4 rows x 128 contiguous bytes of fp32 output, and the column-indexed vectors (bias, gamma)
+// are one float4 per lane per chunk.
+__device__ __forceinline__ void stg_put(float* stg, int lane, const uint32_t (&r)[32]) {
+  uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) p[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-  } else {
-    uint32_t w[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      if (out_dtype == KF_BF16) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
-      } else {
-        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
-      }
-    }
-    uint4* p = reinterpret_cast<uint4*>(base);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) p[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-  }
+  for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
 }
-
-__device__ __forceinline__ void load32(const float* p, float (&v)[32]) {
-  const float4* p4 = reinterpret_cast<const float4*>(p);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float4 t = __ldg(p4 + i);
-    v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-  }
+__device__ __forceinline__ float4 stg_get(const float* stg, int lane, int i) {
+  const int row = 4 * i + (lane >> 3);
+  return reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)];
 }
-
-// acc*ts + bias for 32 consecutive columns starting at n0
-__device__ __forceinline__ void scale_bias(const uint32_t (&r)[32], float ts, const float* bias, int n0, float (&v)[32]) {
-  if (bias) {
-    float b[32];
-    load32(bias + n0, b);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(r[i]), ts, b[i]);
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
+  return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w));
+}
+__device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
+  uint2 o;
+  if (out_dtype == KF_BF16) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
   } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ts;
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
   }
+  return o;
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -114,7 +107,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sfs + (size_t)STAGES * SF_STAGE_BYTES);
+  uint8_t* stg_all = sfs + (size_t)STAGES * SF_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + EPI_WARPS * STG_WARP_BYTES);
   uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_holder + 1;
@@ -127,8 +121,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 4);
-    mbar_init(&tempty[1], 4);
+    mbar_init(&tempty[0], EPI_WARPS);
+    mbar_init(&tempty[1], EPI_WARPS);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -218,162 +212,160 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
+    // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 32-column chunk)
+    const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    const int wq = (warp - 2) >> 2;               // which 32-column chunk of the 128-column tile
+    float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES);
+    const int c4 = 4 * (lane & 7);                // this lane's 4 columns inside the chunk
+    const int rsub = lane >> 3;                   // row 4*i + rsub in pass i
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
       const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
       const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
-      if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
-      tc_fence_after();
-      const int m = m_blk * BM + row_in_tile;
-      const bool row_ok = m < g.M;
+      const int rbase = m_blk * BM + quarter * 32;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
       uint32_t r[32];
-      float v[32];
+
+      if (EPI == KF_EPI_ROPE) {
+        // wq = (head inside the tile, which half of the head this warp writes: 0 = columns 0..31, 1 = columns 32..63)
+        const int hc = wq >> 1, part = wq & 1;
+        const int n0 = n_blk * BN + hc * 64;
+        const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
+        const int nbatch = g.M / g.Ntok;
+        const float4 b_lo = g.bias ? ldg4(g.bias + n0 + c4) : z4, b_hi = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
+        if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
+        tc_fence_after();
+        uint32_t r2[32];
+        tmem_ld32(taddr + hc * 64, r);
+        tmem_ld32(taddr + hc * 64 + 32, r2);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[as]);               // accumulator is in registers: hand TMEM back
+        float4 lo[8], hi[8];
+        stg_put(stg, lane, r);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo[i] = fma4(stg_get(stg, lane, i), ts, b_lo);
+        __syncwarp();
+        stg_put(stg, lane, r2);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hi[i] = fma4(stg_get(stg, lane, i), ts, b_hi);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = rbase + 4 * i + rsub;
+          if (m < g.M) {
+            const int b = m / g.Ntok, t = m - b * g.Ntok;
+            float4 o = part ? hi[i] : lo[i];
+            if (which < 2 && t >= g.prefix) {
+              const size_t off = (size_t)(t - g.prefix) * 64 + part * 32 + c4;
+              const float4 sn = ldg4(g.sin + off), cs = ldg4(g.cos + off);
+              if (part == 0)      // lo' = lo*cos - hi*sin
+                o = make_float4(lo[i].x * cs.x - hi[i].x * sn.x, lo[i].y * cs.y - hi[i].y * sn.y, lo[i].z * cs.z - hi[i].z * sn.z,
+                                lo[i].w * cs.w - hi[i].w * sn.w);
+              else                // hi' = hi*cos + lo*sin
+                o = make_float4(hi[i].x * cs.x + lo[i].x * sn.x, hi[i].y * cs.y + lo[i].y * sn.y, hi[i].z * cs.z + lo[i].z * sn.z,
+                                hi[i].w * cs.w + lo[i].w * sn.w);
+            }
+            uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + part * 32 + c4) * 2;
+            *reinterpret_cast<uint2*>(dst) = pack4(o, g.out_dtype);
+          }
+        }
+        continue;
+      }
+
+      const int n = n_blk * BN + wq * 32 + c4;                   // this lane's first column
+      const float4 b4 = g.bias ? ldg4(g.bias + n) : z4;
+      float4 rr[8];
+      float4 g4 = z4;
+      if (EPI == KF_EPI_RES) {                                    // residual loads go out before the accumulator wait
+        g4 = ldg4(g.gamma + n);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = rbase + 4 * i + rsub;
+          rr[i] = m < g.M ? *reinterpret_cast<const float4*>(g.R + (size_t)m * g.N + n) : z4;
+        }
+      }
+      if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
+      tc_fence_after();
+      tmem_ld32(taddr + wq * 32, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[as]);                   // accumulator is in registers: hand TMEM back
+      stg_put(stg, lane, r);
+      __syncwarp();
 
       if (EPI == KF_EPI_PLAIN) {
         const int esz = g.out_dtype == KF_F32 ? 4 : 2;
-        const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int n0 = n_blk * BN + c * 32;
-          scale_bias(r, ts, g.bias, n0, v);
-          if (g.flags & KF_G_GELU) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+        for (int i = 0; i < 8; ++i) {
+          const int m = rbase + 4 * i + rsub;
+          float4 v = fma4(stg_get(stg, lane, i), ts, b4);
+          if (g.flags & KF_G_GELU) v = make_float4(gelu_erf(v.x), gelu_erf(v.y), gelu_erf(v.z), gelu_erf(v.w));
+          if (g.flags & KF_G_ROUND_BF16) v = make_float4(bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w));
+          if (m < g.M) {
+            const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
+            uint8_t* dst = static_cast<uint8_t*>(g.C) + ((size_t)orow * g.N + n) * esz;
+            if (g.out_dtype == KF_F32) *reinterpret_cast<float4*>(dst) = v;
+            else *reinterpret_cast<uint2*>(dst) = pack4(v, g.out_dtype);
           }
-          if (g.flags & KF_G_ROUND_BF16) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = bf16_round(v[i]);
-          }
-          if (row_ok) store_row32(static_cast<uint8_t*>(g.C) + ((size_t)orow * g.N + n0) * esz, g.out_dtype, v);
         }
       } else if (EPI == KF_EPI_RES) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int n0 = n_blk * BN + c * 32;
-          scale_bias(r, ts, g.bias, n0, v);
-          if (row_ok) {
-            float gm[32], rr[32];
-            load32(g.gamma + n0, gm);
-            load32(g.R + (size_t)m * g.N + n0, rr);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = fmaf(gm[i], v[i], rr[i]);
-            store_row32(static_cast<float*>(g.C) + (size_t)m * g.N + n0, KF_F32, v);
-          }
-        }
-      } else if (EPI == KF_EPI_ROPE) {
-        const int b = m / g.Ntok, t = m - b * g.Ntok;
-        const int nbatch = g.M / g.Ntok;
-#pragma unroll 1
-        for (int hc = 0; hc < BN / 64; ++hc) {
-          uint32_t r2[32];
-          float hi[32];
-          tmem_ld32(taddr + hc * 64, r);
-          tmem_ld32(taddr + hc * 64 + 32, r2);
-          tmem_ld_wait();
-          const int n0 = n_blk * BN + hc * 64;
-          scale_bias(r, ts, g.bias, n0, v);
-          scale_bias(r2, ts, g.bias, n0 + 32, hi);
-          const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
-          if (row_ok) {
-            if (which < 2 && t >= g.prefix) {
-              const float* sp = g.sin + (size_t)(t - g.prefix) * 64;
-              const float* cp = g.cos + (size_t)(t - g.prefix) * 64;
-              float s_lo[32], c_lo[32];
-              load32(sp, s_lo);
-              load32(cp, c_lo);
-              float lo2[32];
-#pragma unroll
-              for (int i = 0; i < 32; ++i) lo2[i] = v[i] * c_lo[i] - hi[i] * s_lo[i];
-              load32(sp + 32, s_lo);
-              load32(cp + 32, c_lo);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                hi[i] = hi[i] * c_lo[i] + v[i] * s_lo[i];
-                v[i] = lo2[i];
-              }
-            }
-            uint8_t* dst = static_cast<uint8_t*>(g.C) + ((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 * 2;
-            store_row32(dst, g.out_dtype, v);
-            store_row32(dst + 64, g.out_dtype, hi);
-          }
+        for (int i = 0; i < 8; ++i) {
+          const int m = rbase + 4 * i + rsub;
+          const float4 v = fma4(stg_get(stg, lane, i), ts, b4);
+          if (m < g.M)
+            *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
+                make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
         }
       } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
         const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
         const bool rb = g.flags & KF_Q_ROUND_BF16;
         float tso = 1.f;
         if (g.out_fmt == KF_FMT_NV4) tso = __ldg(g.tso);
-        uint32_t sfw0 = 0, sfw1 = 0;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int n0 = n_blk * BN + c * 32;
-          scale_bias(r, ts, g.bias, n0, v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v[i] = gelu_erf(v[i]);
-            if (rb) v[i] = bf16_round(v[i]);
-          }
-          const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
-          const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
-          float am0 = 0.f, am1 = 0.f;
+        for (int i = 0; i < 8; ++i) {
+          const int m = rbase + 4 * i + rsub;
+          const bool ok = m < g.M;
+          const float4 a = fma4(stg_get(stg, lane, i), ts, b4);
+          float v[4] = {gelu_erf(a.x), gelu_erf(a.y), gelu_erf(a.z), gelu_erf(a.w)};
+          if (rb) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            am0 = fmaxf(am0, fabsf(v[i]));
-            am1 = fmaxf(am1, fabsf(v[16 + i]));
+            for (int k = 0; k < 4; ++k) v[k] = bf16_round(v[k]);
           }
-          int by0, by1;
-          if (g.out_fmt == KF_FMT_MX8) {
-            uint32_t o[8];
-            const float am = fmaxf(am0, am1);
-            quant_mx8<16>(va, am, div_true, o, by0);
-            quant_mx8<16>(vb, am, div_true, o + 4, by0);
-            if (row_ok) {
-              uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
-              p[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              p[1] = make_uint4(o[4], o[5], o[6], o[7]);
-            }
-            sfw0 |= (uint32_t)(row_ok ? by0 : 0) << (8 * c);
-          } else if (g.out_fmt == KF_FMT_MX4) {
-            uint32_t o[4];
-            const float am = fmaxf(am0, am1);
-            quant_mx4<16>(va, am, div_true, o, by0);
-            quant_mx4<16>(vb, am, div_true, o + 2, by0);
-            if (row_ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-            sfw0 |= (uint32_t)(row_ok ? by0 : 0) << (8 * c);
+          float am = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+          am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+          am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));          // 16 columns: one nv4 block
+          int byte;
+          uint32_t o[1];
+          if (g.out_fmt == KF_FMT_NV4) {
+            quant_nv4<4>(v, am, tso, div_true, o, byte);
+            if (ok) *reinterpret_cast<uint16_t*>(g.Qo + (size_t)m * (g.N >> 1) + (n >> 1)) = (uint16_t)o[0];
+            const uint32_t b_hi = __shfl_down_sync(0xffffffffu, (uint32_t)byte, 4);        // the block of columns 16..31
+            if ((lane & 7) == 0)      // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
+              *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n_blk * 8 + wq * 2, g.N >> 6)) = ok ? (uint16_t)(byte | (b_hi << 8)) : (uint16_t)0;
           } else {
-            uint32_t o[4];
-            quant_nv4<16>(va, am0, tso, div_true, o, by0);
-            quant_nv4<16>(vb, am1, tso, div_true, o + 2, by1);
-            if (row_ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-            const uint32_t two = row_ok ? ((uint32_t)by0 | ((uint32_t)by1 << 8)) : 0u;
-            if (c < 2) sfw0 |= two << (16 * c);
-            else sfw1 |= two << (16 * (c - 2));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));        // 32 columns: one mx block
+            if (g.out_fmt == KF_FMT_MX8) {
+              quant_mx8<4>(v, am, div_true, o, byte);
+              if (ok) *reinterpret_cast<uint32_t*>(g.Qo + (size_t)m * g.N + n) = o[0];
+            } else {
+              quant_mx4<4>(v, am, div_true, o, byte);
+              if (ok) *reinterpret_cast<uint16_t*>(g.Qo + (size_t)m * (g.N >> 1) + (n >> 1)) = (uint16_t)o[0];
+            }
+            if ((lane & 7) == 0) g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)byte : (uint8_t)0;
           }
-        }
-        // scale words of this row for the tile's 128 columns (rows beyond M inside the last tile get zeros)
-        if (g.out_fmt == KF_FMT_NV4) {
-          uint32_t* p = reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 8, g.N >> 6));
-          p[0] = sfw0;
-          *reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 8 + 4, g.N >> 6)) = sfw1;
-        } else {
-          *reinterpret_cast<uint32_t*>(g.SFo + sf_offset(m, n_blk * 4, g.N >> 7)) = sfw0;
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[as]);
+      __syncwarp();                                               // staging tile is reused by the next tile
     }
   }
 
