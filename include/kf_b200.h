@@ -54,6 +54,7 @@ extern "C" {
 /* GEMM flags (share the flag word with KF_Q_ROUND_BF16 / KF_Q_RECIP_DIV, which act on the QUANT epilogue) */
 #define KF_G_GELU 8        /* PLAIN: apply gelu_erf after the bias */
 #define KF_G_ROUND_BF16 16 /* PLAIN: round the value to bf16 before storing (matters for an f32 output) */
+#define KF_G_PRE_ROUND_BF16 32 /* PLAIN: round acc*ts to bf16 BEFORE the bias is added (a bf16 GEMM followed by bias + GELU) */
 
 /* Library version and the SM architecture the kernels were built for ("sm_100a"). */
 KF_API const char* kf_version(void);
@@ -139,10 +140,12 @@ KF_API int kf_im2col_patch16(const void* x, void* out, int B, int S, void* strea
 
 /* ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] (ConvTranspose2d k2 s2 as a GEMM, column (dy*2+dx)*C + c) -> bias + GELU +
  * pixel shuffle + depthwise 3x3 (dww fp32 [9, C], tap-major, zero padding) + LayerNorm2D -> out bf16 [B, 2Hs, 2Ws, C].
+ * pre_act != 0: g already holds bf16(gelu(conv + bias)) (applied by the GEMM epilogue: KF_G_PRE_ROUND_BF16 | KF_G_GELU
+ * with the bias repeated 4x), so bias + GELU are skipped here.
  * Replaces dw_ln (infer-opt/round11_attn_tier0/impl/head_ext11.cu:72-250) = ScaleBlock.forward after conv1
  * (src/lightly_train/_task_models/dinov3_eomt_semantic_segmentation/scale_block.py:39-44). */
 KF_API int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B,
-                    int Hs, int Ws, int C, float eps, void* stream);
+                    int Hs, int Ws, int C, float eps, int pre_act, void* stream);
 
 /* Per-pixel semantic scores: scores[b,c,p] = sum_q sigmoid(mask_logits[b,q,p]) * softmax(class_logits[b,q,:])[c]
  * (fp32 [B, ncls+1, HW], optional) and labels[b,p] = argmax over the ncls real classes (uint8, optional).

@@ -18,7 +18,7 @@ KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
 KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV = 1, 2, 4
 
 KF_EPI = {"plain": 0, "res": 1, "rope": 2, "quant": 3}
-KF_G_GELU, KF_G_ROUND_BF16 = 8, 16
+KF_G_GELU, KF_G_ROUND_BF16, KF_G_PRE_ROUND_BF16 = 8, 16, 32
 
 
 class GemmParams(C.Structure):
@@ -65,7 +65,7 @@ def lib() -> C.CDLL:
             "kf_tensor_peak_probe": [i32, i32, i32, C.POINTER(C.c_double), vp],
             "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp],
             "kf_im2col_patch16": [vp, vp, i32, i32, vp],
-            "kf_dw_ln": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
+            "kf_dw_ln": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, vp],
             "kf_semantic": [vp, vp, i32, i32, i32, i32, vp, vp, vp],
             "kf_resize_norm": [vp, vp, i32, i32, i32, i32, C.POINTER(C.c_float), C.POINTER(C.c_float), vp],
         }

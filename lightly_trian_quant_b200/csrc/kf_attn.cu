@@ -9,8 +9,8 @@
 //            swizzled smem, O_tile accumulation with the rescale factor in registers);
 //            warp 4: TMA producer (Q once, K / V double buffered, 4-D tensor maps so rows past N read zero);
 //            warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16;  O_tile = P V: 8 MMAs of K=16, V as the MN-major operand)
-//   numerics softmax scale 1/8 folded into exp2; running max never reset; m, l, O in fp32; P rounded to the input
-//            16-bit type; every mbarrier wait is bounded.
+//   numerics softmax scale 1/8 folded into exp2; running max never reset and raised lazily; m, l, O in fp32; P rounded
+//            to the input 16-bit type; every mbarrier wait is bounded.
 //
 // Replaces a16::fwd_kernel / attn16_fwd (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404; mma.sync m16n8k16 +
 // TMA on sm_120).  The power-of-two Q pre-scale `pre` of the reference protects its fp16 accumulators
@@ -142,7 +142,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // A: 16 keys = 32 bytes inside key atom kk/4 of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
           const uint64_t ad = pdesc + (uint64_t)((kk >> 2) * (AT_TILE >> 4) + (kk & 3) * 2);
           const uint64_t bd = vdesc + (uint64_t)(kk * (2048 >> 4));
-          mma_f16(t_o, ad, bd, idesc_o, kk != 0);
+          mma_f16(t_o, ad, bd, idesc_o, (j | kk) != 0);      // O accumulates in TMEM over all key tiles
         }
         tc_commit(o_full);
         tc_commit(&kv_empty[st]);
@@ -160,13 +160,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax: thread = query row
+    // O accumulates in TMEM across key tiles.  The running maximum is only raised when the tile maximum exceeds it
+    // by more than 8 in the exponent domain (P then stays <= 2^8, harmless in bf16 / fp32), so the rescale of O
+    // (TMEM load, multiply, store) happens on the first tiles and then almost never.
     const int row = warp * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float sc = a.scale_log2;
+    const float thr = 8.0f / sc;
     float m_run = -INFINITY, l_run = 0.f;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     uint8_t* prow = smem + AT_OFF_P + row * 128;
     const int sw = row & 7;
     bool ok = true;
@@ -174,75 +175,88 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!mbar_wait(s_full, j & 1, ctx, 17)) { ok = false; break; }
       tc_fence_after();
       const int kbase = j * AT_BN;
-      const bool tail = kbase + AT_BN > a.N;
-      uint32_t r[32];
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_lane + AT_COL_S + c * 32, r);
-        tmem_ld_wait();
-        if (tail) {
+      uint32_t r[4][32];
+      tmem_ld32(t_lane + AT_COL_S, r[0]);
+      tmem_ld32(t_lane + AT_COL_S + 32, r[1]);
+      tmem_ld32(t_lane + AT_COL_S + 64, r[2]);
+      tmem_ld32(t_lane + AT_COL_S + 96, r[3]);
+      tmem_ld_wait();
+      if (kbase + AT_BN > a.N) {                                // key tail: columns past N never win the max and give P = 0
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (kbase + c * 32 + i < a.N) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+            if (kbase + c * 32 + i >= a.N) r[c][i] = 0xff800000u;
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = ex2((m_run - m_new) * sc);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+      const float m_new = (mx > m_run + thr) ? mx : m_run;       // first tile: m_run = -inf, so m_new = mx
+      const float alpha = ex2((m_run - m_new) * sc);             // 1 when unchanged, 0 on the first tile
+      const bool need = (m_new != m_run) && j > 0;
+      const uint32_t any = __ballot_sync(0xffffffffu, need);
       const float mneg = -m_new * sc;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(t_lane + AT_COL_S + c * 32, r);
-        tmem_ld_wait();
-        float p[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = ex2(fmaf(__uint_as_float(r[i]), sc, mneg));
-          if (tail && kbase + c * 32 + i >= a.N) e = 0.f;
-          p[i] = e;
-          sum += e;
-        }
+      for (int c = 0; c < 4; ++c) {
         // 32 keys = 64 bytes = four 16-byte chunks of this row inside key atom c/2, XOR-swizzled by the row
         uint8_t* atom = prow + (c >> 1) * AT_TILE;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
+          float p[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
+            sum += p[k];
+          }
           const int chunk = ((c & 1) * 4 + i) ^ sw;
           *reinterpret_cast<uint4*>(atom + chunk * 16) =
-              make_uint4(pack16(p[8 * i], p[8 * i + 1], a.f16), pack16(p[8 * i + 2], p[8 * i + 3], a.f16),
-                         pack16(p[8 * i + 4], p[8 * i + 5], a.f16), pack16(p[8 * i + 6], p[8 * i + 7], a.f16));
+              make_uint4(pack16(p[0], p[1], a.f16), pack16(p[2], p[3], a.f16), pack16(p[4], p[5], a.f16), pack16(p[6], p[7], a.f16));
         }
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
+      if (any) {                                                 // some row of this warp raised its maximum: rescale O in TMEM
+        if (!mbar_wait(o_full, (j - 1) & 1, ctx, 18)) { ok = false; break; }
+        tc_fence_after();
+        tmem_ld32(t_lane + AT_COL_O, r[0]);
+        tmem_ld32(t_lane + AT_COL_O + 32, r[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          r[0][i] = __float_as_uint(__uint_as_float(r[0][i]) * alpha);
+          r[1][i] = __float_as_uint(__uint_as_float(r[1][i]) * alpha);
+        }
+        tmem_st32(t_lane + AT_COL_O, r[0]);
+        tmem_st32(t_lane + AT_COL_O + 32, r[1]);
+        tmem_st_wait();
+      }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(p_full);
-      if (!mbar_wait(o_full, j & 1, ctx, 18)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t r2[32];
-      tmem_ld32(t_lane + AT_COL_O, r);
-      tmem_ld32(t_lane + AT_COL_O + 32, r2);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        o[i] = fmaf(o[i], alpha, __uint_as_float(r[i]));
-        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(r2[i]));
-      }
-      tc_fence_before();
     }
+    if (ok) ok = mbar_wait(o_full, (n_kt - 1) & 1, ctx, 19);
     const int n = qt * AT_BM + row;
-    if (ok && n < a.N) {
-      const float inv = 1.0f / l_run;
-      uint32_t w[32];
+    if (ok) {
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(t_lane + AT_COL_O, r0);
+      tmem_ld32(t_lane + AT_COL_O + 32, r1);
+      tmem_ld_wait();
+      if (n < a.N) {
+        const float inv = 1.0f / l_run;
+        uint32_t w[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) w[i] = pack16(o[2 * i] * inv, o[2 * i + 1] * inv, a.f16);
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.O) + (((size_t)b * a.N + n) * a.H + h) * (AT_D * 2));
+        for (int i = 0; i < 16; ++i) {
+          w[i] = pack16(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, a.f16);
+          w[16 + i] = pack16(__uint_as_float(r1[2 * i]) * inv, __uint_as_float(r1[2 * i + 1]) * inv, a.f16);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.O) + (((size_t)b * a.N + n) * a.H + h) * (AT_D * 2));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      }
     }
   }
 

@@ -307,7 +307,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int m = rbase + 4 * i + rsub;
-          float4 v = fma4(stg_get(stg, lane, i), ts, b4);
+          float4 v;
+          if (g.flags & KF_G_PRE_ROUND_BF16) {      // the GEMM result is rounded to bf16 before the bias is added
+            const float4 a = stg_get(stg, lane, i);
+            v = make_float4(bf16_round(a.x * ts) + b4.x, bf16_round(a.y * ts) + b4.y, bf16_round(a.z * ts) + b4.z, bf16_round(a.w * ts) + b4.w);
+          } else {
+            v = fma4(stg_get(stg, lane, i), ts, b4);
+          }
           if (g.flags & KF_G_GELU) v = make_float4(gelu_erf(v.x), gelu_erf(v.y), gelu_erf(v.z), gelu_erf(v.w));
           if (g.flags & KF_G_ROUND_BF16) v = make_float4(bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w));
           if (m < g.M) {

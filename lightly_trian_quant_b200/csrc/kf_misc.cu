@@ -27,94 +27,134 @@ __global__ void __launch_bounds__(256) im2col16_kernel(const __nv_bfloat16* __re
 
 // ------------------------------------------------------------------------------------------------ ScaleBlock tail
 // g [B*Hs*Ws, 4C] bf16 is the ConvTranspose2d(k=2, s=2) GEMM output with column (dy*2+dx)*C + c.  For each output
-// pixel (Y, X) = (2y+dy, 2x+dx):  a = bf16(gelu(g + bias[c]));  o = bf16(sum over the 3x3 taps of a * dww[tap][c])
-// with zero padding, fp32 accumulation in tap order;  out = bf16(LayerNorm over c of o) in NHWC.
-// One CTA = 4 x 8 output pixels; the activations of the 6 x 10 halo are staged through shared memory 256 channels at
-// a time, the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics.
+// pixel (Y, X) = (2y+dy, 2x+dx):  a = bf16(gelu(g + bias[c]))  (skipped when the GEMM epilogue already applied it:
+// pre_act != 0);  o = bf16(sum over the 3x3 taps of a * dww[tap][c]) with zero padding, fp32 accumulation in tap
+// order;  out = bf16(LayerNorm over c of o) in NHWC.
+// One CTA = 4 x 8 output pixels.  Per 256-channel slab: the 6 x 10 halo is brought in with 16-byte loads (512
+// contiguous bytes per pixel), each thread then convolves 8 channels of 4 pixels with the 72 tap weights held in
+// registers; the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics.
 constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 256;
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 __global__ void __launch_bounds__(256, 2)
 dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias, const float* __restrict__ dww, const float* __restrict__ lnw,
-             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps) {
+             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps, int pre_act) {
   extern __shared__ __align__(16) uint8_t dsm[];
-  __nv_bfloat162* act = reinterpret_cast<__nv_bfloat162*>(dsm);                               // [60][128] channel pairs
-  __nv_bfloat162* res = reinterpret_cast<__nv_bfloat162*>(dsm + DW_HW * DW_CH * 2);           // [32][C/2]
+  uint4* act = reinterpret_cast<uint4*>(dsm);                               // [60 pixels][32 groups of 8 channels]
+  uint4* res = reinterpret_cast<uint4*>(dsm + DW_HW * DW_CH * 2);           // [32 pixels][C/8]
   const int t = threadIdx.x;
   const int Ho = 2 * Hs, Wo = 2 * Ws;
   const int X0 = blockIdx.x * DW_TW, Y0 = blockIdx.y * DW_TH, b = blockIdx.z;
-  const int cp = t & 127, half = t >> 7;
-  const int C2 = C >> 1;
+  const int grp = t & 31, prow = t >> 5;                                     // 8-channel group, pixel sub-index 0..7
+  const int C8 = C >> 3;
 
   for (int ch = 0; ch < C; ch += DW_CH) {
-    const int c0 = ch + cp * 2;
-    const float b0 = __ldg(bias + c0), b1 = __ldg(bias + c0 + 1);
-#pragma unroll 2
-    for (int px = half; px < DW_HW; px += 2) {
+    // ---- halo: 60 pixels x 32 uint4
+    for (int idx = t; idx < DW_HW * 32; idx += 256) {
+      const int px = idx >> 5, q = idx & 31;
       const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
       const int Y = Y0 + hy - 1, X = X0 + hx - 1;
-      __nv_bfloat162 v = __floats2bfloat162_rn(0.f, 0.f);
+      uint4 v = make_uint4(0, 0, 0, 0);
       if (Y >= 0 && Y < Ho && X >= 0 && X < Wo) {
         const int64_t row = ((int64_t)b * Hs + (Y >> 1)) * Ws + (X >> 1);
-        const __nv_bfloat162 raw = *reinterpret_cast<const __nv_bfloat162*>(g + row * 4 * C + ((Y & 1) * 2 + (X & 1)) * C + c0);
-        const float2 f = __bfloat1622float2(raw);
-        v = __floats2bfloat162_rn(gelu_erf(f.x + b0), gelu_erf(f.y + b1));
+        v = __ldg(reinterpret_cast<const uint4*>(g + row * 4 * C + ((Y & 1) * 2 + (X & 1)) * C + ch) + q);
+        if (!pre_act) {
+          float f[8];
+          bf16x8_to_f32(v, f);
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8)), b1 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8) + 1);
+          const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + bb[k]);
+          v = f32_to_bf16x8(f);
+        }
       }
-      act[px * 128 + cp] = v;
+      act[idx] = v;
     }
-    float w0[9], w1[9];
+    // ---- the 9 x 8 tap weights of this thread's channel group
+    float w[9][8];
 #pragma unroll
     for (int k = 0; k < 9; ++k) {
-      w0[k] = __ldg(dww + k * C + c0);
-      w1[k] = __ldg(dww + k * C + c0 + 1);
+      const float4 w0 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8)), w1 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8) + 1);
+      w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
     }
     __syncthreads();
-#pragma unroll 4
-    for (int px = half; px < DW_TH * DW_TW; px += 2) {
+    // ---- depthwise 3x3: thread = (8 channels, pixels prow, prow+8, prow+16, prow+24)
+#pragma unroll
+    for (int k4 = 0; k4 < 4; ++k4) {
+      const int px = prow + 8 * k4;
       const int oy = px / DW_TW, ox = px - oy * DW_TW;
-      float a0 = 0.f, a1 = 0.f;
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll
       for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
         for (int kx = 0; kx < 3; ++kx) {
-          const float2 f = __bfloat1622float2(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 128 + cp]);
-          a0 = fmaf(f.x, w0[ky * 3 + kx], a0);
-          a1 = fmaf(f.y, w1[ky * 3 + kx], a1);
+          float f[8];
+          bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 32 + grp], f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] = fmaf(f[k], w[ky * 3 + kx][k], acc[k]);
         }
-      res[px * C2 + (ch >> 1) + cp] = __floats2bfloat162_rn(a0, a1);
+      res[px * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc);
     }
     __syncthreads();
   }
 
-  // LayerNorm over the channels of each pixel: 8 warps x 4 pixels
+  // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels, lane = 8 channels per 256-channel slab
   const int warp = t >> 5, lane = t & 31;
   const float invC = 1.0f / (float)C;
   for (int px = warp; px < DW_TH * DW_TW; px += 8) {
     const int oy = px / DW_TW, ox = px - oy * DW_TW;
     const int Y = Y0 + oy, X = X0 + ox;
-    const __nv_bfloat162* r = res + px * C2;
+    const uint4* r = res + px * C8;
     float s = 0.f;
-    for (int i = lane; i < C2; i += 32) {
-      const float2 f = __bfloat1622float2(r[i]);
-      s += f.x + f.y;
+    for (int i = lane; i < C8; i += 32) {
+      float f[8];
+      bf16x8_to_f32(r[i], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += f[k];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     const float mean = s * invC;
     float ss = 0.f;
-    for (int i = lane; i < C2; i += 32) {
-      const float2 f = __bfloat1622float2(r[i]);
-      ss = fmaf(f.x - mean, f.x - mean, ss);
-      ss = fmaf(f.y - mean, f.y - mean, ss);
+    for (int i = lane; i < C8; i += 32) {
+      float f[8];
+      bf16x8_to_f32(r[i], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss = fmaf(f[k] - mean, f[k] - mean, ss);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float rstd = rsqrtf(ss * invC + eps);
     if (Y < Ho && X < Wo) {
-      __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (((int64_t)b * Ho + Y) * Wo + X) * C);
-      for (int i = lane; i < C2; i += 32) {
-        const float2 f = __bfloat1622float2(r[i]);
-        const float2 w = __ldg(reinterpret_cast<const float2*>(lnw) + i), bb = __ldg(reinterpret_cast<const float2*>(lnb) + i);
-        dst[i] = __floats2bfloat162_rn((f.x - mean) * rstd * w.x + bb.x, (f.y - mean) * rstd * w.y + bb.y);
+      uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)b * Ho + Y) * Wo + X) * C);
+      for (int i = lane; i < C8; i += 32) {
+        float f[8];
+        bf16x8_to_f32(r[i], f);
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
+        const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = (f[k] - mean) * rstd * ww[k] + cc[k];
+        dst[i] = f32_to_bf16x8(f);
       }
     }
   }
@@ -213,11 +253,12 @@ extern "C" int kf_im2col_patch16(const void* x, void* out, int B, int S, void* s
 }
 
 extern "C" int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B, int Hs, int Ws, int C,
-                        float eps, void* stream) {
+                        float eps, int pre_act, void* stream) {
   KF_REQUIRE(B >= 0 && Hs > 0 && Ws > 0, "kf_dw_ln: bad shape B=%d Hs=%d Ws=%d", B, Hs, Ws);
   KF_REQUIRE(C > 0 && C % 256 == 0 && C <= 1024, "kf_dw_ln: C=%d must be a multiple of 256 up to 1024", C);
   if (B == 0) return KF_OK;
-  KF_REQUIRE(g && bias && dww && lnw && lnb && out && al16(g) && al16(out) && al16(lnw) && al16(lnb), "kf_dw_ln: tensors must be non-null and 16-byte aligned");
+  KF_REQUIRE(g && (bias || pre_act) && dww && lnw && lnb && out && al16(g) && al16(out) && al16(lnw) && al16(lnb) && al16(dww) && al16(bias),
+             "kf_dw_ln: tensors must be non-null and 16-byte aligned");
   const size_t smem = (size_t)DW_HW * DW_CH * 2 + (size_t)DW_TH * DW_TW * C * 2;
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -229,7 +270,7 @@ extern "C" int kf_dw_ln(const void* g, const float* bias, const float* dww, cons
   }
   dim3 grid((2 * Ws + DW_TW - 1) / DW_TW, (2 * Hs + DW_TH - 1) / DW_TH, B);
   dw_ln_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(g), bias, dww, lnw, lnb,
-                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps);
+                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps, pre_act);
   return cuda_status(cudaGetLastError(), "kf_dw_ln launch");
 }
 

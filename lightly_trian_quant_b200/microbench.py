@@ -1,0 +1,142 @@
+"""Per-kernel micro-benchmarks of the hot path at the ViT shapes (CUDA events on the launching stream, rotating buffers
+larger than L2 so operands come from HBM, not from cache).
+
+    python -m lightly_trian_quant_b200.microbench gemm --fmt nv4 --kind fc1 --batch 8 [--iters 20]
+    python -m lightly_trian_quant_b200.microbench attn --batch 8 --tokens 1605
+    python -m lightly_trian_quant_b200.microbench ln_quant --fmt mx8 --batch 8
+    python -m lightly_trian_quant_b200.microbench quant_rows --fmt nv4 --batch 8 --k 1024
+    python -m lightly_trian_quant_b200.microbench peak --fmt nv4
+
+`kind` selects the GEMM shape AND its fused epilogue: qkv (bias + RoPE + relayout), proj / fc2 (bias, LayerScale,
+fp32 residual in place), fc1 (bias + GELU + quantise-out), plain (bf16 out).  Prints one JSON line.
+Timing method after infer-opt/round10_lowp_probe/bench10.py:1-8,62-63 (cold weights: R independent copies > L2).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+BF = torch.bfloat16
+SHAPES = {"qkv": (1024, 3072), "proj": (1024, 1024), "fc1": (1024, 4096), "fc2": (4096, 1024), "plain": (1024, 4096)}
+
+
+def _time(fn, iters, warm=5):
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(warm + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def _act(M, K, fmt, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(M, K, generator=g, device="cuda").to(BF)
+    if fmt == "bf16":
+        return x
+    a = ops.ActBuf(M, K, fmt)
+    if fmt == "nv4":
+        a.ts.fill_(float(x.float().abs().max()) / 2688.0)
+    ops.quant_rows(x, a)
+    return a
+
+
+def bench_gemm(args):
+    K, N = SHAPES[args.kind]
+    M = args.tokens * args.batch
+    fmt = args.fmt
+    copies = max(2, int(2 * 126e6 / (N * K)) + 1) if args.cold else 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    Ws = [ops.QWeight(torch.randn(N, K, generator=g, device="cuda") * 0.02, fmt) for _ in range(min(copies, 8))]
+    acts = [_act(M, K, fmt, s) for s in range(2)]
+    bias = torch.randn(N, device="cuda") * 0.02
+    gamma = torch.rand(N, device="cuda")
+    H = 16
+    sin, cos = torch.randn(args.tokens, 64, device="cuda"), torch.randn(args.tokens, 64, device="cuda")
+    res = [torch.randn(M, N, device="cuda") for _ in range(2)] if args.kind in ("proj", "fc2") else None
+    outq = ops.ActBuf(M, N, fmt if fmt != "bf16" else "mx8") if args.kind == "fc1" else None
+    if outq is not None and outq.fmt == "nv4":
+        outq.ts.fill_(0.01)
+    outb = torch.empty(M, N, device="cuda", dtype=BF) if args.kind == "plain" else None
+
+    def fn(i):
+        a, W = acts[i % 2], Ws[i % len(Ws)]
+        if args.kind == "qkv":
+            ops.qkv_rope(a, W, bias, sin, cos, args.tokens, 5, H)
+        elif args.kind in ("proj", "fc2"):
+            ops.gemm_res(a, W, bias, gamma, res[i % 2], out=res[i % 2])
+        elif args.kind == "fc1":
+            if fmt == "bf16":
+                ops.gemm_plain(a, W, bias, gelu=True)
+            else:
+                ops.gemm_gelu_q(a, W, bias, outq, round_bf16=True)
+        else:
+            ops.gemm_plain(a, W, out=outb)
+
+    t = _time(fn, args.iters)
+    fl = 2.0 * M * N * K
+    return {"kernel": f"gemm {fmt} {args.kind}", "M": M, "N": N, "K": K, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
+
+
+def bench_attn(args):
+    B, N, H = args.batch, args.tokens, 16
+    qkvs = [torch.randn(3, B, N, H, 64, device="cuda").to(BF) for _ in range(2)]
+    outs = [torch.empty(B, N, H * 64, device="cuda", dtype=BF) for _ in range(2)]
+    t = _time(lambda i: ops.attn_fwd(qkvs[i % 2], out=outs[i % 2]), args.iters)
+    fl = 4.0 * B * H * N * N * 64
+    return {"kernel": "attn_fwd bf16", "B": B, "N": N, "H": H, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
+
+
+def bench_ln_quant(args):
+    M, d = args.tokens * args.batch, args.k
+    n = max(2, int(2 * 126e6 / (M * d * 4)) + 1)
+    xs = [torch.randn(M, d, device="cuda") for _ in range(n)]
+    bufs = [ops.ActBuf(M, d, args.fmt) for _ in range(n)]
+    w, b = torch.ones(d, device="cuda"), torch.zeros(d, device="cuda")
+    t = _time(lambda i: ops.ln_quant(xs[i % n], w, b, 1e-5, bufs[i % n], round_bf16=True), args.iters)
+    by = M * d * 4 + bufs[0].q.numel() + bufs[0].sf.numel()
+    return {"kernel": f"ln_quant {args.fmt}", "M": M, "d": d, "us": t * 1e6, "GB/s": by / t / 1e9, "bytes": by}
+
+
+def bench_quant_rows(args):
+    M, K = args.tokens * args.batch, args.k
+    n = max(2, int(2 * 126e6 / (M * K * 2)) + 1)
+    xs = [torch.randn(M, K, device="cuda").to(BF) for _ in range(n)]
+    bufs = [ops.ActBuf(M, K, args.fmt) for _ in range(n)]
+    t = _time(lambda i: ops.quant_rows(xs[i % n], bufs[i % n]), args.iters)
+    by = M * K * 2 + bufs[0].q.numel() + bufs[0].sf.numel()
+    return {"kernel": f"quant_rows bf16->{args.fmt}", "M": M, "K": K, "us": t * 1e6, "GB/s": by / t / 1e9, "bytes": by}
+
+
+def bench_peak(args):
+    return {"kernel": f"tcgen05 instruction-rate probe {args.fmt}", "TFLOP/s_n128": ops.tensor_peak_tflops(args.fmt, 128),
+            "TFLOP/s_n256": ops.tensor_peak_tflops(args.fmt, 256)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "ln_quant", "quant_rows", "peak"])
+    ap.add_argument("--fmt", default="nv4")
+    ap.add_argument("--kind", default="fc1", choices=list(SHAPES))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=1605)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--cold", type=int, default=1)
+    args = ap.parse_args()
+    torch.set_grad_enabled(False)
+    fn = {"gemm": bench_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "peak": bench_peak}[args.what]
+    print(json.dumps(fn(args)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -204,7 +204,7 @@ MXW = QWeight
 
 
 def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
-          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block"):
+          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block", pre_round=False):
     p = GemmParams()
     if isinstance(a, ActBuf):
         if a.fmt != W.fmt or a.K != W.K:
@@ -220,7 +220,8 @@ def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin
     p.fmt, p.epi, p.M, p.N, p.K = KF_FMT[W.fmt], KF_EPI[epi], M, W.N, W.K
     p.W, p.SFW, p.ts_w = W.q.data_ptr(), _ptr(W.sf), _ptr(W.ts)
     p.out_dtype = _DT[out_dtype]
-    p.flags = (KF_G_GELU if gelu else 0) | (KF_Q_ROUND_BF16 if round_bf16 else 0) | (KF_Q_RECIP_DIV if recip_div else 0)
+    p.flags = (KF_G_GELU if gelu else 0) | (KF_Q_ROUND_BF16 if round_bf16 else 0) | (KF_Q_RECIP_DIV if recip_div else 0) \
+        | (_lib.KF_G_PRE_ROUND_BF16 if pre_round else 0)
     p.Ntok, p.prefix, p.H = Ntok, prefix, H
     _need_cuda(bias, gamma, R, C, sin, cos)
     p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
@@ -235,13 +236,13 @@ def _f32c(t, n, what):
 
 
 def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.bfloat16, out: Optional[torch.Tensor] = None,
-               tag: str = "block") -> torch.Tensor:
+               tag: str = "block", pre_round: bool = False) -> torch.Tensor:
     """[M, N] = act(a @ W^T (* ts) + bias) in bf16 / f16 / f32 (mm, gemm_plain, fwd_bias, fwd_gelu, fwd_plain)."""
     M = a.M if isinstance(a, ActBuf) else a.shape[0]
     _f32c(bias, W.N, "bias")
     if out is None:
         out = torch.empty(M, W.N, dtype=out_dtype, device=W.q.device)
-    _gemm(a, W, "plain", bias=bias, C=out, out_dtype=out.dtype, gelu=gelu, tag=tag)
+    _gemm(a, W, "plain", bias=bias, C=out, out_dtype=out.dtype, gelu=gelu, tag=tag, pre_round=pre_round)
     return out
 
 
@@ -342,15 +343,16 @@ def ln_tail(x: torch.Tensor, w, b, eps: float, Q: int, npre: int):
     return qb, xb
 
 
-def dw_ln(g: torch.Tensor, bias, dww, lnw, lnb, B: int, Hs: int, Ws: int, eps: float) -> torch.Tensor:
-    """ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] -> bf16 [B, 2Hs, 2Ws, C] (dw_ln_launch, head11.py:60-67)."""
-    _need_cuda(g, bias, dww, lnw, lnb)
+def dw_ln(g: torch.Tensor, bias, dww, lnw, lnb, B: int, Hs: int, Ws: int, eps: float, pre_act: bool = False) -> torch.Tensor:
+    """ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] -> bf16 [B, 2Hs, 2Ws, C] (dw_ln_launch, head11.py:60-67).
+    pre_act=True: g already is bf16(gelu(conv + bias)) (fused into the GEMM epilogue), bias may be None."""
     C = g.shape[1] // 4
-    if g.dtype != torch.bfloat16 or not g.is_contiguous() or g.shape[0] != B * Hs * Ws or dww.shape != (9, C):
+    _need_cuda(g, dww, lnw, lnb)
+    if g.dtype != torch.bfloat16 or not g.is_contiguous() or g.shape[0] != B * Hs * Ws or dww.shape != (9, C) or (bias is None and not pre_act):
         raise KfError("dw_ln: g must be contiguous bf16 [B*Hs*Ws, 4C] and dww fp32 [9, C]")
     out = torch.empty(B, 2 * Hs, 2 * Ws, C, dtype=torch.bfloat16, device=g.device)
-    _run("dw_ln", lambda: _lib.lib().kf_dw_ln(g.data_ptr(), bias.data_ptr(), dww.data_ptr(), lnw.data_ptr(), lnb.data_ptr(), out.data_ptr(), B, Hs, Ws, C,
-                                              float(eps), _stream()))
+    _run("dw_ln", lambda: _lib.lib().kf_dw_ln(g.data_ptr(), _ptr(bias), dww.data_ptr(), lnw.data_ptr(), lnb.data_ptr(), out.data_ptr(), B, Hs, Ws, C,
+                                              float(eps), 1 if pre_act else 0, _stream()))
     return out
 
 

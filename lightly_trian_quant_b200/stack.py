@@ -193,7 +193,7 @@ class Head:
             # ConvTranspose2d weight [Cin, Cout, 2, 2] -> GEMM weight [(dy, dx, Cout), Cin]
             wr = c1.weight.detach().permute(2, 3, 1, 0).reshape(4 * C, C).to(BF)
             self.stages.append(dict(
-                W=ops.QWeight(wr.float() if fmt != "bf16" else wr, fmt), bias=c1.bias.detach().to(BF).float().contiguous(),
+                W=ops.QWeight(wr.float() if fmt != "bf16" else wr, fmt), bias4=c1.bias.detach().to(BF).float().repeat(4).contiguous(),
                 dww=c2.weight.detach().reshape(C, 9).t().to(BF).float().contiguous(), g=f(nrm.weight), b=f(nrm.bias), eps=nrm.eps,
                 ts=_site_ts(fmt, dev)))
 
@@ -205,14 +205,14 @@ class Head:
         z = xb
         for st in self.stages:
             if self.fmt == "bf16":
-                g = ops.gemm_plain(z, st["W"], tag="head")
+                g = ops.gemm_plain(z, st["W"], st["bias4"], gelu=True, pre_round=True, tag="head")
             else:
                 if self.calib.on and self.fmt == "nv4":
                     set_ts(st["ts"], z)
                 a = _with_ts(ops.act_buf(z.shape[0], C, self.fmt, z.device, 2), st["ts"])
                 ops.quant_rows(z, a)
-                g = ops.gemm_plain(a, st["W"], tag="head")
-            u = ops.dw_ln(g, st["bias"], st["dww"], st["g"], st["b"], B, Hs, Ws, st["eps"])
+                g = ops.gemm_plain(a, st["W"], st["bias4"], gelu=True, pre_round=True, tag="head")
+            u = ops.dw_ln(g, None, st["dww"], st["g"], st["b"], B, Hs, Ws, st["eps"], pre_act=True)
             z = u.view(B * 4 * Hs * Ws, C)
             Hs, Ws = 2 * Hs, 2 * Ws
         h = qb
