@@ -236,6 +236,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int n0 = n_blk * BN + hc * 64;
         const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
         const int nbatch = g.M / g.Ntok;
+        const int b0 = rbase / g.Ntok, t0 = rbase - b0 * g.Ntok;   // one division per tile; rows advance from here
         const float4 b_lo = g.bias ? ldg4(g.bias + n0 + c4) : z4, b_hi = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
         if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
         tc_fence_after();
@@ -261,7 +262,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int i = 0; i < 8; ++i) {
           const int m = rbase + 4 * i + rsub;
           if (m < g.M) {
-            const int b = m / g.Ntok, t = m - b * g.Ntok;
+            int b = b0, t = t0 + 4 * i + rsub;
+            while (t >= g.Ntok) {
+              t -= g.Ntok;
+              ++b;
+            }
             float4 o = part ? hi[i] : lo[i];
             if (which < 2 && t >= g.prefix) {
               const size_t off = (size_t)(t - g.prefix) * 64 + part * 32 + c4;
