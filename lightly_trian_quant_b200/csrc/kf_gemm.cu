@@ -286,7 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
 
       const int n = n_blk * BN + wq * 32 + c4;                   // this lane's first column
-      const float4 b4 = g.bias ? ldg4(g.bias + n) : z4;
+      const float4 b4 = (g.bias && EPI != KF_EPI_QUANT) ? ldg4(g.bias + n) : z4;
       float4 rr[8];
       float4 g4 = z4;
       if (EPI == KF_EPI_RES) {                                    // residual loads go out before the accumulator wait
@@ -304,8 +304,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[as]);                   // accumulator is in registers: hand TMEM back
-      stg_put(stg, lane, r);
-      __syncwarp();
+      if (EPI != KF_EPI_QUANT) {
+        stg_put(stg, lane, r);
+        __syncwarp();
+      }
 
       if (EPI == KF_EPI_PLAIN) {
         const int esz = g.out_dtype == KF_F32 ? 4 : 2;
@@ -338,42 +340,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
         }
       } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
+        // Row layout (no restaging): the thread owns 32 consecutive columns of row rbase + lane = two nv4 blocks or one
+        // mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values;
+        // the outputs are 4-8x smaller than fp32, so their 16-byte per-row stores cost little.
         const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
         const bool rb = g.flags & KF_Q_ROUND_BF16;
-        float tso = 1.f;
-        if (g.out_fmt == KF_FMT_NV4) tso = __ldg(g.tso);
+        const int m = rbase + lane;
+        const bool ok = m < g.M;
+        const int n0 = n_blk * BN + wq * 32;
+        float v[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = rbase + 4 * i + rsub;
-          const bool ok = m < g.M;
-          const float4 a = fma4(stg_get(stg, lane, i), ts, b4);
-          float v[4] = {gelu_erf(a.x), gelu_erf(a.y), gelu_erf(a.z), gelu_erf(a.w)};
-          if (rb) {
+        for (int q4 = 0; q4 < 8; ++q4) {
+          const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : z4;
+          v[4 * q4] = gelu_erf(fmaf(__uint_as_float(r[4 * q4]), ts, bb.x));
+          v[4 * q4 + 1] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 1]), ts, bb.y));
+          v[4 * q4 + 2] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 2]), ts, bb.z));
+          v[4 * q4 + 3] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 3]), ts, bb.w));
+        }
+        if (rb) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) v[k] = bf16_round(v[k]);
+          for (int k = 0; k < 32; ++k) v[k] = bf16_round(v[k]);
+        }
+        float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          am0 = fmaxf(am0, fabsf(v[k]));
+          am1 = fmaxf(am1, fabsf(v[16 + k]));
+        }
+        const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
+        const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
+        int by0, by1;
+        if (g.out_fmt == KF_FMT_NV4) {
+          uint32_t o[4];
+          quant_nv4<16>(va, am0, __ldg(g.tso), div_true, o, by0);
+          quant_nv4<16>(vb, am1, __ldg(g.tso), div_true, o + 2, by1);
+          if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+          // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
+          *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n_blk * 8 + wq * 2, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
+        } else if (g.out_fmt == KF_FMT_MX8) {
+          uint32_t o[8];
+          const float am = fmaxf(am0, am1);
+          quant_mx8<16>(va, am, div_true, o, by0);
+          quant_mx8<16>(vb, am, div_true, o + 4, by0);
+          if (ok) {
+            uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
+            p[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            p[1] = make_uint4(o[4], o[5], o[6], o[7]);
           }
-          float am = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-          am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-          am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));          // 16 columns: one nv4 block
-          int byte;
-          uint32_t o[1];
-          if (g.out_fmt == KF_FMT_NV4) {
-            quant_nv4<4>(v, am, tso, div_true, o, byte);
-            if (ok) *reinterpret_cast<uint16_t*>(g.Qo + (size_t)m * (g.N >> 1) + (n >> 1)) = (uint16_t)o[0];
-            const uint32_t b_hi = __shfl_down_sync(0xffffffffu, (uint32_t)byte, 4);        // the block of columns 16..31
-            if ((lane & 7) == 0)      // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
-              *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n_blk * 8 + wq * 2, g.N >> 6)) = ok ? (uint16_t)(byte | (b_hi << 8)) : (uint16_t)0;
-          } else {
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));        // 32 columns: one mx block
-            if (g.out_fmt == KF_FMT_MX8) {
-              quant_mx8<4>(v, am, div_true, o, byte);
-              if (ok) *reinterpret_cast<uint32_t*>(g.Qo + (size_t)m * g.N + n) = o[0];
-            } else {
-              quant_mx4<4>(v, am, div_true, o, byte);
-              if (ok) *reinterpret_cast<uint16_t*>(g.Qo + (size_t)m * (g.N >> 1) + (n >> 1)) = (uint16_t)o[0];
-            }
-            if ((lane & 7) == 0) g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)byte : (uint8_t)0;
-          }
+          g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
+        } else {
+          uint32_t o[4];
+          const float am = fmaxf(am0, am1);
+          quant_mx4<16>(va, am, div_true, o, by0);
+          quant_mx4<16>(vb, am, div_true, o + 2, by0);
+          if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+          g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
         }
       }
       __syncwarp();                                               // staging tile is reused by the next tile
