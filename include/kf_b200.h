@@ -170,9 +170,12 @@ KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H,
 
 /* Tensor-core instruction-rate probe: every SM issues `iters` x 4 tcgen05.mma (M=128, N=n, 32 K-bytes each) of the
  * given operand format on shared-memory-resident operands; *flops_per_launch receives the FLOPs one launch performs.
+ * sf_copies (0..8) scale-factor atoms are re-copied smem -> TMEM (tcgen05.cp) before every group of 4 MMAs, as a real
+ * block-scaled main loop must (mx8: 2, mx4: 4, nv4: 8 at a 128 x 128 tile); 0 copies them once; 8 + c issues the c copies
+ * per stage from a second warp with no ordering against the MMA stream (do the two overlap in the hardware?).
  * The caller times the launch to obtain the FP8 / FP4 / bf16 instruction-rate ceiling of the part.
  * Counterpart: the mma.sync probe infer-opt/round10_lowp_probe/peak_extra.cu. */
-KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, double* flops_per_launch, void* stream);
+KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream);
 
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.

@@ -5,7 +5,8 @@
 //              the 128x4 blocked layout, one 512-byte atom per 128 rows x 4 k-blocks
 //   tile       128 x 128 output tile per CTA step, 128 bytes of K per pipeline stage (one TMA swizzle atom per row)
 //   pipeline   warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy), warp 1 = MMA issuer
-//              (tcgen05.cp scale atoms smem -> TMEM, 4 MMAs of 32 K-bytes per stage), warps 2..17 = epilogue: the
+//              (4 MMAs of 32 K-bytes per stage), warp 18 = scale-factor copier (tcgen05.cp atoms smem -> TMEM,
+//              overlapping the MMAs), warps 2..17 = epilogue: the
 //              fused epilogues are bound by CUDA-core issue and memory latency, not by TMEM bandwidth, so 16 warps
 //              each take one (32-row TMEM quarter, 32-column chunk) piece of the tile: tcgen05.ld one accumulator row
 //              per thread, hand TMEM back at once, restage through warp-private swizzled shared memory so every
@@ -32,7 +33,9 @@ constexpr int TILE_BYTES = (BM + BN) * BKB;            // 32 KB of operands per 
 constexpr int SF_STAGE_BYTES = 4096;                   // up to 4 atoms for A and 4 for W per stage
 constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
 constexpr int EPI_WARPS = 16;
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int SF_WARP = 2 + EPI_WARPS;                 // warp index of the scale-factor copier
+constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);
+constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 32 columns each (A at +0, W at +16)
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;                       // accumulators: columns [0,256); scale factors from 256
 constexpr size_t GEMM_SMEM = 1024 + (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
@@ -110,7 +113,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* stg_all = sfs + (size_t)STAGES * SF_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + EPI_WARPS * STG_WARP_BYTES);
   uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t *sf_full = bars + 2 * STAGES + 4, *sf_empty = sf_full + SF_BUFS;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,6 +122,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < SF_BUFS; ++b) {
+      mbar_init(&sf_full[b], 1);
+      mbar_init(&sf_empty[b], 1);
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
@@ -169,7 +177,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                  : KIND == KIND_MX8 ? idesc_bs(0, 1, BN)
                                  : KIND == KIND_NV4 ? idesc_bs(1, 0, BN)
                                                     : idesc_bs(1, 1, BN);
-      uint32_t s = 0, ph = 0, lt = 0;
+      uint32_t s = 0, ph = 0, lt = 0, sb = 0, sph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
         const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
@@ -181,14 +189,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * TILE_BYTES);
           const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + BM * BKB);
-          const uint32_t sf_t = tmem_base + TMEM_SF_COL + (kt & 1) * 32;     // scale factors of A, then of W at +16
-          if (SCALED) {
-            const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
-#pragma unroll
-            for (int a = 0; a < ATOMS; ++a) {
-              tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
-              tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + 2048 + a * 512));
-            }
+          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * 32;           // scale factors of A, then of W at +16
+          if (SCALED) {                          // copied into TMEM by the scale-copy warp, which runs ahead of the MMAs
+            if (!mbar_wait(&sf_full[sb], sph, ctx, 5)) { ok = false; break; }
+            tc_fence_after();
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {                                       // 32 K-bytes per MMA
@@ -205,9 +209,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
           tc_commit(&empty[s]);
+          if (SCALED) {
+            tc_commit(&sf_empty[sb]);
+            if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
+          }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) tc_commit(&tfull[as]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == SF_WARP) {
+    // ------------------------------------------------------------------ scale-factor copier
+    // tcgen05.cp of one 512-byte atom costs about as much tensor-pipe time as an MMA, but it overlaps with the MMAs
+    // when it is issued from another warp; issued from the MMA thread the two serialise.  This warp therefore moves
+    // the atoms of stage s (shared memory -> one of SF_BUFS TMEM buffers) as soon as the TMA has landed them and hands
+    // the buffer to the MMA warp through an mbarrier.
+    if (SCALED && lane == 0) {
+      uint32_t s = 0, ph = 0, sb = 0, sph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int kt = 0; kt < g.k_tiles; ++kt) {
+          if (!mbar_wait(&sf_empty[sb], sph ^ 1, ctx, 6)) { ok = false; break; }
+          if (!mbar_wait(&full[s], ph, ctx, 7)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * 32;
+          const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a) {
+            tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
+            tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + 2048 + a * 512));
+          }
+          tc_commit(&sf_full[sb]);
+          if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
       }
     }
     __syncwarp();

@@ -10,7 +10,7 @@ namespace kf {
 constexpr int PK_SMEM = 1024 + 16384 + 32768 + 4096 + 64;
 
 template <int KIND, int N>
-__global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* err) {
+__global__ void __launch_bounds__(128, 1) peak_kernel(int iters, int sf_copies, unsigned int* err) {
   extern __shared__ uint8_t raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
   uint8_t *a = smem, *b = smem + 16384, *sf = smem + 16384 + 32768;
@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* e
   for (int i = threadIdx.x; i < (16384 + 32768 + 4096) / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
     mbar_init(bar, 1);
+    mbar_init(bar + 2, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -42,6 +43,10 @@ __global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* e
     }
     for (int it = 0; it < iters; ++it) {
       const uint32_t d = tmem + ((N <= 128) ? (it & 1) * N : 0);
+      if (KIND != KF_FMT_BF16) {           // optionally re-copy scale atoms every stage, as a real main loop must
+        for (int c = 0; c < (sf_copies <= 8 ? sf_copies : 0); ++c)
+          tc_cp_sf(sft + 32 * (it & 1) + 4 * (c & 7), smem_desc_sf(smem_u32(sf) + (c & 7) * 512));
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (KIND == KF_FMT_BF16) mma_f16(d, ad + 2 * j, bd + 2 * j, IDESC, 1);
@@ -52,6 +57,14 @@ __global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* e
     }
     tc_commit(bar);
     mbar_wait(bar, 0, ctx, 50);
+  } else if (threadIdx.x == 32 && sf_copies > 8 && KIND != KF_FMT_BF16) {
+    // sf_copies = 8 + c: the c copies per stage are issued by a second warp into a scratch TMEM region, with no
+    // ordering against the MMA stream: shows whether tcgen05.cp and tcgen05.mma overlap in the hardware
+    const uint32_t scratch = tmem + 256 + (N > 128 ? 128 : 0) + 64;
+    for (int it = 0; it < iters; ++it)
+      for (int c = 0; c < sf_copies - 8; ++c) tc_cp_sf(scratch + 4 * (c & 7), smem_desc_sf(smem_u32(sf) + (c & 7) * 512));
+    tc_commit(bar + 2);
+    mbar_wait(bar + 2, 0, ctx, 51);
   }
   tc_fence_before();
   __syncthreads();
@@ -62,11 +75,11 @@ __global__ void __launch_bounds__(128, 1) peak_kernel(int iters, unsigned int* e
 }
 
 template <int KIND>
-static int launch_peak(int n, int iters, int sms, unsigned int* err, cudaStream_t st) {
+static int launch_peak(int n, int iters, int sf_copies, int sms, unsigned int* err, cudaStream_t st) {
   auto go = [&](auto kern) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(peak_kernel)");
-    kern<<<sms, 128, PK_SMEM, st>>>(iters, err);
+    kern<<<sms, 128, PK_SMEM, st>>>(iters, sf_copies, err);
     return cuda_status(cudaGetLastError(), "kf_tensor_peak_probe launch");
   };
   return n == 256 ? go(peak_kernel<KIND, 256>) : go(peak_kernel<KIND, 128>);
@@ -76,10 +89,11 @@ static int launch_peak(int n, int iters, int sms, unsigned int* err, cudaStream_
 
 using namespace kf;
 
-extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, double* flops_per_launch, void* stream) {
+extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream) {
   KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_tensor_peak_probe: unknown format %d", fmt);
   KF_REQUIRE(n == 128 || n == 256, "kf_tensor_peak_probe: n must be 128 or 256");
   KF_REQUIRE(iters > 0 && iters <= (1 << 22), "kf_tensor_peak_probe: iters out of range");
+  KF_REQUIRE(sf_copies >= 0 && sf_copies <= 16, "kf_tensor_peak_probe: sf_copies must be 0..16");
   int sms = 0;
   int st = device_sm_count(&sms);
   if (st != KF_OK) return st;
@@ -89,9 +103,9 @@ extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, double* flops_per
   if (flops_per_launch) *flops_per_launch = 2.0 * 128.0 * n * k_per_mma * 4.0 * iters * sms;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   switch (fmt) {
-    case KF_FMT_MX8: return launch_peak<KF_FMT_MX8>(n, iters, sms, err, cs);
-    case KF_FMT_NV4: return launch_peak<KF_FMT_NV4>(n, iters, sms, err, cs);
-    case KF_FMT_MX4: return launch_peak<KF_FMT_MX4>(n, iters, sms, err, cs);
-    default: return launch_peak<KF_FMT_BF16>(n, iters, sms, err, cs);
+    case KF_FMT_MX8: return launch_peak<KF_FMT_MX8>(n, iters, sf_copies, sms, err, cs);
+    case KF_FMT_NV4: return launch_peak<KF_FMT_NV4>(n, iters, sf_copies, sms, err, cs);
+    case KF_FMT_MX4: return launch_peak<KF_FMT_MX4>(n, iters, sf_copies, sms, err, cs);
+    default: return launch_peak<KF_FMT_BF16>(n, iters, sf_copies, sms, err, cs);
   }
 }

@@ -118,8 +118,12 @@ def bench_quant_rows(args):
 
 
 def bench_peak(args):
-    return {"kernel": f"tcgen05 instruction-rate probe {args.fmt}", "TFLOP/s_n128": ops.tensor_peak_tflops(args.fmt, 128),
-            "TFLOP/s_n256": ops.tensor_peak_tflops(args.fmt, 256)}
+    out = {"kernel": f"tcgen05 instruction-rate probe {args.fmt}", "TFLOP/s_n128": ops.tensor_peak_tflops(args.fmt, 128),
+           "TFLOP/s_n256": ops.tensor_peak_tflops(args.fmt, 256)}
+    if args.fmt != "bf16":
+        for c in (1, 2, 4, 8, 10, 12, 16):
+            out[f"TFLOP/s_n128_sfcopies{c}"] = ops.tensor_peak_tflops(args.fmt, 128, sf_copies=c)
+    return out
 
 
 def main():

@@ -389,7 +389,7 @@ def resize_norm(frames: torch.Tensor, size: int, mean=IMAGENET_MEAN, std=IMAGENE
     return out
 
 
-def tensor_peak_tflops(fmt: str, n: int = 256, iters: int = 4096, reps: int = 5) -> float:
+def tensor_peak_tflops(fmt: str, n: int = 256, iters: int = 4096, reps: int = 5, sf_copies: int = 0) -> float:
     """measured tcgen05 instruction-rate ceiling (TFLOP/s) for operand format fmt at M=128, N=n (best of reps)."""
     import ctypes as C
 
@@ -399,7 +399,7 @@ def tensor_peak_tflops(fmt: str, n: int = 256, iters: int = 4096, reps: int = 5)
     for _ in range(reps + 1):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        check(L.kf_tensor_peak_probe(KF_FMT[fmt], n, iters, C.byref(fl), _stream()), "kf_tensor_peak_probe")
+        check(L.kf_tensor_peak_probe(KF_FMT[fmt], n, iters, sf_copies, C.byref(fl), _stream()), "kf_tensor_peak_probe")
         e1.record()
         e1.synchronize()
         best = max(best, fl.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
