@@ -177,6 +177,15 @@ KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H,
  * Counterpart: the mma.sync probe infer-opt/round10_lowp_probe/peak_extra.cu. */
 KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream);
 
+/* The same attention forward with the quantisation of its output fused into the epilogue: the O row of every head is
+ * rounded to the 16-bit input type and written as codes + blocked scales of the [B*N, H*64] operand the proj GEMM
+ * reads (format out_fmt, nv4 with the static per-tensor scale tso).  Scale rows B*N..pad128(B*N) are not touched.
+ * Replaces attn16_fwd followed by quant_rows / quantx (infer-opt/round13_mxfp8_full/impl/stack13.py:105-106,
+ * infer-opt/round14_fp4_full/impl/stack14b.py:104-110); the reference lists this fusion as estimated but not built
+ * (infer-opt/round14_fp4_full/NOTES.md:142-143). */
+KF_API int kf_attn_fwd_quant(int dtype, const void* qkv, int B, int N, int H, float pre, int out_fmt, void* Qo, void* SFo,
+                             const float* tso, int flags, void* stream);
+
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
  * No counterpart in the reference (its mbarrier waits spin without a bound: infer-opt/round12_lowp_stack/impl/attn16o.cu:77-79). */

@@ -32,6 +32,10 @@ struct AttnArgs {
   int f16;          // 0 = bf16, 1 = f16
   float scale_log2; // softmax scale * log2(e)
   unsigned int* err;
+  // optional fused quantisation of the output (the proj GEMM's A operand): out_fmt < 0 = off
+  int out_fmt, flags;
+  uint8_t *Qo, *SFo;
+  const float* tso;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -245,7 +249,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld32(t_lane + AT_COL_O, r0);
       tmem_ld32(t_lane + AT_COL_O + 32, r1);
       tmem_ld_wait();
-      if (n < a.N) {
+      if (n < a.N && a.out_fmt >= 0) {
+        // O row of this head (64 values) -> rounded to the 16-bit type -> 4 nv4 blocks or 2 mx blocks, written as the
+        // codes and scale bytes of row b*N + n, columns h*64.. of the [B*N, H*64] operand
+        const float inv = 1.0f / l_run;
+        const bool div_true = !(a.flags & KF_Q_RECIP_DIV);
+        float v[64];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = __uint_as_float(r0[i]) * inv;
+          v[32 + i] = __uint_as_float(r1[i]) * inv;
+        }
+#pragma unroll
+        for (int i = 0; i < 64; ++i) v[i] = a.f16 ? __half2float(__float2half_rn(v[i])) : bf16_round(v[i]);
+        const size_t m = (size_t)b * a.N + n;
+        const int d = a.H * AT_D;
+        if (a.out_fmt == KF_FMT_NV4) {
+          const float tso = __ldg(a.tso);
+          uint32_t o[8], word = 0;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float(&blk)[16] = *reinterpret_cast<const float(*)[16]>(&v[16 * k]);
+            float am = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(blk[i]));
+            int by;
+            quant_nv4<16>(blk, am, tso, div_true, o + 2 * k, by);
+            word |= (uint32_t)by << (8 * k);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(a.Qo + m * (d >> 1) + h * 32);
+          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          *reinterpret_cast<uint32_t*>(a.SFo + sf_offset((int)m, h * 4, d >> 6)) = word;
+        } else {
+          uint32_t half = 0;
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[32 * k]);
+            const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[32 * k + 16]);
+            float am = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(v[32 * k + i]));
+            int by;
+            if (a.out_fmt == KF_FMT_MX8) {
+              uint32_t o[8];
+              quant_mx8<16>(va, am, div_true, o, by);
+              quant_mx8<16>(vb, am, div_true, o + 4, by);
+              uint4* dst = reinterpret_cast<uint4*>(a.Qo + m * d + h * 64 + k * 32);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            } else {
+              uint32_t o[4];
+              quant_mx4<16>(va, am, div_true, o, by);
+              quant_mx4<16>(vb, am, div_true, o + 2, by);
+              *reinterpret_cast<uint4*>(a.Qo + m * (d >> 1) + h * 32 + k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            half |= (uint32_t)by << (8 * k);
+          }
+          *reinterpret_cast<uint16_t*>(a.SFo + sf_offset((int)m, h * 2, d >> 7)) = (uint16_t)half;
+        }
+      } else if (n < a.N) {
         const float inv = 1.0f / l_run;
         uint32_t w[32];
 #pragma unroll
@@ -301,13 +364,21 @@ static int make_tmap_qkv(CUtensorMap* map, const void* base, int B, int N, int H
 
 using namespace kf;
 
-extern "C" int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream) {
-  (void)pre;
+static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H, int out_fmt, void* Qo, void* SFo, const float* tso, int flags,
+                       void* stream) {
   KF_REQUIRE(dtype == KF_BF16 || dtype == KF_F16, "kf_attn_fwd: dtype must be bf16 or f16");
   KF_REQUIRE(B >= 0 && N > 0 && H > 0, "kf_attn_fwd: bad shape B=%d N=%d H=%d", B, N, H);
   if (B == 0) return KF_OK;
-  KF_REQUIRE(qkv && O && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(O) & 15) == 0,
-             "kf_attn_fwd: qkv and O must be non-null and 16-byte aligned");
+  KF_REQUIRE(qkv && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0, "kf_attn_fwd: qkv must be non-null and 16-byte aligned");
+  if (out_fmt < 0) {
+    KF_REQUIRE(O && (reinterpret_cast<uintptr_t>(O) & 15) == 0, "kf_attn_fwd: O must be non-null and 16-byte aligned");
+  } else {
+    KF_REQUIRE(out_fmt == KF_FMT_MX8 || out_fmt == KF_FMT_NV4 || out_fmt == KF_FMT_MX4, "kf_attn_fwd_quant: bad output format %d", out_fmt);
+    KF_REQUIRE(Qo && SFo && (reinterpret_cast<uintptr_t>(Qo) & 15) == 0 && (reinterpret_cast<uintptr_t>(SFo) & 15) == 0,
+               "kf_attn_fwd_quant: Qo and SFo must be non-null and 16-byte aligned");
+    KF_REQUIRE(out_fmt != KF_FMT_NV4 || tso, "kf_attn_fwd_quant: nv4 needs the per-tensor scale");
+    KF_REQUIRE((H * 64) % 128 == 0, "kf_attn_fwd_quant: H*64 must be a multiple of 128");
+  }
   const size_t plane = (size_t)B * N * H * 64 * 2;
   const uint8_t* base = static_cast<const uint8_t*>(qkv);
   CUtensorMap tq, tk, tv;
@@ -329,8 +400,20 @@ extern "C" int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, in
   a.O = O; a.B = B; a.N = N; a.H = H; a.f16 = dtype == KF_F16;
   a.scale_log2 = 0.125f * 1.4426950408889634f;
   a.err = dev_error_ptr();
+  a.out_fmt = out_fmt; a.flags = flags; a.Qo = static_cast<uint8_t*>(Qo); a.SFo = static_cast<uint8_t*>(SFo); a.tso = tso;
   KF_REQUIRE(a.err != nullptr, "kf_attn_fwd: device error word unavailable");
   const int q_tiles = (N + AT_BM - 1) / AT_BM;
   attn_fwd_kernel<<<B * H * q_tiles, AT_THREADS, AT_SMEM, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, a);
   return cuda_status(cudaGetLastError(), "kf_attn_fwd launch");
+}
+
+extern "C" int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream) {
+  (void)pre;
+  return attn_launch(dtype, qkv, O, B, N, H, -1, nullptr, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int kf_attn_fwd_quant(int dtype, const void* qkv, int B, int N, int H, float pre, int out_fmt, void* Qo, void* SFo, const float* tso, int flags,
+                                 void* stream) {
+  (void)pre;
+  return attn_launch(dtype, qkv, nullptr, B, N, H, out_fmt, Qo, SFo, tso, flags, stream);
 }

@@ -7,6 +7,8 @@
 //   mx8  byte = min(exp(fl32(amax/448)) + (mant != 0), 255);  q = e4m3_rn_sat(clamp(x * 2^(127 - max(byte,1)), +-448))
 //   mx4  byte = min(exp(fl32(amax/6))   + (mant != 0), 254);  q = e2m1_rn_sat(x * 2^(127 - byte))
 //   nv4  sf = e4m3_rn(min((amax/6)/ts, 448));  q = e2m1_rn_sat(x / (float(sf) * ts)), 0 when the scale is 0
+// LN + quant is persistent (warps stride over the rows) with the LayerNorm weight and bias of the lane's columns held
+// in registers, so the only per-row loads are the row itself.
 #include "kf_common.cuh"
 
 namespace kf {
@@ -131,7 +133,21 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
 // ------------------------------------------------------------------------------------------------ LayerNorm (+ quant)
 // One warp per row; lane l holds the 8 consecutive elements [i*256 + l*8, +8) for i < NV (d = NV*256).
 template <int NV>
-__device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float* __restrict__ w, const float* __restrict__ b, float eps,
+__device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, const float* __restrict__ b, int lane, float (&ww)[NV][8], float (&bb)[NV][8]) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const float4* wp = reinterpret_cast<const float4*>(w + i * 256 + lane * 8);
+    const float4* bp = reinterpret_cast<const float4*>(b + i * 256 + lane * 8);
+    const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1), b0 = __ldg(bp), b1 = __ldg(bp + 1);
+    ww[i][0] = w0.x; ww[i][1] = w0.y; ww[i][2] = w0.z; ww[i][3] = w0.w; ww[i][4] = w1.x; ww[i][5] = w1.y; ww[i][6] = w1.z; ww[i][7] = w1.w;
+    bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w; bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
+  }
+}
+
+// LayerNorm of one row with the affine parameters already in registers (the persistent kernels load them once per
+// warp: re-reading them per row doubles the load instructions of a kernel that is otherwise one pass over x).
+template <int NV>
+__device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float (&ww)[NV][8], const float (&bb)[NV][8], float eps,
                                        int lane, bool valid, float (&v)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -165,15 +181,9 @@ __device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   const float rstd = rsqrtf(ss * inv_d + eps);
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const float4* wp = reinterpret_cast<const float4*>(w + i * 256 + lane * 8);
-    const float4* bp = reinterpret_cast<const float4*>(b + i * 256 + lane * 8);
-    float4 w0 = __ldg(wp), w1 = __ldg(wp + 1), b0 = __ldg(bp), b1 = __ldg(bp + 1);
-    float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * ww[j] + bb[j];
-  }
+    for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * ww[i][j] + bb[i][j];
 }
 
 template <int NV, int FMT>
@@ -182,15 +192,17 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
                                                        uint8_t* __restrict__ sf, float* __restrict__ y_dbg) {
   constexpr int D = NV * 256;
   const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= rows_pad) return;
-  const bool valid = row < M;
-  float v[NV][8];
-  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, valid, v);
+  float ww[NV][8], bb[NV][8];
+  ln_affine_load<NV>(w, b, lane, ww, bb);
   float ts = 1.f;
   if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   const bool rb = flags & KF_Q_ROUND_BF16;
+  // persistent: warp w of the grid takes rows w, w + W, w + 2W, ... (rows M..rows_pad only get zero scale words)
+  for (int row = blockIdx.x * 4 + (threadIdx.x >> 5); row < rows_pad; row += gridDim.x * 4) {
+  const bool valid = row < M;
+  float v[NV][8];
+  ln_row<NV>(x + (int64_t)row * D, ww, bb, eps, lane, valid, v);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (rb) {
@@ -231,6 +243,7 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
       *reinterpret_cast<uint32_t*>(sf + sf_offset(row, kb, nkb4)) = word;
     }
   }
+  }
 }
 
 template <int NV, typename TO>
@@ -240,8 +253,9 @@ __global__ void __launch_bounds__(128) ln_rows_kernel(const float* __restrict__ 
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= M) return;
-  float v[NV][8];
-  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, true, v);
+  float v[NV][8], ww[NV][8], bb[NV][8];
+  ln_affine_load<NV>(w, b, lane, ww, bb);
+  ln_row<NV>(x + (int64_t)row * D, ww, bb, eps, lane, true, v);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     uint32_t o[4];
@@ -271,8 +285,9 @@ __global__ void __launch_bounds__(128) ln_tail_kernel(const float* __restrict__ 
   if (row >= M) return;
   const int img = row / Ntok, t = row - img * Ntok;
   if (t >= Q && t < Q + npre) return;
-  float v[NV][8];
-  ln_row<NV>(x + (int64_t)row * D, w, b, eps, lane, true, v);
+  float v[NV][8], ww[NV][8], bb[NV][8];
+  ln_affine_load<NV>(w, b, lane, ww, bb);
+  ln_row<NV>(x + (int64_t)row * D, ww, bb, eps, lane, true, v);
   const int P = Ntok - Q - npre;
   __nv_bfloat16* y = t < Q ? qb + ((int64_t)img * Q + t) * D : xb + ((int64_t)img * P + (t - Q - npre)) * D;
 #pragma unroll
@@ -306,7 +321,10 @@ template <int NV>
 static int launch_ln_quant(int fmt, const float* x, const float* w, const float* b, float eps, int M, const float* ts, int flags, void* q, void* sf,
                            float* y_dbg, cudaStream_t st) {
   int rows_pad = (M + 127) / 128 * 128;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   unsigned grid = (unsigned)((rows_pad + 3) / 4);
+  if (grid > (unsigned)sms * 4) grid = (unsigned)sms * 4;          // persistent: about 4 CTAs of 4 warps per SM
   uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
   if (fmt == KF_FMT_MX8) ln_quant_kernel<NV, KF_FMT_MX8><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
   else if (fmt == KF_FMT_NV4) ln_quant_kernel<NV, KF_FMT_NV4><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);

@@ -85,7 +85,7 @@ class ActBuf:
     def __init__(self, M: int, K: int, fmt: str = "mx8", device="cuda", ts: Optional[torch.Tensor] = None):
         self.M, self.K, self.fmt = M, K, fmt
         self.q = torch.empty(M, code_cols(K, fmt), dtype=torch.uint8, device=device)
-        self.sf = torch.empty(sf_bytes(M, K, fmt), dtype=torch.uint8, device=device)
+        self.sf = torch.zeros(sf_bytes(M, K, fmt), dtype=torch.uint8, device=device)   # padded rows stay zero
         self.ts = ts if ts is not None else (torch.ones(1, dtype=torch.float32, device=device) if fmt == "nv4" else None)
 
 
@@ -300,6 +300,20 @@ def attn_fwd(qkv: torch.Tensor, pre: float = 1.0, out: Optional[torch.Tensor] = 
 
 
 attn16_fwd = attn_fwd
+
+
+def attn_fwd_quant(qkv: torch.Tensor, out: ActBuf, pre: float = 1.0, recip_div: bool = False) -> ActBuf:
+    """attention forward whose output is written directly as the quantised [B*N, H*64] operand `out` (codes + blocked
+    scales; out.ts is the static nv4 scale): attn16_fwd + quant_rows in one kernel."""
+    _need_cuda(qkv, out.q)
+    if qkv.dim() != 5 or qkv.shape[0] != 3 or qkv.shape[4] != 64 or not qkv.is_contiguous() or qkv.dtype not in (torch.bfloat16, torch.float16):
+        raise KfError("attn_fwd_quant: qkv must be contiguous [3, B, N, H, 64] bf16 or f16")
+    _, B, N, H, _ = qkv.shape
+    if (out.M, out.K) != (B * N, H * 64):
+        raise KfError(f"attn_fwd_quant: out must be [{B * N}, {H * 64}], got [{out.M}, {out.K}]")
+    _run("attn_fwd", lambda: _lib.lib().kf_attn_fwd_quant(_DT[qkv.dtype], qkv.data_ptr(), B, N, H, float(pre), KF_FMT[out.fmt], out.q.data_ptr(),
+                                                          out.sf.data_ptr(), _ptr(out.ts), KF_Q_RECIP_DIV if recip_div else 0, _stream()))
+    return out
 
 
 # ------------------------------------------------------------------------------------------------ patch embed / head / pre / post

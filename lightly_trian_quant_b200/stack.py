@@ -16,8 +16,8 @@ Variant grammar  base[+flag...]:   base in b200_mx8 | b200_nv4 | b200_mx4 | b200
     +f16attn   q, k, v and the attention output in fp16 instead of bf16
     +bf16head  keep the two ConvTranspose GEMMs of the head in bf16 instead of the block-scaled format
 
-Kernel sequence per block (8 launches), the decomposition of infer-opt/round14_fp4_full/impl/stack14b.py:85-130:
-    ln_quant | qkv GEMM (+bias +RoPE +[3,B,N,H,64]) | attention | quant_rows | proj GEMM (+bias, gamma, residual) |
+Kernel sequence per block (7 launches), the decomposition of infer-opt/round14_fp4_full/impl/stack14b.py:85-130:
+    ln_quant | qkv GEMM (+bias +RoPE +[3,B,N,H,64]) | attention (+quantise-out) | proj GEMM (+bias, gamma, residual) |
     ln_quant | fc1 GEMM (+bias +GELU +quantise-out) | fc2 GEMM (+bias, gamma, residual)
 NVFP4 activations use static per-tensor scales measured on the first call (headroom 2,
 infer-opt/round14_fp4_full/impl/fp4util.py:41,68-75; stack14b.py:49-52); that call must run eagerly.
@@ -120,12 +120,11 @@ def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, cali
     a = _with_ts(ops.act_buf(M, d, fmt, x.device, 0), L.ts_ln1)
     ops.ln_quant(x, L.ln1_w, L.ln1_b, L.ln1_eps, a, round_bf16=round_bf16)
     qkv = ops.qkv_rope(a, L.qkv, L.bqkv, sin, cos, N, prefix, heads, out_dtype=attn_dtype)
-    o = ops.attn_fwd(qkv).view(M, d)
-    # ---- attention output quant -> proj (gamma + residual, in place on the stream)
+    # ---- attention with its output quantised in the epilogue -> proj (gamma + residual, in place on the stream)
     if cal and nv4:
-        set_ts(L.ts_o, o)
+        set_ts(L.ts_o, ops.attn_fwd(qkv))
     a2 = _with_ts(ops.act_buf(M, d, fmt, x.device, 1), L.ts_o)
-    ops.quant_rows(o, a2)
+    ops.attn_fwd_quant(qkv, a2)
     ops.gemm_res(a2, L.proj, L.bproj, L.g1, x2, out=x2)
     # ---- LN2 + quant -> fc1 (GELU + quantise-out) -> fc2 (gamma + residual)
     if cal and nv4:

@@ -63,3 +63,29 @@ def test_attn_permutation_of_keys_is_neutral():
     o2 = ops.attn_fwd(qkv2.contiguous())
     ops.check_device_error()
     assert go.rel_fro(o2.float().cpu().numpy(), o1.float().cpu().numpy()) < 4e-3
+
+
+@pytest.mark.parametrize("fmt", ["mx8", "nv4", "mx4"])
+def test_attn_fused_quantise_out(fmt):
+    """attention with the output quantisation fused in: bit-exact against the oracle quantiser applied to the bf16
+    output of the unfused kernel (same arithmetic up to the final rounding), scales in the blocked layout."""
+    import numpy as np
+
+    from oracle import quant_oracle as qo
+
+    ops = _ops()
+    B, N, H = 2, 333, 4
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(3, B, N, H, 64, generator=g).to(torch.bfloat16).cuda()
+    o = ops.attn_fwd(qkv).view(B * N, H * 64)
+    on = o.float().cpu().numpy()
+    out = ops.ActBuf(B * N, H * 64, fmt, device="cuda")
+    ts = None
+    if fmt == "nv4":
+        ts = qo.nv4_ts(on) * np.float32(2.0)
+        out.ts.copy_(torch.from_numpy(ts))
+    ops.attn_fwd_quant(qkv, out)
+    ops.check_device_error()
+    eq, es, _ = qo.quantize(on, fmt, ts)
+    assert np.array_equal(out.q.cpu().numpy(), eq)
+    assert np.array_equal(out.sf.cpu().numpy(), qo.to_blocked(es).reshape(-1))
