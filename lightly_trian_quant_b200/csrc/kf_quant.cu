@@ -9,7 +9,7 @@
 //   nv4  sf = e4m3_rn(min((amax/6)/ts, 448));  q = e2m1_rn_sat(x / (float(sf) * ts)), 0 when the scale is 0
 // LN + quant is persistent (warps stride over the rows) with the LayerNorm weight and bias of the lane's columns held
 // in registers, so the only per-row loads are the row itself.
-#include "kf_common.cuh"
+#include "kf_sm100.cuh"
 
 namespace kf {
 
@@ -146,14 +146,21 @@ __device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, cons
 
 // LayerNorm of one row with the affine parameters already in registers (the persistent kernels load them once per
 // warp: re-reading them per row doubles the load instructions of a kernel that is otherwise one pass over x).
-template <int NV>
-__device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float (&ww)[NV][8], const float (&bb)[NV][8], float eps,
+template <int NV, bool FROM_SMEM = false>
+__device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8], const float (&bb)[NV][8], float eps,
                                        int lane, bool valid, float (&v)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (valid) {
       const float4* p = reinterpret_cast<const float4*>(xr + i * 256 + lane * 8);
-      float4 a = __ldg(p), c = __ldg(p + 1);
+      float4 a, c;
+      if (FROM_SMEM) {
+        a = p[0];
+        c = p[1];
+      } else {
+        a = __ldg(p);
+        c = __ldg(p + 1);
+      }
       v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
     } else {
 #pragma unroll
@@ -186,23 +193,58 @@ __device__ __forceinline__ void ln_row(const float* __restrict__ xr, const float
     for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * ww[i][j] + bb[i][j];
 }
 
+// Rows are streamed through shared memory: each warp owns a ring of LNQ_RING row buffers filled by 1-D bulk copies
+// (cp.async.bulk + mbarrier), so two to three rows per warp (8-12 KB) are in flight while the warp normalises and
+// quantises the current one; with 16 warps per SM that keeps well over 100 KB of HBM reads outstanding per SM, which
+// register-staged loads cannot (they stop while the warp computes).
+constexpr int LNQ_RING = 3;
+
 template <int NV, int FMT>
 __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                                        int M, int rows_pad, const float* __restrict__ ts_ptr, int flags, uint8_t* __restrict__ q,
-                                                       uint8_t* __restrict__ sf, float* __restrict__ y_dbg) {
+                                                       uint8_t* __restrict__ sf, float* __restrict__ y_dbg, unsigned int* err) {
   constexpr int D = NV * 256;
-  const int lane = threadIdx.x & 31;
+  extern __shared__ __align__(128) uint8_t lsm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* ring = reinterpret_cast<float*>(lsm) + (size_t)warp * LNQ_RING * D;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(lsm + (size_t)4 * LNQ_RING * D * 4) + warp * LNQ_RING;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(lsm + (size_t)4 * LNQ_RING * D * 4 + 4 * LNQ_RING * 8);
+  if (threadIdx.x == 0) *abort_flag = 0;
+  if (lane == 0) {
+    for (int i = 0; i < LNQ_RING; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const WaitCtx ctx{abort_flag, err};
+  const int W = gridDim.x * 4, gw = blockIdx.x * 4 + warp;
+  auto issue = [&](int k) {                       // lane 0: start the copy of this warp's k-th row into slot k % RING
+    const int r = gw + k * W;
+    if (r < M) {
+      mbar_expect_tx(&bars[k % LNQ_RING], D * 4);
+      bulk_load_1d(ring + (size_t)(k % LNQ_RING) * D, x + (int64_t)r * D, D * 4, &bars[k % LNQ_RING]);
+    }
+  };
+  if (lane == 0)
+    for (int k = 0; k < LNQ_RING; ++k) issue(k);
   float ww[NV][8], bb[NV][8];
   ln_affine_load<NV>(w, b, lane, ww, bb);
   float ts = 1.f;
   if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   const bool rb = flags & KF_Q_ROUND_BF16;
-  // persistent: warp w of the grid takes rows w, w + W, w + 2W, ... (rows M..rows_pad only get zero scale words)
-  for (int row = blockIdx.x * 4 + (threadIdx.x >> 5); row < rows_pad; row += gridDim.x * 4) {
+  // persistent: warp gw of the grid takes rows gw, gw + W, gw + 2W, ... (rows M..rows_pad only get zero scale words)
+  int k = 0;
+  for (int row = gw; row < rows_pad; row += W, ++k) {
   const bool valid = row < M;
+  const int slot = k % LNQ_RING;
+  if (valid && !mbar_wait(&bars[slot], (k / LNQ_RING) & 1, ctx, 30)) break;
   float v[NV][8];
-  ln_row<NV>(x + (int64_t)row * D, ww, bb, eps, lane, valid, v);
+  ln_row<NV, true>(ring + (size_t)slot * D, ww, bb, eps, lane, valid, v);
+  __syncwarp();                                   // every lane has its part of the row: the slot can be refilled
+  if (lane == 0) {
+    fence_proxy_async_smem();
+    issue(k + LNQ_RING);
+  }
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (rb) {
@@ -326,10 +368,18 @@ static int launch_ln_quant(int fmt, const float* x, const float* w, const float*
   unsigned grid = (unsigned)((rows_pad + 3) / 4);
   if (grid > (unsigned)sms * 4) grid = (unsigned)sms * 4;          // persistent: about 4 CTAs of 4 warps per SM
   uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
-  if (fmt == KF_FMT_MX8) ln_quant_kernel<NV, KF_FMT_MX8><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
-  else if (fmt == KF_FMT_NV4) ln_quant_kernel<NV, KF_FMT_NV4><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
-  else ln_quant_kernel<NV, KF_FMT_MX4><<<grid, 128, 0, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg);
-  return cuda_status(cudaGetLastError(), "kf_ln_quant launch");
+  unsigned int* err = dev_error_ptr();
+  KF_REQUIRE(err != nullptr, "kf_ln_quant: device error word unavailable");
+  const size_t smem = (size_t)4 * LNQ_RING * NV * 256 * 4 + 4 * LNQ_RING * 8 + 16;
+  auto go = [&](auto kern) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_quant_kernel)");
+    kern<<<grid, 128, smem, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg, err);
+    return cuda_status(cudaGetLastError(), "kf_ln_quant launch");
+  };
+  if (fmt == KF_FMT_MX8) return go(ln_quant_kernel<NV, KF_FMT_MX8>);
+  if (fmt == KF_FMT_NV4) return go(ln_quant_kernel<NV, KF_FMT_NV4>);
+  return go(ln_quant_kernel<NV, KF_FMT_MX4>);
 }
 
 template <int NV>

@@ -1,5 +1,5 @@
 // Thin inline-PTX layer over the sm_100a primitives the GEMM and attention kernels are built from: mbarriers with
-// bounded waits, TMA tile loads (never multicast), 1-D bulk copies, TMEM allocation, tcgen05.mma / cp / ld / commit,
+// bounded waits, TMA tile loads (single-CTA destination only), 1-D bulk copies, TMEM allocation, tcgen05.mma / cp / ld / commit,
 // and the shared-memory / instruction descriptors of the 5th-generation tensor core.
 #pragma once
 #include <cuda.h>
