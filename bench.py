@@ -165,7 +165,7 @@ def main():
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
-    from lightly_trian_quant_b200 import modeldef, ops, stack
+    from lightly_trian_quant_b200 import modeldef, ops, sharding, stack
 
     cfg = modeldef.VIT_L
     fmt = args.variant.split("+")[0].split("_")[1]
@@ -175,10 +175,11 @@ def main():
     B = args.batch
 
     # this rank's shard of the video: frames rank, rank+world, ...; grouped into micro-batches of B (cyclic)
-    shard = list(range(rank, N_FRAMES, world))
-    n_batches = max(2, (len(shard) + B - 1) // B)
-    video = synth_video(N_FRAMES, dev)[shard]
-    dev_batches = [video[[(j * B + i) % len(shard) for i in range(B)]].contiguous() for j in range(n_batches)]
+    shard = sharding.shard_frames(N_FRAMES, rank, world)
+    batches = sharding.micro_batches(shard, B, min_batches=2)
+    n_batches = len(batches)
+    video = synth_video(N_FRAMES, dev)
+    dev_batches = [video[idx].contiguous() for idx in batches]
     host_batches = [b.cpu().pin_memory() for b in dev_batches]
     del video
 
@@ -230,7 +231,7 @@ def main():
     barrier()
     ms_total = reduce_max(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    fps = world * B * args.steps / (ms_total * 1e-3)
+    fps = sharding.aggregate_fps(B, world, args.steps, ms_total)
 
     # ---------------------------------------------------------------- end to end with host frames (double buffered)
     copy_s = torch.cuda.Stream()
@@ -270,7 +271,7 @@ def main():
     s1.record()
     barrier()
     e2e_ms = reduce_max(s0.elapsed_time(s1))
-    e2e_fps = world * B * args.steps / (e2e_ms * 1e-3)
+    e2e_fps = sharding.aggregate_fps(B, world, args.steps, e2e_ms)
     h2d, d2h = static_in.numel(), static_out.numel()
 
     # ---------------------------------------------------------------- per-kernel-class timing (instrumented eager pass)
