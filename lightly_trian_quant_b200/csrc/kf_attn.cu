@@ -2,29 +2,39 @@
 // dimension 64, no mask, RoPE already applied by the qkv epilogue.
 //
 //   input    qkv [3, B, N, H, 64] bf16 | f16 (the physical layout the qkv GEMM epilogue writes)
-//   output   O [B, N, H*64] bf16 | f16 (the proj GEMM's A operand before quantisation)
-//   CTA      128 query rows of one (batch, head); key tiles of 128; two CTAs share an SM so one CTA's softmax
-//            overlaps the other's MMAs
-//   roles    warps 0..3: softmax (one query row per thread: tcgen05.ld S, running max / sum in fp32, P -> 16-bit ->
-//            swizzled smem, O_tile accumulation with the rescale factor in registers);
-//            warp 4: TMA producer (Q once, K / V double buffered, 4-D tensor maps so rows past N read zero);
-//            warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16;  O_tile = P V: 8 MMAs of K=16, V as the MN-major operand)
-//   numerics softmax scale 1/8 folded into exp2; running max never reset and raised lazily; m, l, O in fp32; P rounded
-//            to the input 16-bit type; every mbarrier wait is bounded.
+//   output   O [B, N, H*64] bf16 | f16, or directly the quantised operand of the proj GEMM (kf_attn_fwd_quant)
+//   CTA      128 query rows of one (batch, head); key tiles of 64; two CTAs per SM
+//   roles    warps 0..3: softmax, one query row per thread (tcgen05.ld of the S row, running max / sum in fp32,
+//            P -> 16 bit -> swizzled smem); warp 4: TMA producer (Q once, K / V in a 3-deep ring, 4-D tensor maps
+//            so rows past N read zero); warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16; O += P V: 4 MMAs of K=16 with
+//            V as the MN-major operand)
+//   pipeline S is double buffered in TMEM and P in shared memory: S(j+1) is computed while the softmax of tile j
+//            runs, so the softmax warps - whose exp2 work on the MUFU unit is the bound of this kernel - never wait
+//            for a tensor-core round trip.  O accumulates in TMEM over all key tiles; the running maximum is raised
+//            only when a tile maximum exceeds it by more than 2^8 in the exponent domain, so the rescale of O (TMEM
+//            load, multiply, store) happens on the first tiles and then almost never.
+//   numerics softmax scale 1/8 folded into exp2 (fp32, one MUFU operation per element; the packed f16x2 exp2 was
+//            measured slower); m, l, O in fp32; P rounded to the input 16-bit type.  Every mbarrier wait is bounded.
 //
 // Replaces a16::fwd_kernel / attn16_fwd (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404; mma.sync m16n8k16 +
 // TMA on sm_120).  The power-of-two Q pre-scale `pre` of the reference protects its fp16 accumulators
 // (attn16o.cu:184-194); with fp32 accumulation it is mathematically neutral and is accepted but not applied.
+#include <type_traits>
+
 #include "kf_sm100.cuh"
 
 namespace kf {
 
-constexpr int AT_BM = 128, AT_BN = 128, AT_D = 64;
+constexpr int AT_BM = 128, AT_BN = 64, AT_D = 64;
 constexpr int AT_THREADS = 192;
-constexpr int AT_TILE = AT_BM * AT_D * 2;             // 16 KB: one [128 x 64] 16-bit tile
-constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_TILE, AT_OFF_V = 3 * AT_TILE, AT_OFF_P = 5 * AT_TILE, AT_OFF_BAR = 7 * AT_TILE;
+constexpr int AT_KV = 3;                               // K / V ring depth
+constexpr int AT_QTILE = AT_BM * AT_D * 2;             // 16 KB
+constexpr int AT_KTILE = AT_BN * AT_D * 2;             // 8 KB
+constexpr int AT_PTILE = AT_BM * AT_BN * 2;            // 16 KB: 128 rows x 64 keys, one 128-byte swizzle atom per row
+constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_P = AT_OFF_V + AT_KV * AT_KTILE,
+              AT_OFF_BAR = AT_OFF_P + 2 * AT_PTILE;
 constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
-constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128;
+constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128;   // S buffers at columns 0 and 64
 
 struct AttnArgs {
   void* O;
@@ -43,7 +53,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
 __device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
   if (f16) {
     __half2 h = __floats2half2_rn(a, b);
@@ -58,8 +67,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const AttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AT_OFF_BAR);
-  uint64_t *q_full = bars, *k_full = bars + 1, *v_full = bars + 3, *kv_empty = bars + 5, *s_full = bars + 7, *p_full = bars + 8, *o_full = bars + 9;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t *q_full = bars, *k_full = bars + 1, *v_full = k_full + AT_KV, *kv_empty = v_full + AT_KV, *s_full = kv_empty + AT_KV, *p_full = s_full + 2,
+           *o_full = p_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -71,13 +81,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < AT_KV; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+    }
     mbar_init(o_full, 1);
     *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;   // the swizzled tiles need a 1024-byte aligned base
     fence_mbar_init();
@@ -105,15 +117,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
-      mbar_expect_tx(q_full, AT_TILE);
+      mbar_expect_tx(q_full, AT_QTILE);
       tma_load_4d(smem + AT_OFF_Q, &tmQ, 0, h, qt * AT_BM, b, q_full);
       for (int j = 0; j < n_kt; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, ctx, 11)) break;
-        mbar_expect_tx(&k_full[st], AT_TILE);
-        tma_load_4d(smem + AT_OFF_K + st * AT_TILE, &tmK, 0, h, j * AT_BN, b, &k_full[st]);
-        mbar_expect_tx(&v_full[st], AT_TILE);
-        tma_load_4d(smem + AT_OFF_V + st * AT_TILE, &tmV, 0, h, j * AT_BN, b, &v_full[st]);
+        const int st = j % AT_KV;
+        if (!mbar_wait(&kv_empty[st], ((j / AT_KV) & 1) ^ 1, ctx, 11)) break;
+        mbar_expect_tx(&k_full[st], AT_KTILE);
+        tma_load_4d(smem + AT_OFF_K + st * AT_KTILE, &tmK, 0, h, j * AT_BN, b, &k_full[st]);
+        mbar_expect_tx(&v_full[st], AT_KTILE);
+        tma_load_4d(smem + AT_OFF_V + st * AT_KTILE, &tmV, 0, h, j * AT_BN, b, &v_full[st]);
       }
     }
     __syncwarp();
@@ -124,77 +136,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_s = idesc_f16(fmt, AT_BN);
       const uint32_t idesc_o = idesc_f16(fmt, AT_D) | (1u << 16);          // B (= V) is MN-major
       const uint64_t qdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_Q));
-      const uint64_t pdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_P));
-      const uint32_t t_s = tmem_base + AT_COL_S, t_o = tmem_base + AT_COL_O;
-      bool ok = mbar_wait(q_full, 0, ctx, 12);
-      if (ok) ok = mbar_wait(&k_full[0], 0, ctx, 13);
-      if (ok) {
-        tc_fence_after();
-        const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K));
+      const uint32_t t_o = tmem_base + AT_COL_O;
+      auto issue_s = [&](int t) {                                         // S(t) = Q K(t)^T into S buffer t & 1
+        const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + (t % AT_KV) * AT_KTILE));
+        const uint32_t t_s = tmem_base + AT_COL_S + (t & 1) * AT_BN;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
-        tc_commit(s_full);
+        tc_commit(&s_full[t & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0, ctx, 12);
+      for (int t = 0; t < 2 && t < n_kt && ok; ++t) {
+        ok = mbar_wait(&k_full[t % AT_KV], (t / AT_KV) & 1, ctx, 13);
+        if (ok) {
+          tc_fence_after();
+          issue_s(t);
+        }
       }
       for (int j = 0; j < n_kt && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(p_full, j & 1, ctx, 14)) break;
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, ctx, 15)) break;
+        const int st = j % AT_KV;
+        if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, ctx, 14)) break;
+        if (!mbar_wait(&v_full[st], (j / AT_KV) & 1, ctx, 15)) break;
         tc_fence_after();
-        const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_TILE));
+        const uint64_t pdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_P + (j & 1) * AT_PTILE));
+        const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_KTILE));
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // A: 16 keys = 32 bytes inside key atom kk/4 of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
-          const uint64_t ad = pdesc + (uint64_t)((kk >> 2) * (AT_TILE >> 4) + (kk & 3) * 2);
-          const uint64_t bd = vdesc + (uint64_t)(kk * (2048 >> 4));
-          mma_f16(t_o, ad, bd, idesc_o, (j | kk) != 0);      // O accumulates in TMEM over all key tiles
-        }
+        for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 32 bytes of the P row; B: 16 key rows of V = two 8-row groups of 1024 bytes
+          mma_f16(t_o, pdesc + 2 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | kk) != 0);
         tc_commit(o_full);
         tc_commit(&kv_empty[st]);
-        if (j + 1 < n_kt) {
-          const int sn = (j + 1) & 1;
-          if (!mbar_wait(&k_full[sn], ((j + 1) >> 1) & 1, ctx, 16)) break;
+        if (j + 2 < n_kt) {                  // the softmax of tile j has consumed S buffer j & 1 (it arrived on p_full): refill it
+          const int t = j + 2;
+          if (!mbar_wait(&k_full[t % AT_KV], (t / AT_KV) & 1, ctx, 16)) break;
           tc_fence_after();
-          const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + sn * AT_TILE));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
-          tc_commit(s_full);
+          issue_s(t);
         }
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax: thread = query row
-    // O accumulates in TMEM across key tiles.  The running maximum is only raised when the tile maximum exceeds it
-    // by more than 8 in the exponent domain (P then stays <= 2^8, harmless in bf16 / fp32), so the rescale of O
-    // (TMEM load, multiply, store) happens on the first tiles and then almost never.
     const int row = warp * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float sc = a.scale_log2;
     const float thr = 8.0f / sc;
     float m_run = -INFINITY, l_run = 0.f;
-    uint8_t* prow = smem + AT_OFF_P + row * 128;
     const int sw = row & 7;
     bool ok = true;
     for (int j = 0; j < n_kt; ++j) {
-      if (!mbar_wait(s_full, j & 1, ctx, 17)) { ok = false; break; }
+      const int sb = j & 1;
+      if (!mbar_wait(&s_full[sb], (j >> 1) & 1, ctx, 17)) { ok = false; break; }
       tc_fence_after();
       const int kbase = j * AT_BN;
-      uint32_t r[4][32];
-      tmem_ld32(t_lane + AT_COL_S, r[0]);
-      tmem_ld32(t_lane + AT_COL_S + 32, r[1]);
-      tmem_ld32(t_lane + AT_COL_S + 64, r[2]);
-      tmem_ld32(t_lane + AT_COL_S + 96, r[3]);
+      uint32_t r[2][32];
+      tmem_ld32(t_lane + AT_COL_S + sb * AT_BN, r[0]);
+      tmem_ld32(t_lane + AT_COL_S + sb * AT_BN + 32, r[1]);
       tmem_ld_wait();
       if (kbase + AT_BN > a.N) {                                // key tail: columns past N never win the max and give P = 0
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (kbase + c * 32 + i >= a.N) r[c][i] = 0xff800000u;
       }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
       const float m_new = (mx > m_run + thr) ? mx : m_run;       // first tile: m_run = -inf, so m_new = mx
@@ -203,27 +209,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t any = __ballot_sync(0xffffffffu, need);
       const float mneg = -m_new * sc;
       float sum = 0.f;
+      // the P row of this tile: 64 keys = 128 bytes = eight 16-byte chunks, XOR-swizzled by the row (one swizzle atom)
+      uint8_t* prow = smem + AT_OFF_P + sb * AT_PTILE + row * 128;
+      auto exp_row = [&](auto is_f16) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        // 32 keys = 64 bytes = four 16-byte chunks of this row inside key atom c/2, XOR-swizzled by the row
-        uint8_t* atom = prow + (c >> 1) * AT_TILE;
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float p[8];
+          for (int i = 0; i < 4; ++i) {
+            float p[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
-            sum += p[k];
+            for (int k = 0; k < 8; ++k) {
+              p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
+              sum += p[k];
+            }
+            constexpr int F = decltype(is_f16)::value;
+            *reinterpret_cast<uint4*>(prow + (((c * 4 + i) ^ sw) * 16)) =
+                make_uint4(pack16(p[0], p[1], F), pack16(p[2], p[3], F), pack16(p[4], p[5], F), pack16(p[6], p[7], F));
           }
-          const int chunk = ((c & 1) * 4 + i) ^ sw;
-          *reinterpret_cast<uint4*>(atom + chunk * 16) =
-              make_uint4(pack16(p[0], p[1], a.f16), pack16(p[2], p[3], a.f16), pack16(p[4], p[5], a.f16), pack16(p[6], p[7], a.f16));
-        }
-      }
+      };
+      if (a.f16) exp_row(std::integral_constant<int, 1>{});
+      else exp_row(std::integral_constant<int, 0>{});
       l_run = l_run * alpha + sum;
       m_run = m_new;
+      // Every phase of o_full is consumed in order (a parity wait is only meaningful when the waiter is at most one
+      // phase behind); PV(j-1) was issued a whole softmax ago, so this wait is normally already satisfied.
+      if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, ctx, 18)) { ok = false; break; }
       if (any) {                                                 // some row of this warp raised its maximum: rescale O in TMEM
-        if (!mbar_wait(o_full, (j - 1) & 1, ctx, 18)) { ok = false; break; }
         tc_fence_after();
         tmem_ld32(t_lane + AT_COL_O, r[0]);
         tmem_ld32(t_lane + AT_COL_O + 32, r[1]);
@@ -239,7 +250,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[sb]);
     }
     if (ok) ok = mbar_wait(o_full, (n_kt - 1) & 1, ctx, 19);
     const int n = qt * AT_BM + row;
@@ -334,12 +345,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// 4-D tensor map over one of q / k / v: dims (64, H, N, B) of 16-bit elements, box (64, 1, 128, 1), 128-byte swizzle;
+// 4-D tensor map over one of q / k / v: dims (64, H, N, B) of 16-bit elements, box (64, 1, rows, 1), 128-byte swizzle;
 // rows past N are out of bounds in their own dimension and read as zero.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int make_tmap_qkv(CUtensorMap* map, const void* base, int B, int N, int H) {
+static int make_tmap_qkv(CUtensorMap* map, const void* base, int B, int N, int H, int box_rows) {
   void* p = nullptr;
   cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
@@ -349,7 +360,7 @@ static int make_tmap_qkv(CUtensorMap* map, const void* base, int B, int N, int H
   EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(p);
   cuuint64_t dims[4] = {64, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
   cuuint64_t strides[3] = {128, (cuuint64_t)H * 128, (cuuint64_t)N * H * 128};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -382,11 +393,11 @@ static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H,
   const size_t plane = (size_t)B * N * H * 64 * 2;
   const uint8_t* base = static_cast<const uint8_t*>(qkv);
   CUtensorMap tq, tk, tv;
-  int st = make_tmap_qkv(&tq, base, B, N, H);
+  int st = make_tmap_qkv(&tq, base, B, N, H, AT_BM);
   if (st != KF_OK) return st;
-  st = make_tmap_qkv(&tk, base + plane, B, N, H);
+  st = make_tmap_qkv(&tk, base + plane, B, N, H, AT_BN);
   if (st != KF_OK) return st;
-  st = make_tmap_qkv(&tv, base + 2 * plane, B, N, H);
+  st = make_tmap_qkv(&tv, base + 2 * plane, B, N, H, AT_BN);
   if (st != KF_OK) return st;
   static bool attr_set[64] = {false};
   int dev = 0;

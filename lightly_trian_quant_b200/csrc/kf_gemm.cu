@@ -28,17 +28,15 @@ namespace kf {
 
 constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
 constexpr int BM = 128, BN = 128, BKB = 128;          // tile rows, tile columns, K bytes per stage
-constexpr int STAGES = 4;
 constexpr int TILE_BYTES = (BM + BN) * BKB;            // 32 KB of operands per stage
-constexpr int SF_STAGE_BYTES = 4096;                   // up to 4 atoms for A and 4 for W per stage
-constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
+constexpr int STG_WARP_BYTES = 16 * 32 * 4;            // per epilogue warp: one 16 x 32 fp32 staging tile (half a chunk)
 constexpr int EPI_WARPS = 16;
 constexpr int SF_WARP = 2 + EPI_WARPS;                 // warp index of the scale-factor copier
 constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);
 constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 32 columns each (A at +0, W at +16)
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;                       // accumulators: columns [0,256); scale factors from 256
-constexpr size_t GEMM_SMEM = 1024 + (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
+constexpr int SMEM_BUDGET = 227 * 1024;
 
 struct GemmArgs {
   const uint8_t *sfa, *sfw;
@@ -63,6 +61,15 @@ template <>
 struct KindTraits<KIND_MX4> { static constexpr int ATOMS = 2; };   // 256 elements per stage = 8 k-blocks of 32
 template <>
 struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
+// The main loop is bound by the number of operand bytes in flight (a stage is occupied from the TMA issue until the
+// MMAs that read it retire), so every kind takes as many stages as fit beside the epilogue staging tiles.
+template <int KIND>
+struct Pipe {
+  static constexpr int SF_STAGE_BYTES = 2 * KindTraits<KIND>::ATOMS * 512;      // atoms of A, then atoms of W
+  static constexpr int STAGE_BYTES = TILE_BYTES + SF_STAGE_BYTES;
+  static constexpr int STAGES = (SMEM_BUDGET - 1024 - 256 - EPI_WARPS * STG_WARP_BYTES) / STAGE_BYTES;
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * STG_WARP_BYTES + 256;
+};
 
 // ------------------------------------------------------------------------------------------------ epilogue pieces
 // tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns); global memory wants a warp to touch
@@ -71,14 +78,24 @@ struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
 // continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4 columns 4*(l&7).. of row 4*i + (l>>3), so a
 // warp instruction covers 4 rows x 128 contiguous bytes of fp32 output, and the column-indexed vectors (bias, gamma)
 // are one float4 per lane per chunk.
-__device__ __forceinline__ void stg_put(float* stg, int lane, const uint32_t (&r)[32]) {
-  uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
+// The staging tile holds 16 rows, so the chunk goes through it in two halves (lanes 0..15 write, all read; then lanes 16..31).
+template <typename F>
+__device__ __forceinline__ void stg_foreach(float* stg, int lane, const uint32_t (&r)[32], F&& f) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-}
-__device__ __forceinline__ float4 stg_get(const float* stg, int lane, int i) {
-  const int row = 4 * i + (lane >> 3);
-  return reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)];
+  for (int h = 0; h < 2; ++h) {
+    if ((lane >> 4) == h) {
+      uint4* row = reinterpret_cast<uint4*>(stg + (lane & 15) * 32);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = 4 * i + (lane >> 3);
+      f(4 * h + i, reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)]);   // pass 4h+i: row 16h + 4i + (lane>>3)
+    }
+    __syncwarp();
+  }
 }
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
@@ -104,7 +121,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
-  constexpr uint32_t TX_BYTES = TILE_BYTES + 2 * ATOMS * 512;
+  constexpr int STAGES = Pipe<KIND>::STAGES, SF_STAGE_BYTES = Pipe<KIND>::SF_STAGE_BYTES;
+  constexpr uint32_t TX_BYTES = TILE_BYTES + SF_STAGE_BYTES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -163,7 +181,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (SCALED) {
             uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
             bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
-            bulk_load_1d(sa + 2048, g.sfw + ((size_t)n_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
+            bulk_load_1d(sa + ATOMS * 512, g.sfw + ((size_t)n_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -238,7 +256,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int a = 0; a < ATOMS; ++a) {
             tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
-            tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + 2048 + a * 512));
+            tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + (ATOMS + a) * 512));
           }
           tc_commit(&sf_full[sb]);
           if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
@@ -284,16 +302,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[as]);               // accumulator is in registers: hand TMEM back
         float4 lo[8], hi[8];
-        stg_put(stg, lane, r);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) lo[i] = fma4(stg_get(stg, lane, i), ts, b_lo);
-        __syncwarp();
-        stg_put(stg, lane, r2);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) hi[i] = fma4(stg_get(stg, lane, i), ts, b_hi);
-        __syncwarp();
+        stg_foreach(stg, lane, r, [&](int i, float4 a) { lo[i] = fma4(a, ts, b_lo); });
+        stg_foreach(stg, lane, r2, [&](int i, float4 a) { hi[i] = fma4(a, ts, b_hi); });
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int m = rbase + 4 * i + rsub;
@@ -340,23 +350,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[as]);                   // accumulator is in registers: hand TMEM back
-      if (EPI != KF_EPI_QUANT) {
-        stg_put(stg, lane, r);
-        __syncwarp();
-      }
 
       if (EPI == KF_EPI_PLAIN) {
         const int esz = g.out_dtype == KF_F32 ? 4 : 2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        stg_foreach(stg, lane, r, [&](int i, float4 a) {
           const int m = rbase + 4 * i + rsub;
           float4 v;
-          if (g.flags & KF_G_PRE_ROUND_BF16) {      // the GEMM result is rounded to bf16 before the bias is added
-            const float4 a = stg_get(stg, lane, i);
+          if (g.flags & KF_G_PRE_ROUND_BF16)        // the GEMM result is rounded to bf16 before the bias is added
             v = make_float4(bf16_round(a.x * ts) + b4.x, bf16_round(a.y * ts) + b4.y, bf16_round(a.z * ts) + b4.z, bf16_round(a.w * ts) + b4.w);
-          } else {
-            v = fma4(stg_get(stg, lane, i), ts, b4);
-          }
+          else
+            v = fma4(a, ts, b4);
           if (g.flags & KF_G_GELU) v = make_float4(gelu_erf(v.x), gelu_erf(v.y), gelu_erf(v.z), gelu_erf(v.w));
           if (g.flags & KF_G_ROUND_BF16) v = make_float4(bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w));
           if (m < g.M) {
@@ -365,16 +368,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (g.out_dtype == KF_F32) *reinterpret_cast<float4*>(dst) = v;
             else *reinterpret_cast<uint2*>(dst) = pack4(v, g.out_dtype);
           }
-        }
+        });
       } else if (EPI == KF_EPI_RES) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        stg_foreach(stg, lane, r, [&](int i, float4 a) {
           const int m = rbase + 4 * i + rsub;
-          const float4 v = fma4(stg_get(stg, lane, i), ts, b4);
+          const float4 v = fma4(a, ts, b4);
           if (m < g.M)
             *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
                 make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
-        }
+        });
       } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
         // Row layout (no restaging): the thread owns 32 consecutive columns of row rbase + lane = two nv4 blocks or one
         // mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values;
@@ -433,7 +435,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
         }
       }
-      __syncwarp();                                               // staging tile is reused by the next tile
     }
   }
 
@@ -508,11 +509,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Pipe<KIND>::SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmW, g);
+  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, Pipe<KIND>::SMEM, st>>>(tmA, tmW, g);
   return cuda_status(cudaGetLastError(), "kf_gemm_bs launch");
 }
 

@@ -89,11 +89,12 @@ def bench_gemm(args):
 
 def bench_attn(args):
     B, N, H = args.batch, args.tokens, 16
-    qkvs = [torch.randn(3, B, N, H, 64, device="cuda").to(BF) for _ in range(2)]
-    outs = [torch.empty(B, N, H * 64, device="cuda", dtype=BF) for _ in range(2)]
+    dt = torch.float16 if args.dtype == "f16" else BF
+    qkvs = [torch.randn(3, B, N, H, 64, device="cuda").to(dt) for _ in range(2)]
+    outs = [torch.empty(B, N, H * 64, device="cuda", dtype=dt) for _ in range(2)]
     t = _time(lambda i: ops.attn_fwd(qkvs[i % 2], out=outs[i % 2]), args.iters)
     fl = 4.0 * B * H * N * N * 64
-    return {"kernel": "attn_fwd bf16", "B": B, "N": N, "H": H, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
+    return {"kernel": f"attn_fwd {args.dtype}", "B": B, "N": N, "H": H, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
 
 
 def bench_ln_quant(args):
@@ -136,6 +137,7 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cold", type=int, default=1)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     args = ap.parse_args()
     torch.set_grad_enabled(False)
     fn = {"gemm": bench_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "peak": bench_peak}[args.what]

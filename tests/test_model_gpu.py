@@ -149,6 +149,26 @@ def test_tiny_model_end_to_end(fmt, init):
         assert 1.0 - c_ml <= min(max(3.0 * sens, 1e-4), 5e-2), (c_ml, sens)
 
 
+@pytest.mark.parametrize("arch,fmt,side", [("vit_l", "nv4", 640), ("vit_b", "mx8", 640), ("vit_l", "mx4", 384)])
+def test_full_size_model_end_to_end(arch, fmt, side):
+    """The benchmark architectures at their real widths and depths (ViT-L/16: 24 blocks, d 1024; ViT-B/16: 12 blocks,
+    d 768; 200 queries, 640 x 640 -> 1605 / 1805 tokens), upstream init, one frame: mask- and class-logit cosine
+    >= 0.9999 against the emulated model at the same format.  The emulation of one ViT-L frame takes ~10-20 s of CPU."""
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.VIT_L if arch == "vit_l" else modeldef.VIT_B
+    model = modeldef.build_model(cfg, 0, "upstream", "cpu")
+    x = torch.rand(1, 3, side, side, generator=torch.Generator().manual_seed(11)).to(BF)
+    gmodel = copy_to_cuda(model)
+    fn, _ = stack.make_variant(arch, gmodel, f"b200_{fmt}+s{side}")
+    ml, cl = fn(x.cuda())
+    ops.check_device_error()
+    g = side // 16 * 4
+    assert ml.shape == (1, cfg.num_queries, g, g) and torch.isfinite(ml.float()).all()
+    ml_ref, cl_ref = mo.EmuModel(model, fmt, ts=_collect_ts(fn))(x.float())
+    c_ml, c_cl = mo.cosine(ml.float().cpu(), ml_ref), mo.cosine(cl.float().cpu(), cl_ref)
+    assert c_ml >= 0.9999 and c_cl >= 0.9999, (c_ml, c_cl)
+
+
 @pytest.mark.parametrize("fmt", ["mx8", "nv4", "mx4"])
 def test_block_teacher_forced(fmt):
     """One transformer block on the GPU against the emulated block fed the same fp32 stream: the block's UPDATE
