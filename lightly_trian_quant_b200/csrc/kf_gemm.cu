@@ -3,19 +3,24 @@
 //
 //   operands   K-major codes: e4m3 bytes (mx8), packed e2m1 nibbles (nv4 / mx4) or plain bf16; scale factors in
 //              the 128x4 blocked layout, one 512-byte atom per 128 rows x 4 k-blocks
-//   tile       128 x 128 output tile per CTA step, 128 bytes of K per pipeline stage (one TMA swizzle atom per row)
+//   tile       128 x 256 output tile per CTA step (one MMA instruction is 128 x 256 x 32 K-bytes), 128 bytes of K per
+//              pipeline stage.  The tile shape is set by shared-memory bandwidth: a 128 x 128 MMA reads its 8 KB of
+//              operands in the ~68 clk it executes, which alone saturates the 128 B/clk of the shared-memory array,
+//              and the TMA writes of the next stages need the same array (measured: main loop at half the instruction
+//              rate).  At 128 x 256 an MMA reads 12 KB per ~136 clk.
 //   pipeline   warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy), warp 1 = MMA issuer
-//              (4 MMAs of 32 K-bytes per stage), warp 18 = scale-factor copier (tcgen05.cp atoms smem -> TMEM,
-//              overlapping the MMAs), warps 2..17 = epilogue: the
-//              fused epilogues are bound by CUDA-core issue and memory latency, not by TMEM bandwidth, so 16 warps
-//              each take one (32-row TMEM quarter, 32-column chunk) piece of the tile: tcgen05.ld one accumulator row
-//              per thread, hand TMEM back at once, restage through warp-private swizzled shared memory so every
-//              global load / store is coalesced; two accumulator stages in TMEM so the epilogue of tile i overlaps
-//              the main loop of tile i+1; persistent CTAs, one per SM, static round-robin over tiles
+//              (4 MMAs per stage), warp 18 = scale-factor copier (tcgen05.cp atoms smem -> TMEM; the copies take
+//              tensor-pipe time but overlap the MMAs when another warp issues them), warps 2..17 = epilogue.
+//              One 256-column accumulator in TMEM: each epilogue warp takes (32-row TMEM quarter, 64 columns) into
+//              registers and hands TMEM back at once, so the next tile's main loop runs under the epilogue math;
+//              persistent CTAs, one per SM, static round-robin over tiles
 //   epilogues  PLAIN  out = act(acc*ts + bias)                       -> f32 | bf16 | f16 [M,N]
 //              RES    out = R + gamma * (acc*ts + bias)              -> f32 [M,N]         (proj, fc2)
 //              ROPE   bias + rotary embedding of q,k + relayout      -> bf16 | f16 [3,B,Ntok,H,64]   (qkv)
 //              QUANT  gelu(acc*ts + bias) quantised again            -> codes [M,N] + blocked scales (fc1 -> fc2)
+//              PLAIN and QUANT work in the TMEM row layout (a thread owns 64 consecutive columns of one row);
+//              RES and ROPE restage through warp-private swizzled shared memory so that their fp32 / table traffic
+//              is coalesced.
 //
 // Replaces (reference checkout paths): infer-opt/round13_mxfp8_full/impl/mgx_core.cu:118-444 (MXFP8, mma.sync) and
 // infer-opt/round14_fp4_full/impl/fp4g_core.cu:153-470 (NVFP4 / MXFP4, mma.sync); epilogue math per
@@ -27,16 +32,21 @@
 namespace kf {
 
 constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
-constexpr int BM = 128, BN = 128, BKB = 128;          // tile rows, tile columns, K bytes per stage
-constexpr int TILE_BYTES = (BM + BN) * BKB;            // 32 KB of operands per stage
-constexpr int STG_WARP_BYTES = 16 * 32 * 4;            // per epilogue warp: one 16 x 32 fp32 staging tile (half a chunk)
+constexpr int BM = 128, BN = 256, BKB = 128;          // tile rows, tile columns, K bytes per stage
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * BKB, TILE_BYTES = (BM + BN) * BKB;   // 16 KB of A, then 32 KB of W per stage
+constexpr int SF_STAGE_BYTES = 6144;                   // up to 4 atoms for A, then up to 4 + 4 for the two 128-row halves of W
+constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
 constexpr int EPI_WARPS = 16;
 constexpr int SF_WARP = 2 + EPI_WARPS;                 // warp index of the scale-factor copier
 constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);
-constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 32 columns each (A at +0, W at +16)
+constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 48 columns each (A at +0, W at +16)
+constexpr int SF_BUF_COLS = 48;
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_SF_COL = 256;                       // accumulators: columns [0,256); scale factors from 256
-constexpr int SMEM_BUDGET = 227 * 1024;
+constexpr int TMEM_SF_COL = 256;                       // accumulator: columns [0,256); scale factors from 256
+constexpr size_t GEMM_SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
+static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
+static_assert(TMEM_SF_COL + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
 
 struct GemmArgs {
   const uint8_t *sfa, *sfw;
@@ -61,43 +71,28 @@ template <>
 struct KindTraits<KIND_MX4> { static constexpr int ATOMS = 2; };   // 256 elements per stage = 8 k-blocks of 32
 template <>
 struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
-// The main loop is bound by the number of operand bytes in flight (a stage is occupied from the TMA issue until the
-// MMAs that read it retire), so every kind takes as many stages as fit beside the epilogue staging tiles.
-template <int KIND>
-struct Pipe {
-  static constexpr int SF_STAGE_BYTES = 2 * KindTraits<KIND>::ATOMS * 512;      // atoms of A, then atoms of W
-  static constexpr int STAGE_BYTES = TILE_BYTES + SF_STAGE_BYTES;
-  static constexpr int STAGES = (SMEM_BUDGET - 1024 - 256 - EPI_WARPS * STG_WARP_BYTES) / STAGE_BYTES;
-  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * STG_WARP_BYTES + 256;
-};
 
 // ------------------------------------------------------------------------------------------------ epilogue pieces
-// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns); global memory wants a warp to touch
-// consecutive addresses.  Each epilogue warp therefore restages its 32 x 32 chunk through a private shared-memory
-// tile (128 bytes per row, 16-byte pieces XOR-swizzled by the row so both directions are bank-conflict free) and
-// continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4 columns 4*(l&7).. of row 4*i + (l>>3), so a
-// warp instruction covers 4 rows x 128 contiguous bytes of fp32 output, and the column-indexed vectors (bias, gamma)
-// are one float4 per lane per chunk.
-// The staging tile holds 16 rows, so the chunk goes through it in two halves (lanes 0..15 write, all read; then lanes 16..31).
-template <typename F>
-__device__ __forceinline__ void stg_foreach(float* stg, int lane, const uint32_t (&r)[32], F&& f) {
+// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns per load).  Where global memory wants a
+// warp to touch consecutive addresses (the fp32 residual stream, the rotary tables), the warp restages a 32 x 32
+// chunk through a private shared-memory tile (128 bytes per row, 16-byte pieces XOR-swizzled by the row so both
+// directions are bank-conflict free) and continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4
+// columns 4*(l&7).. of row 4*i + (l>>3), so a warp instruction covers 4 rows x 128 contiguous bytes.
+__device__ __forceinline__ void stg_put(float* stg, int lane, const uint32_t (&r)[32]) {
+  uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    if ((lane >> 4) == h) {
-      uint4* row = reinterpret_cast<uint4*>(stg + (lane & 15) * 32);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-    }
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = 4 * i + (lane >> 3);
-      f(4 * h + i, reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)]);   // pass 4h+i: row 16h + 4i + (lane>>3)
-    }
-    __syncwarp();
-  }
+  for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+}
+__device__ __forceinline__ float4 stg_get(const float* stg, int lane, int i) {
+  const int row = 4 * i + (lane >> 3);
+  return reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)];
 }
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ld4_stream(const float* p) {   // read once: do not keep the line in L1
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
   return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w));
 }
@@ -115,23 +110,107 @@ __device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
   return o;
 }
 
+// QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
+// or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
+__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, int m, int n0) {
+  const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
+  const bool ok = m < g.M;
+  float v[32];
+#pragma unroll
+  for (int q4 = 0; q4 < 8; ++q4) {
+    const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[4 * q4] = gelu_erf(fmaf(__uint_as_float(r[4 * q4]), ts, bb.x));
+    v[4 * q4 + 1] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 1]), ts, bb.y));
+    v[4 * q4 + 2] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 2]), ts, bb.z));
+    v[4 * q4 + 3] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 3]), ts, bb.w));
+  }
+  if (g.flags & KF_Q_ROUND_BF16) {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = bf16_round(v[k]);
+  }
+  float am0 = 0.f, am1 = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    am0 = fmaxf(am0, fabsf(v[k]));
+    am1 = fmaxf(am1, fabsf(v[16 + k]));
+  }
+  const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
+  const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
+  int by0, by1;
+  if (g.out_fmt == KF_FMT_NV4) {
+    uint32_t o[4];
+    const float tso = __ldg(g.tso);
+    quant_nv4<16>(va, am0, tso, div_true, o, by0);
+    quant_nv4<16>(vb, am1, tso, div_true, o + 2, by1);
+    if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+    // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
+    *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n0 >> 4, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
+  } else if (g.out_fmt == KF_FMT_MX8) {
+    uint32_t o[8];
+    const float am = fmaxf(am0, am1);
+    quant_mx8<16>(va, am, div_true, o, by0);
+    quant_mx8<16>(vb, am, div_true, o + 4, by0);
+    if (ok) {
+      uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
+      p[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      p[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
+  } else {
+    uint32_t o[4];
+    const float am = fmaxf(am0, am1);
+    quant_mx4<16>(va, am, div_true, o, by0);
+    quant_mx4<16>(vb, am, div_true, o + 2, by0);
+    if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
+    g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
+  }
+}
+
+// PLAIN epilogue of one 32-column chunk in the row layout: the thread writes 64 (16-bit) or 128 (fp32) contiguous bytes.
+__device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, uint8_t* dst_row, int n0) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float v[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float4 bb = g.bias ? ldg4(g.bias + n0 + 8 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float b4[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a = __uint_as_float(r[8 * q + 4 * h + e]);
+        float x = (g.flags & KF_G_PRE_ROUND_BF16) ? bf16_round(a * ts) + b4[e] : fmaf(a, ts, b4[e]);   // the result may be rounded to bf16 before the bias
+        if (g.flags & KF_G_GELU) x = gelu_erf(x);
+        if (g.flags & KF_G_ROUND_BF16) x = bf16_round(x);
+        v[4 * h + e] = x;
+      }
+    }
+    if (dst_row) {
+      if (g.out_dtype == KF_F32) {
+        float4* d = reinterpret_cast<float4*>(dst_row + (size_t)(n0 + 8 * q) * 4);
+        d[0] = make_float4(v[0], v[1], v[2], v[3]);
+        d[1] = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        const uint2 lo = pack4(make_float4(v[0], v[1], v[2], v[3]), g.out_dtype), hi = pack4(make_float4(v[4], v[5], v[6], v[7]), g.out_dtype);
+        *reinterpret_cast<uint4*>(dst_row + (size_t)(n0 + 8 * q) * 2) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ the kernel
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
-  constexpr int STAGES = Pipe<KIND>::STAGES, SF_STAGE_BYTES = Pipe<KIND>::SF_STAGE_BYTES;
-  constexpr uint32_t TX_BYTES = TILE_BYTES + SF_STAGE_BYTES;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
   uint8_t* stg_all = sfs + (size_t)STAGES * SF_STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + EPI_WARPS * STG_WARP_BYTES);
-  uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = bars + 2 * STAGES + 2;
-  uint64_t *sf_full = bars + 2 * STAGES + 4, *sf_empty = sf_full + SF_BUFS;
+  uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = tfull + 1;
+  uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
@@ -145,11 +224,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(&sf_full[b], 1);
       mbar_init(&sf_empty[b], 1);
     }
-    mbar_init(&tfull[0], 1);
-    mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], EPI_WARPS);
-    mbar_init(&tempty[1], EPI_WARPS);
-    *abort_flag = 0;
+    mbar_init(tfull, 1);
+    mbar_init(tempty, EPI_WARPS);
+    *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;     // the swizzled operand tiles need a 1024-byte aligned base
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmW);
@@ -164,24 +241,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_holder;
   const WaitCtx ctx{abort_flag, g.err};
   const int total_tiles = g.m_tiles * g.n_tiles;
+  const bool bad_align = *abort_flag != 0;
+  if (bad_align && threadIdx.x == 0 && atomicCAS(&g.err[0], 0u, (unsigned)(-KF_ERR_DEVICE_WAIT)) == 0u) {
+    g.err[1] = 100;
+    g.err[2] = blockIdx.x;
+  }
 
-  if (warp == 0) {
+  if (bad_align) {
+    // nothing was issued; fall through to the teardown
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
+        const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;              // the last column tile may hold only 128 columns
+        const uint32_t tx = TILE_BYTES + (SCALED ? (1 + w_halves) * ATOMS * 512 : 0);
         for (int kt = 0; kt < g.k_tiles; ++kt) {
           if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) { ok = false; break; }
-          mbar_expect_tx(&full[s], TX_BYTES);
+          mbar_expect_tx(&full[s], tx);
           uint8_t* ta = tiles + (size_t)s * TILE_BYTES;
           tma_load_2d(ta, &tmA, kt * BKB, m_blk * BM, &full[s]);
-          tma_load_2d(ta + BM * BKB, &tmW, kt * BKB, n_blk * BN, &full[s]);
+          tma_load_2d(ta + A_BYTES, &tmW, kt * BKB, n_blk * BN, &full[s]);   // rows past N are filled with zeros
           if (SCALED) {
             uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
             bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
-            bulk_load_1d(sa + ATOMS * 512, g.sfw + ((size_t)n_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
+            for (int h = 0; h < w_halves; ++h)
+              bulk_load_1d(sa + (1 + h) * ATOMS * 512, g.sfw + ((size_t)(2 * n_blk + h) * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -198,16 +285,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t s = 0, ph = 0, lt = 0, sb = 0, sph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
-        const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
-        if (!mbar_wait(&tempty[as], aph ^ 1, ctx, 2)) break;
+        if (!mbar_wait(tempty, (lt & 1) ^ 1, ctx, 2)) break;                  // the epilogue has taken the previous tile out of TMEM
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BN;
+        const uint32_t d_tmem = tmem_base;
         for (int kt = 0; kt < g.k_tiles; ++kt) {
           if (!mbar_wait(&full[s], ph, ctx, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * TILE_BYTES);
-          const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + BM * BKB);
-          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * 32;           // scale factors of A, then of W at +16
+          const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + A_BYTES);
+          // scale factors of this stage: A at +0 (4 columns per atom), W at +16 (8 columns per atom pair: the atom of
+          // columns 0..127 of the tile, then the atom of columns 128..255)
+          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
           if (SCALED) {                          // copied into TMEM by the scale-copy warp, which runs ahead of the MMAs
             if (!mbar_wait(&sf_full[sb], sph, ctx, 5)) { ok = false; break; }
             tc_fence_after();
@@ -221,9 +309,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             } else if (KIND == KIND_MX8) {      // one scale per row per MMA: byte j of the atom's 32-bit word
               mma_mxf8(d_tmem, ad, bd, idesc_with_sf_id(IDESC, j, j), acc, sf_t, sf_t + 16);
             } else if (KIND == KIND_NV4) {      // four scales per row per MMA: atom j
-              mma_nvf4(d_tmem, ad, bd, IDESC, acc, sf_t + 4 * j, sf_t + 16 + 4 * j);
+              mma_nvf4(d_tmem, ad, bd, IDESC, acc, sf_t + 4 * j, sf_t + 16 + 8 * j);
             } else {                            // two scales per row per MMA: half-word (j & 1) of atom j / 2
-              mma_mxf4(d_tmem, ad, bd, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), acc, sf_t + 4 * (j >> 1), sf_t + 16 + 4 * (j >> 1));
+              mma_mxf4(d_tmem, ad, bd, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), acc, sf_t + 4 * (j >> 1), sf_t + 16 + 8 * (j >> 1));
             }
           }
           tc_commit(&empty[s]);
@@ -233,30 +321,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) tc_commit(&tfull[as]);
+        if (ok) tc_commit(tfull);
       }
     }
     __syncwarp();
   } else if (warp == SF_WARP) {
     // ------------------------------------------------------------------ scale-factor copier
-    // tcgen05.cp of one 512-byte atom costs about as much tensor-pipe time as an MMA, but it overlaps with the MMAs
-    // when it is issued from another warp; issued from the MMA thread the two serialise.  This warp therefore moves
-    // the atoms of stage s (shared memory -> one of SF_BUFS TMEM buffers) as soon as the TMA has landed them and hands
-    // the buffer to the MMA warp through an mbarrier.
+    // tcgen05.cp of one 512-byte atom costs about as much tensor-pipe time as a 128 x 128 MMA, but it overlaps with
+    // the MMAs when it is issued from another warp; issued from the MMA thread the two serialise.  This warp therefore
+    // moves the atoms of stage s (shared memory -> one of SF_BUFS TMEM buffers) as soon as the TMA has landed them and
+    // hands the buffer to the MMA warp through an mbarrier.
     if (SCALED && lane == 0) {
       uint32_t s = 0, ph = 0, sb = 0, sph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int n_blk = tile % g.n_tiles;
+        const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;
         for (int kt = 0; kt < g.k_tiles; ++kt) {
           if (!mbar_wait(&sf_empty[sb], sph ^ 1, ctx, 6)) { ok = false; break; }
           if (!mbar_wait(&full[s], ph, ctx, 7)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * 32;
+          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
           const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
 #pragma unroll
           for (int a = 0; a < ATOMS; ++a) {
             tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
-            tc_cp_sf(sf_t + 16 + 4 * a, smem_desc_sf(sa + (ATOMS + a) * 512));
+            tc_cp_sf(sf_t + 16 + 8 * a, smem_desc_sf(sa + (ATOMS + a) * 512));
+            if (w_halves == 2) tc_cp_sf(sf_t + 16 + 8 * a + 4, smem_desc_sf(sa + (2 * ATOMS + a) * 512));
           }
           tc_commit(&sf_full[sb]);
           if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
@@ -266,44 +357,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 32-column chunk)
+    // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 64-column group)
     const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
-    const int wq = (warp - 2) >> 2;               // which 32-column chunk of the 128-column tile
+    const int cg = (warp - 2) >> 2;               // which 64-column group of the 256-column tile
     float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES);
-    const int c4 = 4 * (lane & 7);                // this lane's 4 columns inside the chunk
-    const int rsub = lane >> 3;                   // row 4*i + rsub in pass i
+    const int c4 = 4 * (lane & 7);                // coalesced layout: this lane's 4 columns inside a 32-column chunk
+    const int rsub = lane >> 3;                   // coalesced layout: row 4*i + rsub in pass i
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
     const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
       const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
-      const uint32_t as = lt & 1, aph = (lt >> 1) & 1;
       const int rbase = m_blk * BM + quarter * 32;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-      uint32_t r[32];
+      const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
+      uint32_t r0[32], r1[32];
+      if (!mbar_wait(tfull, lt & 1, ctx, 4)) break;
+      tc_fence_after();
+      tmem_ld32(taddr, r0);
+      tmem_ld32(taddr + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
+      if (n0 >= g.N) continue;                                   // column group past N in the last column tile
 
       if (EPI == KF_EPI_ROPE) {
-        // wq = (head inside the tile, which half of the head this warp writes: 0 = columns 0..31, 1 = columns 32..63)
-        const int hc = wq >> 1, part = wq & 1;
-        const int n0 = n_blk * BN + hc * 64;
+        // the 64 columns of this warp are one head of q, k or v: r0 = first half, r1 = second half.  Both halves go
+        // through the staging tile into the coalesced layout (the first stays in registers, the second is read back
+        // pass by pass), where the rotary tables and the output rows are read / written 4 rows x 128 bytes at a time.
         const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
         const int nbatch = g.M / g.Ntok;
         const int b0 = rbase / g.Ntok, t0 = rbase - b0 * g.Ntok;   // one division per tile; rows advance from here
         const float4 b_lo = g.bias ? ldg4(g.bias + n0 + c4) : z4, b_hi = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
-        if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
-        tc_fence_after();
-        uint32_t r2[32];
-        tmem_ld32(taddr + hc * 64, r);
-        tmem_ld32(taddr + hc * 64 + 32, r2);
-        tmem_ld_wait();
-        tc_fence_before();
+        float4 lo[8];
+        stg_put(stg, lane, r0);
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[as]);               // accumulator is in registers: hand TMEM back
-        float4 lo[8], hi[8];
-        stg_foreach(stg, lane, r, [&](int i, float4 a) { lo[i] = fma4(a, ts, b_lo); });
-        stg_foreach(stg, lane, r2, [&](int i, float4 a) { hi[i] = fma4(a, ts, b_hi); });
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo[i] = fma4(stg_get(stg, lane, i), ts, b_lo);
+        __syncwarp();
+        stg_put(stg, lane, r1);
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int m = rbase + 4 * i + rsub;
@@ -313,127 +409,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               t -= g.Ntok;
               ++b;
             }
-            float4 o = part ? hi[i] : lo[i];
+            const float4 hi = fma4(stg_get(stg, lane, i), ts, b_hi);
+            float4 ol = lo[i], oh = hi;
             if (which < 2 && t >= g.prefix) {
-              const size_t off = (size_t)(t - g.prefix) * 64 + part * 32 + c4;
-              const float4 sn = ldg4(g.sin + off), cs = ldg4(g.cos + off);
-              if (part == 0)      // lo' = lo*cos - hi*sin
-                o = make_float4(lo[i].x * cs.x - hi[i].x * sn.x, lo[i].y * cs.y - hi[i].y * sn.y, lo[i].z * cs.z - hi[i].z * sn.z,
-                                lo[i].w * cs.w - hi[i].w * sn.w);
-              else                // hi' = hi*cos + lo*sin
-                o = make_float4(hi[i].x * cs.x + lo[i].x * sn.x, hi[i].y * cs.y + lo[i].y * sn.y, hi[i].z * cs.z + lo[i].z * sn.z,
-                                hi[i].w * cs.w + lo[i].w * sn.w);
+              const float* tab = g.sin + (size_t)(t - g.prefix) * 64 + c4;
+              const float* tabc = g.cos + (size_t)(t - g.prefix) * 64 + c4;
+              const float4 sl = ldg4(tab), cl = ldg4(tabc), sh = ldg4(tab + 32), ch = ldg4(tabc + 32);
+              // lo' = lo*cos - hi*sin (tables of columns 0..31), hi' = hi*cos + lo*sin (tables of columns 32..63)
+              ol = make_float4(lo[i].x * cl.x - hi.x * sl.x, lo[i].y * cl.y - hi.y * sl.y, lo[i].z * cl.z - hi.z * sl.z, lo[i].w * cl.w - hi.w * sl.w);
+              oh = make_float4(hi.x * ch.x + lo[i].x * sh.x, hi.y * ch.y + lo[i].y * sh.y, hi.z * ch.z + lo[i].z * sh.z, hi.w * ch.w + lo[i].w * sh.w);
             }
-            uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + part * 32 + c4) * 2;
-            *reinterpret_cast<uint2*>(dst) = pack4(o, g.out_dtype);
+            uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + c4) * 2;
+            *reinterpret_cast<uint2*>(dst) = pack4(ol, g.out_dtype);
+            *reinterpret_cast<uint2*>(dst + 64) = pack4(oh, g.out_dtype);
           }
         }
-        continue;
-      }
-
-      const int n = n_blk * BN + wq * 32 + c4;                   // this lane's first column
-      const float4 b4 = (g.bias && EPI != KF_EPI_QUANT) ? ldg4(g.bias + n) : z4;
-      float4 rr[8];
-      float4 g4 = z4;
-      if (EPI == KF_EPI_RES) {                                    // residual loads go out before the accumulator wait
-        g4 = ldg4(g.gamma + n);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = rbase + 4 * i + rsub;
-          rr[i] = m < g.M ? *reinterpret_cast<const float4*>(g.R + (size_t)m * g.N + n) : z4;
-        }
-      }
-      if (!mbar_wait(&tfull[as], aph, ctx, 4)) break;
-      tc_fence_after();
-      tmem_ld32(taddr + wq * 32, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[as]);                   // accumulator is in registers: hand TMEM back
-
-      if (EPI == KF_EPI_PLAIN) {
-        const int esz = g.out_dtype == KF_F32 ? 4 : 2;
-        stg_foreach(stg, lane, r, [&](int i, float4 a) {
-          const int m = rbase + 4 * i + rsub;
-          float4 v;
-          if (g.flags & KF_G_PRE_ROUND_BF16)        // the GEMM result is rounded to bf16 before the bias is added
-            v = make_float4(bf16_round(a.x * ts) + b4.x, bf16_round(a.y * ts) + b4.y, bf16_round(a.z * ts) + b4.z, bf16_round(a.w * ts) + b4.w);
-          else
-            v = fma4(a, ts, b4);
-          if (g.flags & KF_G_GELU) v = make_float4(gelu_erf(v.x), gelu_erf(v.y), gelu_erf(v.z), gelu_erf(v.w));
-          if (g.flags & KF_G_ROUND_BF16) v = make_float4(bf16_round(v.x), bf16_round(v.y), bf16_round(v.z), bf16_round(v.w));
-          if (m < g.M) {
-            const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
-            uint8_t* dst = static_cast<uint8_t*>(g.C) + ((size_t)orow * g.N + n) * esz;
-            if (g.out_dtype == KF_F32) *reinterpret_cast<float4*>(dst) = v;
-            else *reinterpret_cast<uint2*>(dst) = pack4(v, g.out_dtype);
-          }
-        });
+        __syncwarp();                                             // the staging tile is reused by the next tile
       } else if (EPI == KF_EPI_RES) {
-        stg_foreach(stg, lane, r, [&](int i, float4 a) {
-          const int m = rbase + 4 * i + rsub;
-          const float4 v = fma4(a, ts, b4);
-          if (m < g.M)
-            *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
-                make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
-        });
-      } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-        // Row layout (no restaging): the thread owns 32 consecutive columns of row rbase + lane = two nv4 blocks or one
-        // mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values;
-        // the outputs are 4-8x smaller than fp32, so their 16-byte per-row stores cost little.
-        const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
-        const bool rb = g.flags & KF_Q_ROUND_BF16;
-        const int m = rbase + lane;
-        const bool ok = m < g.M;
-        const int n0 = n_blk * BN + wq * 32;
-        float v[32];
+        // two 32-column chunks, each restaged so that the fp32 residual is read and written 128 contiguous bytes per row
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : z4;
-          v[4 * q4] = gelu_erf(fmaf(__uint_as_float(r[4 * q4]), ts, bb.x));
-          v[4 * q4 + 1] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 1]), ts, bb.y));
-          v[4 * q4 + 2] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 2]), ts, bb.z));
-          v[4 * q4 + 3] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 3]), ts, bb.w));
-        }
-        if (rb) {
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + 32 * c + c4;
+          stg_put(stg, lane, c == 0 ? r0 : r1);
+          __syncwarp();
+          const float4 b4 = g.bias ? ldg4(g.bias + n) : z4, g4 = ldg4(g.gamma + n);
 #pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = bf16_round(v[k]);
-        }
-        float am0 = 0.f, am1 = 0.f;
+          for (int hp = 0; hp < 2; ++hp) {                        // four passes at a time: loads first, then the math
+            float4 rr[4];
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          am0 = fmaxf(am0, fabsf(v[k]));
-          am1 = fmaxf(am1, fabsf(v[16 + k]));
-        }
-        const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
-        const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
-        int by0, by1;
-        if (g.out_fmt == KF_FMT_NV4) {
-          uint32_t o[4];
-          quant_nv4<16>(va, am0, __ldg(g.tso), div_true, o, by0);
-          quant_nv4<16>(vb, am1, __ldg(g.tso), div_true, o + 2, by1);
-          if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-          // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
-          *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n_blk * 8 + wq * 2, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
-        } else if (g.out_fmt == KF_FMT_MX8) {
-          uint32_t o[8];
-          const float am = fmaxf(am0, am1);
-          quant_mx8<16>(va, am, div_true, o, by0);
-          quant_mx8<16>(vb, am, div_true, o + 4, by0);
-          if (ok) {
-            uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
-            p[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            p[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            for (int i = 0; i < 4; ++i) {
+              const int m = rbase + 4 * (4 * hp + i) + rsub;
+              rr[i] = m < g.M ? ld4_stream(g.R + (size_t)m * g.N + n) : z4;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int m = rbase + 4 * (4 * hp + i) + rsub;
+              const float4 v = fma4(stg_get(stg, lane, 4 * hp + i), ts, b4);
+              if (m < g.M)
+                *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
+                    make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
+            }
           }
-          g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
-        } else {
-          uint32_t o[4];
-          const float am = fmaxf(am0, am1);
-          quant_mx4<16>(va, am, div_true, o, by0);
-          quant_mx4<16>(vb, am, div_true, o + 2, by0);
-          if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-          g.SFo[sf_offset(m, n_blk * 4 + wq, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
+          __syncwarp();                                           // the staging tile is reused by the next chunk
         }
+      } else if (EPI == KF_EPI_PLAIN) {
+        const int m = rbase + lane;
+        uint8_t* dst_row = nullptr;
+        if (m < g.M) {
+          const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
+          dst_row = static_cast<uint8_t*>(g.C) + (size_t)orow * g.N * (g.out_dtype == KF_F32 ? 4 : 2);
+        }
+        plain_chunk(g, r0, ts, dst_row, n0);
+        plain_chunk(g, r1, ts, dst_row, n0 + 32);
+      } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
+        quant_chunk(g, r0, ts, rbase + lane, n0);
+        quant_chunk(g, r1, ts, rbase + lane, n0 + 32);
       }
     }
   }
@@ -509,11 +539,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Pipe<KIND>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, Pipe<KIND>::SMEM, st>>>(tmA, tmW, g);
+  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmW, g);
   return cuda_status(cudaGetLastError(), "kf_gemm_bs launch");
 }
 
@@ -539,7 +569,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_gemm_bs: unknown operand format %d", fmt);
   KF_REQUIRE(epi >= KF_EPI_PLAIN && epi <= KF_EPI_QUANT, "kf_gemm_bs: unknown epilogue %d", epi);
   KF_REQUIRE(p->M >= 0 && p->N > 0 && p->K > 0, "kf_gemm_bs: bad shape M=%d N=%d K=%d", p->M, p->N, p->K);
-  KF_REQUIRE(p->N % BN == 0, "kf_gemm_bs: N=%d must be a multiple of %d", p->N, BN);
+  KF_REQUIRE(p->N % 128 == 0, "kf_gemm_bs: N=%d must be a multiple of 128", p->N);
   const int kelems = fmt == KF_FMT_MX8 ? 128 : (fmt == KF_FMT_BF16 ? 64 : 256);   // K elements per 128-byte stage
   KF_REQUIRE(p->K % kelems == 0, "kf_gemm_bs: K=%d must be a multiple of %d for this format", p->K, kelems);
   if (p->M == 0) return KF_OK;
@@ -577,7 +607,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.M = p->M; g.N = p->N; g.K = p->K;
   g.Ntok = p->Ntok; g.prefix = p->prefix; g.H = p->H; g.d = p->H * 64;
   g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
-  g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = p->N / BN; g.k_tiles = (int)(kbytes / BKB);
+  g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = (p->N + BN - 1) / BN; g.k_tiles = (int)(kbytes / BKB);
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
   g.row_group = p->out_row_group; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
   g.err = dev_error_ptr();
