@@ -27,14 +27,12 @@ namespace kf {
 
 constexpr int AT_BM = 128, AT_BN = 64, AT_D = 64;
 constexpr int AT_THREADS = 192;
-constexpr int AT_KV = 3;                               // K / V ring depth
+constexpr int AT_KV = 4;                               // K / V ring depth
 constexpr int AT_QTILE = AT_BM * AT_D * 2;             // 16 KB
 constexpr int AT_KTILE = AT_BN * AT_D * 2;             // 8 KB
-constexpr int AT_PTILE = AT_BM * AT_BN * 2;            // 16 KB: 128 rows x 64 keys, one 128-byte swizzle atom per row
-constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_P = AT_OFF_V + AT_KV * AT_KTILE,
-              AT_OFF_BAR = AT_OFF_P + 2 * AT_PTILE;
+constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_BAR = AT_OFF_V + AT_KV * AT_KTILE;
 constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
-constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128;   // S buffers at columns 0 and 64
+constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128, AT_COL_P = 192;   // S buffers at columns 0 and 64, P (16-bit pairs) at 192 and 224
 
 struct AttnArgs {
   void* O;
@@ -53,6 +51,12 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
   if (f16) {
     __half2 h = __floats2half2_rn(a, b);
@@ -72,6 +76,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
+  if (a.err[0] != 0) return;                             // an earlier CTA or launch already failed: do not wait all over again
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (a.N + AT_BM - 1) / AT_BM;
   const int qt = blockIdx.x % q_tiles;
@@ -157,11 +162,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, ctx, 14)) break;
         if (!mbar_wait(&v_full[st], (j / AT_KV) & 1, ctx, 15)) break;
         tc_fence_after();
-        const uint64_t pdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_P + (j & 1) * AT_PTILE));
+        const uint32_t t_p = tmem_base + AT_COL_P + (j & 1) * (AT_BN / 2);
         const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_KTILE));
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 32 bytes of the P row; B: 16 key rows of V = two 8-row groups of 1024 bytes
-          mma_f16(t_o, pdesc + 2 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | kk) != 0);
+        for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 8 TMEM columns of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
+          mma_f16_ta(t_o, t_p + 8 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | kk) != 0);
         tc_commit(o_full);
         tc_commit(&kv_empty[st]);
         if (j + 2 < n_kt) {                  // the softmax of tile j has consumed S buffer j & 1 (it arrived on p_full): refill it
@@ -180,7 +185,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float sc = a.scale_log2;
     const float thr = 8.0f / sc;
     float m_run = -INFINITY, l_run = 0.f;
-    const int sw = row & 7;
     bool ok = true;
     for (int j = 0; j < n_kt; ++j) {
       const int sb = j & 1;
@@ -198,39 +202,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; ++i)
             if (kbase + c * 32 + i >= a.N) r[c][i] = 0xff800000u;
       }
-      float mx = -INFINITY;
+      // the P row of this tile goes to tensor memory (the A operand of the PV product): 64 keys = 32 columns of 16-bit pairs
+      const uint32_t t_p = t_lane + AT_COL_P + sb * (AT_BN / 2);
+      // P = exp2(s*sc + mneg) into shared memory; returns the row sum.  With TRACK the row maximum is gathered in the
+      // same pass (four independent chains), so the maximum is off the critical path of the exponentials.
+      auto exp_row = [&](auto is_f16, auto track, float mneg, float (&mx4)[4]) -> float {
+        constexpr int F = decltype(is_f16)::value;
+        constexpr bool TRACK = decltype(track)::value != 0;
+        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
-      const float m_new = (mx > m_run + thr) ? mx : m_run;       // first tile: m_run = -inf, so m_new = mx
-      const float alpha = ex2((m_run - m_new) * sc);             // 1 when unchanged, 0 on the first tile
-      const bool need = (m_new != m_run) && j > 0;
-      const uint32_t any = __ballot_sync(0xffffffffu, need);
-      const float mneg = -m_new * sc;
-      float sum = 0.f;
-      // the P row of this tile: 64 keys = 128 bytes = eight 16-byte chunks, XOR-swizzled by the row (one swizzle atom)
-      uint8_t* prow = smem + AT_OFF_P + sb * AT_PTILE + row * 128;
-      auto exp_row = [&](auto is_f16) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < 2; ++c) {
+          uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             float p[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
-              sum += p[k];
+            for (int k = 0; k < 8; ++k) p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
+            if (TRACK) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1]));
             }
-            constexpr int F = decltype(is_f16)::value;
-            *reinterpret_cast<uint4*>(prow + (((c * 4 + i) ^ sw) * 16)) =
-                make_uint4(pack16(p[0], p[1], F), pack16(p[2], p[3], F), pack16(p[4], p[5], F), pack16(p[6], p[7], F));
+            s0 += (p[0] + p[1]) + (p[2] + p[3]);
+            s1 += (p[4] + p[5]) + (p[6] + p[7]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) w[4 * i + k] = pack16(p[2 * k], p[2 * k + 1], F);
           }
+          tmem_st16(t_p + 16 * c, w);
+        }
+        return s0 + s1;
       };
-      if (a.f16) exp_row(std::integral_constant<int, 1>{});
-      else exp_row(std::integral_constant<int, 0>{});
+      auto run = [&](auto track, float mneg, float (&mx4)[4]) -> float {
+        return a.f16 ? exp_row(std::integral_constant<int, 1>{}, track, mneg, mx4) : exp_row(std::integral_constant<int, 0>{}, track, mneg, mx4);
+      };
+      // Lazy maximum: the exponentials of tile j > 0 use the running maximum as it is (valid while the tile maximum
+      // exceeds it by less than 2^8 in the exponent domain: P <= 256, sums and O stay in fp32 range); only a row whose
+      // maximum grew by more than that recomputes its P with the new maximum and has its O rescaled.  The first tile has
+      // no running maximum yet and finds its own first.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float sum = 0.f, alpha = 1.f;
+      bool need;
+      if (j > 0) {
+        sum = run(std::integral_constant<int, 1>{}, -m_run * sc, mx4);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      need = j == 0 || mx > m_run + thr;
+      const uint32_t any_need = __ballot_sync(0xffffffffu, need);
+      if (any_need) {                                            // warp-uniform: the tensor-memory stores need the whole warp
+        if (need) {
+          alpha = ex2((m_run - mx) * sc);                        // 0 on the first tile
+          m_run = mx;
+        }
+        sum = run(std::integral_constant<int, 0>{}, -m_run * sc, mx4);
+      }
+      const uint32_t any = j > 0 ? any_need : 0u;
       l_run = l_run * alpha + sum;
-      m_run = m_new;
       // Every phase of o_full is consumed in order (a parity wait is only meaningful when the waiter is at most one
       // phase behind); PV(j-1) was issued a whole softmax ago, so this wait is normally already satisfied.
       if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, ctx, 18)) { ok = false; break; }
@@ -248,8 +278,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st32(t_lane + AT_COL_O + 32, r[1]);
         tmem_st_wait();
       }
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       mbar_arrive(&p_full[sb]);
     }
     if (ok) ok = mbar_wait(o_full, (n_kt - 1) & 1, ctx, 19);

@@ -214,6 +214,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
+  if (g.err[0] != 0) return;                             // an earlier CTA or launch already failed: do not wait all over again
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
