@@ -15,6 +15,7 @@ namespace kf {
 // ---------------------------------------------------------------------------------------------- host side status
 void set_error(const char* fmt, ...);
 int cuda_status(cudaError_t e, const char* what);
+int device_sm_count(int* sms);   // multiprocessor count of the current device (cached)
 
 #define KF_REQUIRE(cond, ...)            \
   do {                                   \

@@ -30,10 +30,13 @@ __global__ void __launch_bounds__(256) im2col16_kernel(const __nv_bfloat16* __re
 // pixel (Y, X) = (2y+dy, 2x+dx):  a = bf16(gelu(g + bias[c]))  (skipped when the GEMM epilogue already applied it:
 // pre_act != 0);  o = bf16(sum over the 3x3 taps of a * dww[tap][c]) with zero padding, fp32 accumulation in tap
 // order;  out = bf16(LayerNorm over c of o) in NHWC.
-// One CTA = 4 x 8 output pixels.  Per 256-channel slab: the 6 x 10 halo is brought in with 16-byte loads (512
-// contiguous bytes per pixel), each thread then convolves 8 channels of 4 pixels with the 72 tap weights held in
-// registers; the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics.
-constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 256;
+// Persistent CTAs, one tile of 4 x 8 output pixels at a time.  The channels go through in slabs of 128: the 6 x 10 halo
+// of a slab (256 contiguous bytes per pixel) is fetched with 16-byte cp.async copies (zero fill outside the image) into
+// a 3-deep shared-memory ring that runs ahead across slabs AND tiles, so two slabs are always in flight while a third is
+// convolved; each thread convolves 8 channels of 2 pixels with the 72 tap weights held in registers; the conv results of
+// all C channels stay in shared memory for the two-pass LayerNorm statistics.
+constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 128, DW_RING = 3;
+constexpr int DW_SLAB_BYTES = DW_HW * DW_CH * 2;        // 15 KB
 
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float (&f)[8]) {
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -52,112 +55,161 @@ __device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
   }
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;                          // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+
+struct DwTile {
+  int b, Y0, X0;
+};
+__device__ __forceinline__ DwTile dw_tile(int tile, int tiles_x, int tiles_y) {
+  DwTile t;
+  t.X0 = (tile % tiles_x) * DW_TW;
+  const int r = tile / tiles_x;
+  t.Y0 = (r % tiles_y) * DW_TH;
+  t.b = r / tiles_y;
+  return t;
+}
 
 __global__ void __launch_bounds__(256, 2)
 dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias, const float* __restrict__ dww, const float* __restrict__ lnw,
-             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps, int pre_act) {
+             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps, int pre_act, int tiles_x, int tiles_y,
+             int total_tiles) {
   extern __shared__ __align__(16) uint8_t dsm[];
-  uint4* act = reinterpret_cast<uint4*>(dsm);                               // [60 pixels][32 groups of 8 channels]
-  uint4* res = reinterpret_cast<uint4*>(dsm + DW_HW * DW_CH * 2);           // [32 pixels][C/8]
+  uint4* res = reinterpret_cast<uint4*>(dsm + DW_RING * DW_SLAB_BYTES);     // [32 pixels][C/8]
   const int t = threadIdx.x;
   const int Ho = 2 * Hs, Wo = 2 * Ws;
-  const int X0 = blockIdx.x * DW_TW, Y0 = blockIdx.y * DW_TH, b = blockIdx.z;
-  const int grp = t & 31, prow = t >> 5;                                     // 8-channel group, pixel sub-index 0..7
-  const int C8 = C >> 3;
+  const int C8 = C >> 3, S = C / DW_CH;
+  const int grp = t & 15, prow = t >> 4;                                     // 8-channel group of the slab, pixel sub-index 0..15
 
-  for (int ch = 0; ch < C; ch += DW_CH) {
-    // ---- halo: 60 pixels x 32 uint4
-    for (int idx = t; idx < DW_HW * 32; idx += 256) {
-      const int px = idx >> 5, q = idx & 31;
-      const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
-      const int Y = Y0 + hy - 1, X = X0 + hx - 1;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (Y >= 0 && Y < Ho && X >= 0 && X < Wo) {
-        const int64_t row = ((int64_t)b * Hs + (Y >> 1)) * Ws + (X >> 1);
-        v = __ldg(reinterpret_cast<const uint4*>(g + row * 4 * C + ((Y & 1) * 2 + (X & 1)) * C + ch) + q);
-        if (!pre_act) {
-          float f[8];
-          bf16x8_to_f32(v, f);
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8)), b1 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8) + 1);
-          const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-          for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + bb[k]);
-          v = f32_to_bf16x8(f);
-        }
+  // issue cursor (runs two slabs ahead of the consume cursor, across tile boundaries)
+  int i_tile = blockIdx.x, i_slab = 0, i_slot = 0;
+  auto issue = [&]() {
+    if (i_tile < total_tiles) {
+      const DwTile T = dw_tile(i_tile, tiles_x, tiles_y);
+      uint4* act = reinterpret_cast<uint4*>(dsm + i_slot * DW_SLAB_BYTES);
+      for (int idx = t; idx < DW_HW * 16; idx += 256) {
+        const int px = idx >> 4, q = idx & 15;
+        const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
+        const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
+        const bool in = Y >= 0 && Y < Ho && X >= 0 && X < Wo;
+        const int64_t row = in ? ((int64_t)T.b * Hs + (Y >> 1)) * Ws + (X >> 1) : 0;
+        const __nv_bfloat16* src = g + row * 4 * C + (in ? ((Y & 1) * 2 + (X & 1)) * C : 0) + i_slab * DW_CH + q * 8;
+        cp_async16_zfill(act + idx, src, in);
       }
-      act[idx] = v;
+      if (++i_slab == S) {
+        i_slab = 0;
+        i_tile += gridDim.x;
+      }
+      if (++i_slot == DW_RING) i_slot = 0;
     }
-    // ---- the 9 x 8 tap weights of this thread's channel group
-    float w[9][8];
-#pragma unroll
-    for (int k = 0; k < 9; ++k) {
-      const float4 w0 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8)), w1 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8) + 1);
-      w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
-    }
-    __syncthreads();
-    // ---- depthwise 3x3: thread = (8 channels, pixels prow, prow+8, prow+16, prow+24)
-#pragma unroll
-    for (int k4 = 0; k4 < 4; ++k4) {
-      const int px = prow + 8 * k4;
-      const int oy = px / DW_TW, ox = px - oy * DW_TW;
-      float acc[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-#pragma unroll
-      for (int ky = 0; ky < 3; ++ky)
-#pragma unroll
-        for (int kx = 0; kx < 3; ++kx) {
-          float f[8];
-          bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 32 + grp], f);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] = fmaf(f[k], w[ky * 3 + kx][k], acc[k]);
-        }
-      res[px * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc);
-    }
-    __syncthreads();
-  }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // every thread commits one group per call, copies or not
+  };
+  issue();
+  issue();
 
-  // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels, lane = 8 channels per 256-channel slab
+  int c_slot = 0;
   const int warp = t >> 5, lane = t & 31;
   const float invC = 1.0f / (float)C;
-  for (int px = warp; px < DW_TH * DW_TW; px += 8) {
-    const int oy = px / DW_TW, ox = px - oy * DW_TW;
-    const int Y = Y0 + oy, X = X0 + ox;
-    const uint4* r = res + px * C8;
-    float s = 0.f;
-    for (int i = lane; i < C8; i += 32) {
-      float f[8];
-      bf16x8_to_f32(r[i], f);
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const DwTile T = dw_tile(tile, tiles_x, tiles_y);
+    for (int sl = 0; sl < S; ++sl) {
+      const int ch = sl * DW_CH;
+      asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of the slab to consume have landed
+      __syncthreads();                                        // ... and everybody's; the previous slab's conv is finished everywhere
+      issue();                                                // refill the slot that conv just left (two slabs stay in flight)
+      uint4* act = reinterpret_cast<uint4*>(dsm + c_slot * DW_SLAB_BYTES);
+      if (!pre_act) {                                         // bias + GELU once per halo element, in place
+        for (int idx = t; idx < DW_HW * 16; idx += 256) {
+          const int px = idx >> 4, q = idx & 15;
+          const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
+          const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
+          if (Y >= 0 && Y < Ho && X >= 0 && X < Wo) {
+            float f[8];
+            bf16x8_to_f32(act[idx], f);
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8)), b1 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8) + 1);
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int k = 0; k < 8; ++k) s += f[k];
+            for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + bb[k]);
+            act[idx] = f32_to_bf16x8(f);
+          }
+        }
+        __syncthreads();
+      }
+      // ---- the 9 x 8 tap weights of this thread's channel group
+      float w[9][8];
+#pragma unroll
+      for (int k = 0; k < 9; ++k) {
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8)), w1 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8) + 1);
+        w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
+      }
+      // ---- depthwise 3x3: thread = (8 channels, pixels prow and prow + 16)
+#pragma unroll
+      for (int k2 = 0; k2 < 2; ++k2) {
+        const int px = prow + 16 * k2;
+        const int oy = px / DW_TW, ox = px - oy * DW_TW;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < 3; ++kx) {
+            float f[8];
+            bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 16 + grp], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = fmaf(f[k], w[ky * 3 + kx][k], acc[k]);
+          }
+        res[px * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc);
+      }
+      if (++c_slot == DW_RING) c_slot = 0;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float mean = s * invC;
-    float ss = 0.f;
-    for (int i = lane; i < C8; i += 32) {
-      float f[8];
-      bf16x8_to_f32(r[i], f);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) ss = fmaf(f[k] - mean, f[k] - mean, ss);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = rsqrtf(ss * invC + eps);
-    if (Y < Ho && X < Wo) {
-      uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)b * Ho + Y) * Wo + X) * C);
+    __syncthreads();                                          // all conv results of the tile are in res
+
+    // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels, lane = 8 channels per 256-channel step
+    for (int px = warp; px < DW_TH * DW_TW; px += 8) {
+      const int oy = px / DW_TW, ox = px - oy * DW_TW;
+      const int Y = T.Y0 + oy, X = T.X0 + ox;
+      const uint4* r = res + px * C8;
+      float s = 0.f;
       for (int i = lane; i < C8; i += 32) {
         float f[8];
         bf16x8_to_f32(r[i], f);
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
-        const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
-        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] = (f[k] - mean) * rstd * ww[k] + cc[k];
-        dst[i] = f32_to_bf16x8(f);
+        for (int k = 0; k < 8; ++k) s += f[k];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s * invC;
+      float ss = 0.f;
+      for (int i = lane; i < C8; i += 32) {
+        float f[8];
+        bf16x8_to_f32(r[i], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(f[k] - mean, f[k] - mean, ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss * invC + eps);
+      if (Y < Ho && X < Wo) {
+        uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)T.b * Ho + Y) * Wo + X) * C);
+        for (int i = lane; i < C8; i += 32) {
+          float f[8];
+          bf16x8_to_f32(r[i], f);
+          const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
+          const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
+          const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = (f[k] - mean) * rstd * ww[k] + cc[k];
+          dst[i] = f32_to_bf16x8(f);
+        }
       }
     }
+    // the next tile's first conv writes res only after the next __syncthreads, which every warp reaches after its LayerNorm
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ semantic scores
@@ -259,18 +311,24 @@ extern "C" int kf_dw_ln(const void* g, const float* bias, const float* dww, cons
   if (B == 0) return KF_OK;
   KF_REQUIRE(g && (bias || pre_act) && dww && lnw && lnb && out && al16(g) && al16(out) && al16(lnw) && al16(lnb) && al16(dww) && al16(bias),
              "kf_dw_ln: tensors must be non-null and 16-byte aligned");
-  const size_t smem = (size_t)DW_HW * DW_CH * 2 + (size_t)DW_TH * DW_TW * C * 2;
+  const size_t smem = (size_t)DW_RING * DW_SLAB_BYTES + (size_t)DW_TH * DW_TW * C * 2;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(dw_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)DW_HW * DW_CH * 2 + DW_TH * DW_TW * 1024 * 2));
+    cudaError_t e = cudaFuncSetAttribute(dw_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)DW_RING * DW_SLAB_BYTES + DW_TH * DW_TW * 1024 * 2));
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dw_ln_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  dim3 grid((2 * Ws + DW_TW - 1) / DW_TW, (2 * Hs + DW_TH - 1) / DW_TH, B);
+  int sms = 0;
+  int st = device_sm_count(&sms);
+  if (st != KF_OK) return st;
+  const int tiles_x = (2 * Ws + DW_TW - 1) / DW_TW, tiles_y = (2 * Hs + DW_TH - 1) / DW_TH;
+  const int64_t total = (int64_t)tiles_x * tiles_y * B;
+  KF_REQUIRE(total < (1ll << 31), "kf_dw_ln: too many tiles");
+  const int grid = (int)(total < 2 * sms ? total : 2 * sms);
   dw_ln_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(g), bias, dww, lnw, lnb,
-                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps, pre_act);
+                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps, pre_act, tiles_x, tiles_y, (int)total);
   return cuda_status(cudaGetLastError(), "kf_dw_ln launch");
 }
 

@@ -5,6 +5,7 @@ larger than L2 so operands come from HBM, not from cache).
     python -m lightly_trian_quant_b200.microbench attn --batch 8 --tokens 1605
     python -m lightly_trian_quant_b200.microbench ln_quant --fmt mx8 --batch 8
     python -m lightly_trian_quant_b200.microbench quant_rows --fmt nv4 --batch 8 --k 1024
+    python -m lightly_trian_quant_b200.microbench dw_ln --batch 14 --hs 80 --k 1024
     python -m lightly_trian_quant_b200.microbench peak --fmt nv4
 
 `kind` selects the GEMM shape AND its fused epilogue: qkv (bias + RoPE + relayout), proj / fc2 (bias, LayerScale,
@@ -118,6 +119,16 @@ def bench_quant_rows(args):
     return {"kernel": f"quant_rows bf16->{args.fmt}", "M": M, "K": K, "us": t * 1e6, "GB/s": by / t / 1e9, "bytes": by}
 
 
+def bench_dw_ln(args):
+    B, Hs, C = args.batch, args.hs, args.k
+    n = max(2, int(2 * 126e6 / (B * Hs * Hs * 4 * C * 2)) + 1)
+    gs = [torch.randn(B * Hs * Hs, 4 * C, device="cuda").to(BF) for _ in range(n)]
+    dww, lnw, lnb = torch.randn(9, C, device="cuda") * 0.3, torch.ones(C, device="cuda"), torch.zeros(C, device="cuda")
+    t = _time(lambda i: ops.dw_ln(gs[i % n], None, dww, lnw, lnb, B, Hs, Hs, 1e-6, pre_act=True), args.iters)
+    by = 2 * gs[0].numel() * 2
+    return {"kernel": "dw_ln", "B": B, "Hs": Hs, "C": C, "us": t * 1e6, "GB/s": by / t / 1e9, "bytes": by}
+
+
 def bench_peak(args):
     out = {"kernel": f"tcgen05 instruction-rate probe {args.fmt}", "TFLOP/s_n128": ops.tensor_peak_tflops(args.fmt, 128),
            "TFLOP/s_n256": ops.tensor_peak_tflops(args.fmt, 256)}
@@ -129,18 +140,19 @@ def bench_peak(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "ln_quant", "quant_rows", "peak"])
+    ap.add_argument("what", choices=["gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak"])
     ap.add_argument("--fmt", default="nv4")
     ap.add_argument("--kind", default="fc1", choices=list(SHAPES))
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=1605)
     ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--hs", type=int, default=80, help="dw_ln: input grid side (output is 2x)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cold", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     args = ap.parse_args()
     torch.set_grad_enabled(False)
-    fn = {"gemm": bench_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "peak": bench_peak}[args.what]
+    fn = {"gemm": bench_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak}[args.what]
     print(json.dumps(fn(args)), flush=True)
 
 
