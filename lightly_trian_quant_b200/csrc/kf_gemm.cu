@@ -139,9 +139,9 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
   int by0, by1;
   if (g.out_fmt == KF_FMT_NV4) {
     uint32_t o[4];
-    const float tso = __ldg(g.tso);
-    quant_nv4<16>(va, am0, tso, div_true, o, by0);
-    quant_nv4<16>(vb, am1, tso, div_true, o + 2, by1);
+    const float tso = __ldg(g.tso), rcp_tso = __frcp_rn(tso);
+    quant_nv4_fast<16>(va, am0, tso, rcp_tso, o, by0);
+    quant_nv4_fast<16>(vb, am1, tso, rcp_tso, o + 2, by1);
     if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
     // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
     *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n0 >> 4, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
