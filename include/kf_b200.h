@@ -168,7 +168,7 @@ KF_API int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, int W
  * Replaces attn16_fwd / a16::fwd_kernel (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404). */
 KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream);
 
-/* Tensor-core instruction-rate probe: every SM issues `iters` x 4 tcgen05.mma (M=128, N=n, 32 K-bytes each) of the
+/* Tensor-core instruction-rate probe: every SM issues `iters` x 4 tcgen05.mma (M=128, N=n in {64,128,256}, 32 K-bytes each) of the
  * given operand format on shared-memory-resident operands; *flops_per_launch receives the FLOPs one launch performs.
  * sf_copies (0..8) scale-factor atoms are re-copied smem -> TMEM (tcgen05.cp) before every group of 4 MMAs, as a real
  * block-scaled main loop must (mx8: 2, mx4: 4, nv4: 8 at a 128 x 128 tile); 0 copies them once; 8 + c issues the c copies

