@@ -27,175 +27,9 @@
 // mgx_core.cu:308-426 and fp4g_core.cu:309-382.
 #include <mutex>
 
-#include "kf_sm100.cuh"
+#include "kf_gemm_epi.cuh"
 
 namespace kf {
-
-constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
-constexpr int BM = 128, BN = 256, BKB = 128;          // tile rows, tile columns, K bytes per stage
-constexpr int STAGES = 3;
-constexpr int A_BYTES = BM * BKB, TILE_BYTES = (BM + BN) * BKB;   // 16 KB of A, then 32 KB of W per stage
-constexpr int SF_STAGE_BYTES = 6144;                   // up to 4 atoms for A, then up to 4 + 4 for the two 128-row halves of W
-constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
-constexpr int EPI_WARPS = 16;
-constexpr int SF_WARP = 2 + EPI_WARPS;                 // warp index of the scale-factor copier
-constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);
-constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 48 columns each (A at +0, W at +16)
-constexpr int SF_BUF_COLS = 48;
-constexpr int TMEM_COLS = 512;
-constexpr int TMEM_SF_COL = 256;                       // accumulator: columns [0,256); scale factors from 256
-constexpr size_t GEMM_SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
-static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
-static_assert(TMEM_SF_COL + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
-
-struct GemmArgs {
-  const uint8_t *sfa, *sfw;
-  const float *ts_a, *ts_w, *bias, *gamma, *R, *sin, *cos, *tso;
-  void* C;
-  uint8_t *Qo, *SFo;
-  int M, N, K;
-  int Ntok, prefix, H, d;
-  int out_dtype, flags, out_fmt;
-  int m_tiles, n_tiles, k_tiles, nkb4;
-  int row_group, row_stride, row_offset;   // PLAIN: output row = (m / group) * stride + offset + m % group (group 0: identity)
-  unsigned int* err;
-};
-
-template <int KIND>
-struct KindTraits;
-template <>
-struct KindTraits<KIND_MX8> { static constexpr int ATOMS = 1; };   // 128 elements per stage = 4 k-blocks of 32
-template <>
-struct KindTraits<KIND_NV4> { static constexpr int ATOMS = 4; };   // 256 elements per stage = 16 k-blocks of 16
-template <>
-struct KindTraits<KIND_MX4> { static constexpr int ATOMS = 2; };   // 256 elements per stage = 8 k-blocks of 32
-template <>
-struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
-
-// ------------------------------------------------------------------------------------------------ epilogue pieces
-// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns per load).  Where global memory wants a
-// warp to touch consecutive addresses (the fp32 residual stream, the rotary tables), the warp restages a 32 x 32
-// chunk through a private shared-memory tile (128 bytes per row, 16-byte pieces XOR-swizzled by the row so both
-// directions are bank-conflict free) and continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4
-// columns 4*(l&7).. of row 4*i + (l>>3), so a warp instruction covers 4 rows x 128 contiguous bytes.
-__device__ __forceinline__ void stg_put(float* stg, int lane, const uint32_t (&r)[32]) {
-  uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-}
-__device__ __forceinline__ float4 stg_get(const float* stg, int lane, int i) {
-  const int row = 4 * i + (lane >> 3);
-  return reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)];
-}
-__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
-__device__ __forceinline__ float4 ld4_stream(const float* p) {   // read once: do not keep the line in L1
-  float4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
-  return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w));
-}
-__device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
-  uint2 o;
-  if (out_dtype == KF_BF16) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-    o.x = *reinterpret_cast<uint32_t*>(&a);
-    o.y = *reinterpret_cast<uint32_t*>(&b);
-  } else {
-    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-    o.x = *reinterpret_cast<uint32_t*>(&a);
-    o.y = *reinterpret_cast<uint32_t*>(&b);
-  }
-  return o;
-}
-
-// QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
-// or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
-__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, int m, int n0) {
-  const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
-  const bool ok = m < g.M;
-  float v[32];
-#pragma unroll
-  for (int q4 = 0; q4 < 8; ++q4) {
-    const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    v[4 * q4] = gelu_erf(fmaf(__uint_as_float(r[4 * q4]), ts, bb.x));
-    v[4 * q4 + 1] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 1]), ts, bb.y));
-    v[4 * q4 + 2] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 2]), ts, bb.z));
-    v[4 * q4 + 3] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 3]), ts, bb.w));
-  }
-  if (g.flags & KF_Q_ROUND_BF16) {
-#pragma unroll
-    for (int k = 0; k < 32; ++k) v[k] = bf16_round(v[k]);
-  }
-  float am0 = 0.f, am1 = 0.f;
-#pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    am0 = fmaxf(am0, fabsf(v[k]));
-    am1 = fmaxf(am1, fabsf(v[16 + k]));
-  }
-  const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
-  const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
-  int by0, by1;
-  if (g.out_fmt == KF_FMT_NV4) {
-    uint32_t o[4];
-    const float tso = __ldg(g.tso), rcp_tso = __frcp_rn(tso);
-    quant_nv4_fast<16>(va, am0, tso, rcp_tso, o, by0);
-    quant_nv4_fast<16>(vb, am1, tso, rcp_tso, o + 2, by1);
-    if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-    // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
-    *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n0 >> 4, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
-  } else if (g.out_fmt == KF_FMT_MX8) {
-    uint32_t o[8];
-    const float am = fmaxf(am0, am1);
-    quant_mx8<16>(va, am, div_true, o, by0);
-    quant_mx8<16>(vb, am, div_true, o + 4, by0);
-    if (ok) {
-      uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
-      p[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      p[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    }
-    g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
-  } else {
-    uint32_t o[4];
-    const float am = fmaxf(am0, am1);
-    quant_mx4<16>(va, am, div_true, o, by0);
-    quant_mx4<16>(vb, am, div_true, o + 2, by0);
-    if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
-    g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
-  }
-}
-
-// PLAIN epilogue of one 32-column chunk in the row layout: the thread writes 64 (16-bit) or 128 (fp32) contiguous bytes.
-__device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, uint8_t* dst_row, int n0) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float v[8];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float4 bb = g.bias ? ldg4(g.bias + n0 + 8 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float b4[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float a = __uint_as_float(r[8 * q + 4 * h + e]);
-        float x = (g.flags & KF_G_PRE_ROUND_BF16) ? bf16_round(a * ts) + b4[e] : fmaf(a, ts, b4[e]);   // the result may be rounded to bf16 before the bias
-        if (g.flags & KF_G_GELU) x = gelu_erf(x);
-        if (g.flags & KF_G_ROUND_BF16) x = bf16_round(x);
-        v[4 * h + e] = x;
-      }
-    }
-    if (dst_row) {
-      if (g.out_dtype == KF_F32) {
-        float4* d = reinterpret_cast<float4*>(dst_row + (size_t)(n0 + 8 * q) * 4);
-        d[0] = make_float4(v[0], v[1], v[2], v[3]);
-        d[1] = make_float4(v[4], v[5], v[6], v[7]);
-      } else {
-        const uint2 lo = pack4(make_float4(v[0], v[1], v[2], v[3]), g.out_dtype), hi = pack4(make_float4(v[4], v[5], v[6], v[7]), g.out_dtype);
-        *reinterpret_cast<uint4*>(dst_row + (size_t)(n0 + 8 * q) * 2) = make_uint4(lo.x, lo.y, hi.x, hi.y);
-      }
-    }
-  }
-}
 
 // ------------------------------------------------------------------------------------------------ the kernel
 template <int KIND, int EPI>
@@ -362,12 +196,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int cg = (warp - 2) >> 2;               // which 64-column group of the 256-column tile
     float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES);
-    const int c4 = 4 * (lane & 7);                // coalesced layout: this lane's 4 columns inside a 32-column chunk
-    const int rsub = lane >> 3;                   // coalesced layout: row 4*i + rsub in pass i
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
@@ -385,87 +216,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
       if (n0 >= g.N) continue;                                   // column group past N in the last column tile
 
-      if (EPI == KF_EPI_ROPE) {
-        // the 64 columns of this warp are one head of q, k or v: r0 = first half, r1 = second half.  Both halves go
-        // through the staging tile into the coalesced layout (the first stays in registers, the second is read back
-        // pass by pass), where the rotary tables and the output rows are read / written 4 rows x 128 bytes at a time.
-        const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
-        const int nbatch = g.M / g.Ntok;
-        const int b0 = rbase / g.Ntok, t0 = rbase - b0 * g.Ntok;   // one division per tile; rows advance from here
-        const float4 b_lo = g.bias ? ldg4(g.bias + n0 + c4) : z4, b_hi = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
-        float4 lo[8];
-        stg_put(stg, lane, r0);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) lo[i] = fma4(stg_get(stg, lane, i), ts, b_lo);
-        __syncwarp();
-        stg_put(stg, lane, r1);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = rbase + 4 * i + rsub;
-          if (m < g.M) {
-            int b = b0, t = t0 + 4 * i + rsub;
-            while (t >= g.Ntok) {
-              t -= g.Ntok;
-              ++b;
-            }
-            const float4 hi = fma4(stg_get(stg, lane, i), ts, b_hi);
-            float4 ol = lo[i], oh = hi;
-            if (which < 2 && t >= g.prefix) {
-              const float* tab = g.sin + (size_t)(t - g.prefix) * 64 + c4;
-              const float* tabc = g.cos + (size_t)(t - g.prefix) * 64 + c4;
-              const float4 sl = ldg4(tab), cl = ldg4(tabc), sh = ldg4(tab + 32), ch = ldg4(tabc + 32);
-              // lo' = lo*cos - hi*sin (tables of columns 0..31), hi' = hi*cos + lo*sin (tables of columns 32..63)
-              ol = make_float4(lo[i].x * cl.x - hi.x * sl.x, lo[i].y * cl.y - hi.y * sl.y, lo[i].z * cl.z - hi.z * sl.z, lo[i].w * cl.w - hi.w * sl.w);
-              oh = make_float4(hi.x * ch.x + lo[i].x * sh.x, hi.y * ch.y + lo[i].y * sh.y, hi.z * ch.z + lo[i].z * sh.z, hi.w * ch.w + lo[i].w * sh.w);
-            }
-            uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + c4) * 2;
-            *reinterpret_cast<uint2*>(dst) = pack4(ol, g.out_dtype);
-            *reinterpret_cast<uint2*>(dst + 64) = pack4(oh, g.out_dtype);
-          }
-        }
-        __syncwarp();                                             // the staging tile is reused by the next tile
-      } else if (EPI == KF_EPI_RES) {
-        // two 32-column chunks, each restaged so that the fp32 residual is read and written 128 contiguous bytes per row
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int n = n0 + 32 * c + c4;
-          stg_put(stg, lane, c == 0 ? r0 : r1);
-          __syncwarp();
-          const float4 b4 = g.bias ? ldg4(g.bias + n) : z4, g4 = ldg4(g.gamma + n);
-#pragma unroll
-          for (int hp = 0; hp < 2; ++hp) {                        // four passes at a time: loads first, then the math
-            float4 rr[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int m = rbase + 4 * (4 * hp + i) + rsub;
-              rr[i] = m < g.M ? ld4_stream(g.R + (size_t)m * g.N + n) : z4;
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int m = rbase + 4 * (4 * hp + i) + rsub;
-              const float4 v = fma4(stg_get(stg, lane, 4 * hp + i), ts, b4);
-              if (m < g.M)
-                *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
-                    make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
-            }
-          }
-          __syncwarp();                                           // the staging tile is reused by the next chunk
-        }
-      } else if (EPI == KF_EPI_PLAIN) {
-        const int m = rbase + lane;
-        uint8_t* dst_row = nullptr;
-        if (m < g.M) {
-          const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
-          dst_row = static_cast<uint8_t*>(g.C) + (size_t)orow * g.N * (g.out_dtype == KF_F32 ? 4 : 2);
-        }
-        plain_chunk(g, r0, ts, dst_row, n0);
-        plain_chunk(g, r1, ts, dst_row, n0 + 32);
-      } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-        quant_chunk(g, r0, ts, rbase + lane, n0);
-        quant_chunk(g, r1, ts, rbase + lane, n0 + 32);
-      }
+      epilogue_math<EPI>(g, r0, r1, ts, rbase, n0, stg, lane);
     }
   }
 
@@ -560,6 +311,16 @@ static int launch_gemm_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& t
 
 static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+int launch_gemm_pair(int fmt, int epi, const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g, int sms, cudaStream_t st);   // kf_gemm2.cu
+
+// The CTA-pair kernel (256 x 256 tiles, kf_gemm2.cu) is selected with KF_GEMM_PAIR=1 in the environment (read at every
+// call, so a test can switch it).  It is off by default: its cross-CTA hand-shakes (stage landed / stage free, relayed
+// through remote mbarrier arrivals) make its main loop slower than the one-CTA kernel's at the ViT shapes.
+static bool pair_mode() {
+  const char* e = getenv("KF_GEMM_PAIR");
+  return e != nullptr && e[0] == '1';
+}
+
 }  // namespace kf
 
 using namespace kf;
@@ -598,7 +359,8 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   CUtensorMap tmA, tmW;
   int st = make_tmap_2d_bytes(&tmA, p->A, (uint64_t)p->M, kbytes, kbytes, BM);
   if (st != KF_OK) return st;
-  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, BN);
+  const bool pair = pair_mode();
+  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, pair ? 128 : BN);
   if (st != KF_OK) return st;
   GemmArgs g{};
   g.sfa = static_cast<const uint8_t*>(p->SFA);
@@ -619,6 +381,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   const int total = g.m_tiles * g.n_tiles;
   const int grid = total < sms ? total : sms;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (pair) return launch_gemm_pair(fmt, epi, tmA, tmW, g, sms, cs);
   switch (fmt) {
     case KF_FMT_MX8: return launch_gemm_epi<KIND_MX8>(epi, tmA, tmW, g, grid, cs);
     case KF_FMT_NV4: return launch_gemm_epi<KIND_NV4>(epi, tmA, tmW, g, grid, cs);
