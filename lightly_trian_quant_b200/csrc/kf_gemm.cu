@@ -37,12 +37,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
+  constexpr int STAGES = Pipe<EPI>::STAGES;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
   uint8_t* stg_all = sfs + (size_t)STAGES * SF_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + EPI_WARPS * STG_WARP_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + Pipe<EPI>::STG_BYTES);
   uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = tfull + 1;
   uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
@@ -195,7 +196,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 64-column group)
     const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int cg = (warp - 2) >> 2;               // which 64-column group of the 256-column tile
-    float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES);
+    float* stg = Pipe<EPI>::STAGING ? reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES) : nullptr;
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
@@ -291,11 +292,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Pipe<EPI>::SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmW, g);
+  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, Pipe<EPI>::SMEM, st>>>(tmA, tmW, g);
   return cuda_status(cudaGetLastError(), "kf_gemm_bs launch");
 }
 

@@ -20,10 +20,13 @@
 
 namespace kf {
 
-constexpr int P_STAGES = 4;
 constexpr int P_TILE_BYTES = 2 * 128 * BKB;              // 16 KB of A rows + 16 KB of W rows per CTA and stage
-constexpr int P_SMEM = P_STAGES * (P_TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 512;
-static_assert(P_SMEM <= 227 * 1024, "shared memory budget");
+template <int EPI>
+struct PairPipe {                                        // as many stages as fit beside the staging tiles of RES / ROPE: 4, or 5 without
+  static constexpr int STG_BYTES = Pipe<EPI>::STG_BYTES;
+  static constexpr int STAGES = (227 * 1024 - 512 - STG_BYTES) / (P_TILE_BYTES + SF_STAGE_BYTES);
+  static constexpr int SMEM = STAGES * (P_TILE_BYTES + SF_STAGE_BYTES) + STG_BYTES + 512;
+};
 
 template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
@@ -31,12 +34,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmSW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
+  constexpr int P_STAGES = PairPipe<EPI>::STAGES;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)P_STAGES * P_TILE_BYTES;
   uint8_t* stg_all = sfs + (size_t)P_STAGES * SF_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + EPI_WARPS * STG_WARP_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + PairPipe<EPI>::STG_BYTES);
   uint64_t *full = bars, *empty = full + P_STAGES, *tfull = empty + P_STAGES, *tempty = tfull + 1;
   uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
@@ -204,7 +208,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ epilogue: 16 warps per CTA, warp = (TMEM lane quarter, 64-column group)
     const int quarter = warp & 3;
     const int cg = (warp - 2) >> 2;
-    float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES);
+    float* stg = Pipe<EPI>::STAGING ? reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES) : nullptr;
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
@@ -249,11 +253,11 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUt
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairPipe<EPI>::SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_pair_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  gemm_pair_kernel<KIND, EPI><<<grid, GEMM_THREADS, P_SMEM, st>>>(tmA, tmW, tmSA, tmSW, g);
+  gemm_pair_kernel<KIND, EPI><<<grid, GEMM_THREADS, PairPipe<EPI>::SMEM, st>>>(tmA, tmW, tmSA, tmSW, g);
   return cuda_status(cudaGetLastError(), "kf_gemm_bs (pair) launch");
 }
 

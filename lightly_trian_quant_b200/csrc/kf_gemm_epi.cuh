@@ -9,7 +9,6 @@ namespace kf {
 
 constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX4, KIND_BF16 = KF_FMT_BF16;
 constexpr int BM = 128, BN = 256, BKB = 128;          // tile rows, tile columns, K bytes per stage
-constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * BKB, TILE_BYTES = (BM + BN) * BKB;   // 16 KB of A, then 32 KB of W per stage
 constexpr int SF_STAGE_BYTES = 6144;                   // up to 4 atoms for A, then up to 4 + 4 for the two 128-row halves of W
 constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
@@ -20,8 +19,16 @@ constexpr int SF_BUFS = 4;                             // scale-factor buffers i
 constexpr int SF_BUF_COLS = 48;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;                       // accumulator: columns [0,256); scale factors from 256
-constexpr size_t GEMM_SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * STG_WARP_BYTES + 256;
-static_assert(GEMM_SMEM <= 227 * 1024, "shared memory budget");
+// Only the epilogues that restage through shared memory (RES, ROPE) reserve the 64 KB of staging tiles.  A fourth
+// pipeline stage in the space the others save was measured: no gain for the block-scaled kinds (NVFP4 plain 111 vs 104 us),
+// 5 % for bf16, so all kernels run 3 stages.
+template <int EPI>
+struct Pipe {
+  static constexpr bool STAGING = EPI == KF_EPI_RES || EPI == KF_EPI_ROPE;
+  static constexpr int STG_BYTES = STAGING ? EPI_WARPS * STG_WARP_BYTES : 0;
+  static constexpr int STAGES = 3;
+  static constexpr size_t SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + STG_BYTES + 256;
+};
 static_assert(TMEM_SF_COL + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
 
 struct GemmArgs {
