@@ -194,3 +194,40 @@ def test_gemm_vitl_shapes_batch8(fmt, kind):
     ops.quant_rows(x[:128].cuda(), a1)
     y1 = ops.gemm_plain(a1, W, out_dtype=torch.float32)
     assert torch.equal(y1, y[:128])
+
+
+@pytest.mark.parametrize("fmt", ["nv4", "mx8", "mx4", "bf16"])
+def test_gemm_pair_kernel_is_bitwise_the_one_cta_kernel(fmt, monkeypatch):
+    """The CTA-pair kernel (cta_group::2, 256 x 256 tiles, KF_GEMM_PAIR=1) accumulates in the same K order and shares
+    the epilogues: PLAIN, RES and QUANT outputs must be bit-identical to the one-CTA kernel's, on a shape with an odd
+    number of row blocks (the follower of the last pair has no rows) and a 128-column tail tile."""
+    ops = _ops()
+    M, N, K = 600, 384, 1024
+    x, w = _mk_x(M, K, 21), _mk_w(N, K, 22, std=0.05)
+    a, W, _, _ = _quant_pair(x, w, fmt)
+    g = torch.Generator().manual_seed(23)
+    bias, gamma = (torch.randn(N, generator=g) * 0.1).cuda(), torch.rand(N, generator=g).cuda()
+    res = torch.randn(M, N, generator=g).cuda()
+
+    def run():
+        out = {"plain": ops.gemm_plain(a, W, bias, out_dtype=torch.bfloat16), "res": ops.gemm_res(a, W, bias, gamma, res.clone())}
+        if fmt != "bf16":
+            q = ops.ActBuf(M, N, fmt, device="cuda")
+            if fmt == "nv4":
+                q.ts.fill_(0.01)
+            ops.gemm_gelu_q(a, W, bias, q, round_bf16=True)
+            out["q"], out["sf"] = q.q.clone(), q.sf.clone()
+        ops.check_device_error()
+        return out
+
+    monkeypatch.setenv("KF_GEMM_PAIR", "0")
+    one = run()
+    monkeypatch.setenv("KF_GEMM_PAIR", "1")
+    two = run()
+    for k in one:
+        assert torch.equal(one[k], two[k]), k
+    # and against the oracle, so that both are not wrong together
+    ad = x.float().numpy() if fmt == "bf16" else go.dequant_operand(a.q.cpu().numpy(), a.sf.cpu().numpy(), a.ts.cpu().numpy() if a.ts is not None else None, fmt, M, K)
+    wd = w.float().numpy() if fmt == "bf16" else go.dequant_operand(W.q.cpu().numpy(), W.sf.cpu().numpy(), W.ts.cpu().numpy() if W.ts is not None else None, fmt, N, K)
+    ref = go.matmul_ref(ad, wd) + bias.cpu().numpy().astype(np.float64)
+    assert go.rel_fro(two["plain"].float().cpu().numpy(), ref) < 2e-3
