@@ -33,8 +33,9 @@ __global__ void __launch_bounds__(256) im2col16_kernel(const __nv_bfloat16* __re
 // Persistent CTAs, one tile of 4 x 8 output pixels at a time.  The channels go through in slabs of 128: the 6 x 10 halo
 // of a slab (256 contiguous bytes per pixel) is fetched with 16-byte cp.async copies (zero fill outside the image) into
 // a 3-deep shared-memory ring that runs ahead across slabs AND tiles, so two slabs are always in flight while a third is
-// convolved; each thread convolves 8 channels of 2 pixels with the 72 tap weights held in registers; the conv results of
-// all C channels stay in shared memory for the two-pass LayerNorm statistics.
+// convolved; each thread convolves 8 channels of 2 adjacent pixels (one 3 x 4 window read for both) with the 72 tap weights
+// held in registers; the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics, which
+// each lane then works out on register-resident values.
 constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 128, DW_RING = 3;
 constexpr int DW_SLAB_BYTES = DW_HW * DW_CH * 2;        // 15 KB
 
@@ -82,23 +83,35 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
   const int t = threadIdx.x;
   const int Ho = 2 * Hs, Wo = 2 * Ws;
   const int C8 = C >> 3, S = C / DW_CH;
-  const int grp = t & 15, prow = t >> 4;                                     // 8-channel group of the slab, pixel sub-index 0..15
+  // conv work item of this thread: 8 channels (grp) of two horizontally adjacent pixels (oy, ox0), (oy, ox0 + 1): the 3 x 4
+  // input window is read and unpacked once for both
+  const int grp = t & 15, strip = t >> 4;
+  const int oy = strip >> 2, ox0 = (strip & 3) * 2;
 
-  // issue cursor (runs two slabs ahead of the consume cursor, across tile boundaries)
+  // issue cursor (runs two slabs ahead of the consume cursor, across tile boundaries).  The (pixel, 16-byte piece)
+  // pairs a thread copies are the same for every slab of a tile: their source offsets are worked out once per tile.
   int i_tile = blockIdx.x, i_slab = 0, i_slot = 0;
+  int64_t i_src[4];
+  bool i_in[4];
   auto issue = [&]() {
     if (i_tile < total_tiles) {
-      const DwTile T = dw_tile(i_tile, tiles_x, tiles_y);
-      uint4* act = reinterpret_cast<uint4*>(dsm + i_slot * DW_SLAB_BYTES);
-      for (int idx = t; idx < DW_HW * 16; idx += 256) {
-        const int px = idx >> 4, q = idx & 15;
-        const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
-        const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
-        const bool in = Y >= 0 && Y < Ho && X >= 0 && X < Wo;
-        const int64_t row = in ? ((int64_t)T.b * Hs + (Y >> 1)) * Ws + (X >> 1) : 0;
-        const __nv_bfloat16* src = g + row * 4 * C + (in ? ((Y & 1) * 2 + (X & 1)) * C : 0) + i_slab * DW_CH + q * 8;
-        cp_async16_zfill(act + idx, src, in);
+      if (i_slab == 0) {
+        const DwTile T = dw_tile(i_tile, tiles_x, tiles_y);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int idx = t + 256 * k;
+          const int px = idx >> 4, q = idx & 15;
+          const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
+          const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
+          i_in[k] = idx < DW_HW * 16 && Y >= 0 && Y < Ho && X >= 0 && X < Wo;
+          const int64_t row = i_in[k] ? ((int64_t)T.b * Hs + (Y >> 1)) * Ws + (X >> 1) : 0;
+          i_src[k] = row * 4 * C + (i_in[k] ? ((Y & 1) * 2 + (X & 1)) * C : 0) + q * 8;
+        }
       }
+      uint4* act = reinterpret_cast<uint4*>(dsm + i_slot * DW_SLAB_BYTES);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (t + 256 * k < DW_HW * 16) cp_async16_zfill(act + t + 256 * k, g + i_src[k] + i_slab * DW_CH, i_in[k]);
       if (++i_slab == S) {
         i_slab = 0;
         i_tile += gridDim.x;
@@ -113,6 +126,7 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
   int c_slot = 0;
   const int warp = t >> 5, lane = t & 31;
   const float invC = 1.0f / (float)C;
+  const int nk = C8 >> 5;                                    // 256-channel steps of the LayerNorm: lane owns 8 channels in each
   for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
     const DwTile T = dw_tile(tile, tiles_x, tiles_y);
     for (int sl = 0; sl < S; ++sl) {
@@ -138,72 +152,83 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
         }
         __syncthreads();
       }
-      // ---- the 9 x 8 tap weights of this thread's channel group
-      float w[9][8];
+      // ---- depthwise 3x3 of the two pixels: taps accumulate in (ky, kx) order for each of them; the 3 x 8 tap weights of
+      // a kernel row are fetched when that row is due (72 weights at once would not fit the register budget)
+      float acc0[8], acc1[8];
 #pragma unroll
-      for (int k = 0; k < 9; ++k) {
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8)), w1 = __ldg(reinterpret_cast<const float4*>(dww + k * C + ch + grp * 8) + 1);
-        w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
-      }
-      // ---- depthwise 3x3: thread = (8 channels, pixels prow and prow + 16)
+      for (int k = 0; k < 8; ++k) acc0[k] = acc1[k] = 0.f;
 #pragma unroll
-      for (int k2 = 0; k2 < 2; ++k2) {
-        const int px = prow + 16 * k2;
-        const int oy = px / DW_TW, ox = px - oy * DW_TW;
-        float acc[8];
+      for (int ky = 0; ky < 3; ++ky) {
+        float w[3][8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        for (int k = 0; k < 3; ++k) {
+          const float4* wp = reinterpret_cast<const float4*>(dww + (ky * 3 + k) * C + ch + grp * 8);
+          const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+          w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
+        }
 #pragma unroll
-        for (int ky = 0; ky < 3; ++ky)
+        for (int cx = 0; cx < 4; ++cx) {
+          float f[8];
+          bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox0 + cx) * 16 + grp], f);
+          if (cx < 3) {
 #pragma unroll
-          for (int kx = 0; kx < 3; ++kx) {
-            float f[8];
-            bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox + kx) * 16 + grp], f);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = fmaf(f[k], w[ky * 3 + kx][k], acc[k]);
+            for (int k = 0; k < 8; ++k) acc0[k] = fmaf(f[k], w[cx][k], acc0[k]);
           }
-        res[px * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc);
+          if (cx > 0) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc1[k] = fmaf(f[k], w[cx - 1][k], acc1[k]);
+          }
+        }
       }
+      res[(oy * DW_TW + ox0) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc0);
+      res[(oy * DW_TW + ox0 + 1) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc1);
       if (++c_slot == DW_RING) c_slot = 0;
     }
     __syncthreads();                                          // all conv results of the tile are in res
 
-    // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels, lane = 8 channels per 256-channel step
+    // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels; the lane's channels stay in registers
     for (int px = warp; px < DW_TH * DW_TW; px += 8) {
-      const int oy = px / DW_TW, ox = px - oy * DW_TW;
-      const int Y = T.Y0 + oy, X = T.X0 + ox;
+      const int py = px / DW_TW, pxx = px - py * DW_TW;
+      const int Y = T.Y0 + py, X = T.X0 + pxx;
       const uint4* r = res + px * C8;
+      float v[4][8];
       float s = 0.f;
-      for (int i = lane; i < C8; i += 32) {
-        float f[8];
-        bf16x8_to_f32(r[i], f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) s += f[k];
+      for (int k = 0; k < 4; ++k) {
+        if (k < nk) {
+          bf16x8_to_f32(r[lane + 32 * k], v[k]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s += v[k][e];
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       const float mean = s * invC;
       float ss = 0.f;
-      for (int i = lane; i < C8; i += 32) {
-        float f[8];
-        bf16x8_to_f32(r[i], f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss = fmaf(f[k] - mean, f[k] - mean, ss);
+      for (int k = 0; k < 4; ++k) {
+        if (k < nk) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss = fmaf(v[k][e] - mean, v[k][e] - mean, ss);
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       const float rstd = rsqrtf(ss * invC + eps);
       if (Y < Ho && X < Wo) {
         uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)T.b * Ho + Y) * Wo + X) * C);
-        for (int i = lane; i < C8; i += 32) {
-          float f[8];
-          bf16x8_to_f32(r[i], f);
-          const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
-          const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
-          const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-          for (int k = 0; k < 8; ++k) f[k] = (f[k] - mean) * rstd * ww[k] + cc[k];
-          dst[i] = f32_to_bf16x8(f);
+        for (int k = 0; k < 4; ++k) {
+          if (k < nk) {
+            const int i = lane + 32 * k;
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
+            const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = (v[k][e] - mean) * rstd * ww[e] + cc[e];
+            dst[i] = f32_to_bf16x8(f);
+          }
         }
       }
     }
