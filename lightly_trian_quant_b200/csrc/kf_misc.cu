@@ -257,22 +257,55 @@ __global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __re
     for (int c = 0; c < ncls1; ++c) prob[q * ncls1 + c] = v[c] / s;
   }
   __syncthreads();
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  // two adjacent pixels per thread (one 32-bit load per query when HW is even); sigmoid by exp2 / reciprocal approximations
+  const int p = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (p >= HW) return;
-  float acc[8];
-  for (int c = 0; c < ncls1; ++c) acc[c] = 0.f;
+  const bool two = p + 1 < HW, vec = two && (HW & 1) == 0;
+  float acc0[8], acc1[8];                      // static indices only (loops over 8 with a guard) so that they stay in registers
+#pragma unroll
+  for (int c = 0; c < 8; ++c) acc0[c] = acc1[c] = 0.f;
   const __nv_bfloat16* m = ml + (int64_t)b * Q * HW + p;
   for (int q = 0; q < Q; ++q) {
-    const float x = __bfloat162float(m[(int64_t)q * HW]);
-    const float sg = 1.0f / (1.0f + expf(-x));
-    for (int c = 0; c < ncls1; ++c) acc[c] = fmaf(sg, prob[q * ncls1 + c], acc[c]);
+    float x0, x1 = 0.f;
+    if (vec) {
+      const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(m + (int64_t)q * HW));
+      x0 = __uint_as_float(u << 16);
+      x1 = __uint_as_float(u & 0xFFFF0000u);
+    } else {
+      x0 = __bfloat162float(m[(int64_t)q * HW]);
+      if (two) x1 = __bfloat162float(m[(int64_t)q * HW + 1]);
+    }
+    float e0, e1, s0, s1;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 * -1.4426950408889634f));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s0) : "f"(1.0f + e0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s1) : "f"(1.0f + e1));
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c < ncls1) {
+        const float pr = prob[q * ncls1 + c];
+        acc0[c] = fmaf(s0, pr, acc0[c]);
+        acc1[c] = fmaf(s1, pr, acc1[c]);
+      }
+    }
   }
-  int best = 0;
-  for (int c = 0; c < ncls1; ++c) {
-    if (scores) scores[((int64_t)b * ncls1 + c) * HW + p] = acc[c];
-    if (c < ncls1 - 1 && acc[c] > acc[best]) best = c;
+  int best0 = 0, best1 = 0;
+  float bv0 = acc0[0], bv1 = acc1[0];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    if (c < ncls1) {
+      if (scores) {
+        scores[((int64_t)b * ncls1 + c) * HW + p] = acc0[c];
+        if (two) scores[((int64_t)b * ncls1 + c) * HW + p + 1] = acc1[c];
+      }
+      if (c < ncls1 - 1 && acc0[c] > bv0) { bv0 = acc0[c]; best0 = c; }      // first maximum wins, as torch.argmax
+      if (c < ncls1 - 1 && acc1[c] > bv1) { bv1 = acc1[c]; best1 = c; }
+    }
   }
-  if (labels) labels[(int64_t)b * HW + p] = (uint8_t)best;
+  if (labels) {
+    labels[(int64_t)b * HW + p] = (uint8_t)best0;
+    if (two) labels[(int64_t)b * HW + p + 1] = (uint8_t)best1;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ resize + normalise
@@ -288,22 +321,52 @@ __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restr
   const int y0 = max((int)(cy - supy + 0.5f), 0), y1 = min((int)(cy + supy + 0.5f), Hi);
   const int x0 = max((int)(cx - supx + 0.5f), 0), x1 = min((int)(cx + supx + 0.5f), Wi);
   float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, wsum = 0.f;
+  // horizontal tap weights once per output pixel (up to 16 taps in registers; wider windows take the generic loop)
+  constexpr int MAXT = 16;
+  const int nx = x1 - x0;
+  const float isx = 1.0f / supx, isy = 1.0f / supy;
   float wxs = 0.f;
-  for (int x = x0; x < x1; ++x) wxs += fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) / supx));
-  for (int y = y0; y < y1; ++y) {
-    const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) / supy));
-    const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi) * 3;
-    float r0 = 0.f, r1 = 0.f, r2 = 0.f;
-    for (int x = x0; x < x1; ++x) {
-      const float wx = fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) / supx));
-      r0 = fmaf(wx, (float)row[x * 3], r0);
-      r1 = fmaf(wx, (float)row[x * 3 + 1], r1);
-      r2 = fmaf(wx, (float)row[x * 3 + 2], r2);
+  if (nx <= MAXT) {
+    float wx[MAXT];
+#pragma unroll
+    for (int k = 0; k < MAXT; ++k) {
+      wx[k] = k < nx ? fmaxf(0.f, 1.f - fabsf((x0 + k + 0.5f - cx) * isx)) : 0.f;
+      wxs += wx[k];
     }
-    acc0 = fmaf(wy, r0, acc0);
-    acc1 = fmaf(wy, r1, acc1);
-    acc2 = fmaf(wy, r2, acc2);
-    wsum += wy;
+    for (int y = y0; y < y1; ++y) {
+      const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
+      const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi + x0) * 3;
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < MAXT; ++k) {
+        if (k < nx) {
+          r0 = fmaf(wx[k], (float)row[k * 3], r0);
+          r1 = fmaf(wx[k], (float)row[k * 3 + 1], r1);
+          r2 = fmaf(wx[k], (float)row[k * 3 + 2], r2);
+        }
+      }
+      acc0 = fmaf(wy, r0, acc0);
+      acc1 = fmaf(wy, r1, acc1);
+      acc2 = fmaf(wy, r2, acc2);
+      wsum += wy;
+    }
+  } else {
+    for (int x = x0; x < x1; ++x) wxs += fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) * isx));
+    for (int y = y0; y < y1; ++y) {
+      const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
+      const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi) * 3;
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f;
+      for (int x = x0; x < x1; ++x) {
+        const float wx = fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) * isx));
+        r0 = fmaf(wx, (float)row[x * 3], r0);
+        r1 = fmaf(wx, (float)row[x * 3 + 1], r1);
+        r2 = fmaf(wx, (float)row[x * 3 + 2], r2);
+      }
+      acc0 = fmaf(wy, r0, acc0);
+      acc1 = fmaf(wy, r1, acc1);
+      acc2 = fmaf(wy, r2, acc2);
+      wsum += wy;
+    }
   }
   const float inv = 1.0f / (wsum * wxs * 255.f);
   const int64_t plane = (int64_t)So * So;
@@ -361,7 +424,7 @@ extern "C" int kf_semantic(const void* mask_logits, const void* class_logits, in
   KF_REQUIRE(B >= 0 && Q > 0 && HW > 0 && ncls >= 1 && ncls <= 7, "kf_semantic: bad shape B=%d Q=%d ncls=%d HW=%d", B, Q, ncls, HW);
   if (B == 0) return KF_OK;
   KF_REQUIRE(mask_logits && class_logits && (scores || labels), "kf_semantic: null tensor pointer");
-  dim3 grid((HW + 255) / 256, B);
+  dim3 grid((HW + 511) / 512, B);
   semantic_kernel<<<grid, 256, (size_t)Q * (ncls + 1) * 4, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(mask_logits), static_cast<const __nv_bfloat16*>(class_logits), Q, ncls + 1, HW, scores, labels);
   return cuda_status(cudaGetLastError(), "kf_semantic launch");
