@@ -296,7 +296,11 @@ def main():
             achieved = flops / (classes[gname]["ms"] * 1e-3) / 1e12
             peak = ops.tensor_peak_tflops(fmt, 256)
             nominal = {"nv4": 9000.0, "mx4": 9000.0, "mx8": 4500.0, "bf16": 2250.0}[fmt]
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+            # DRAM bytes per launch of the dominant kernel: ncu figure per token row (profiles/gemm_nv4_block_dram_traffic.md:
+            # 4987 B per row and launch, averaged over qkv / proj / fc1 / fc2 at 22 470 rows) times the mean rows per launch here
+            rows_mean = B * ((cfg.depth - cfg.num_joint_blocks) * (5 + (SIZE // 16) ** 2) + cfg.num_joint_blocks * (5 + (SIZE // 16) ** 2 + cfg.num_queries)) / cfg.depth
+            traffic = 4987.0 * rows_mean if fmt == "nv4" else None
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                     "kernel": f"gemm_kernel<{fmt}> (qkv, proj, fc1, fc2 of all blocks; {classes[gname]['launches']} launches per step)",
                     "peak_source": f"tcgen05 {fmt} instruction-rate probe (M=128, N=256 as in the kernel, shared-memory-resident operands) measured in this run; "
                                    f"MEASURED_PEAKS.json has no {fmt} figure (bf16 burst {peaks['bf16_tflops'] if peaks else 'n/a'} TFLOP/s of measured); "
