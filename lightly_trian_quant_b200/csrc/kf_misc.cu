@@ -311,50 +311,82 @@ __global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __re
 // ------------------------------------------------------------------------------------------------ resize + normalise
 // frames uint8 [B, Hi, Wi, 3] (HWC) -> bf16 [B, 3, So, So]: separable triangle filter with support scaled by the
 // down-sampling factor (bilinear with antialiasing, align_corners = false), then (v/255 - mean[c]) / std[c].
+// One CTA = 256 consecutive pixels of one output row.  Pass 1: the vertical filter over the input rows of the window, for
+// every input byte of the CTA's horizontal span (threads walk the span four bytes at a time, so the loads are coalesced
+// 32-bit words), result as floats in shared memory.  Pass 2: each thread applies its horizontal taps to the three
+// channels from shared memory.  Spans that do not fit the buffer (extreme down-scaling) take the direct path.
+constexpr int RS_SPAN = 4096;                            // bytes of one input row a CTA can stage (256 outputs at up to 5x down-scaling)
+
 __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restrict__ src, __nv_bfloat16* __restrict__ dst, int Hi, int Wi, int So,
                                                           float m0, float m1, float m2, float s0, float s1, float s2) {
+  __shared__ float vbuf[RS_SPAN];
   const int ox = blockIdx.x * blockDim.x + threadIdx.x, oy = blockIdx.y, b = blockIdx.z;
-  if (ox >= So) return;
   const float sy = (float)Hi / So, sx = (float)Wi / So;
   const float supy = fmaxf(sy, 1.f), supx = fmaxf(sx, 1.f);
-  const float cy = (oy + 0.5f) * sy, cx = (ox + 0.5f) * sx;
-  const int y0 = max((int)(cy - supy + 0.5f), 0), y1 = min((int)(cy + supy + 0.5f), Hi);
-  const int x0 = max((int)(cx - supx + 0.5f), 0), x1 = min((int)(cx + supx + 0.5f), Wi);
-  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, wsum = 0.f;
-  // horizontal tap weights once per output pixel (up to 16 taps in registers; wider windows take the generic loop)
-  constexpr int MAXT = 16;
-  const int nx = x1 - x0;
   const float isx = 1.0f / supx, isy = 1.0f / supy;
-  float wxs = 0.f;
-  if (nx <= MAXT) {
-    float wx[MAXT];
-#pragma unroll
-    for (int k = 0; k < MAXT; ++k) {
-      wx[k] = k < nx ? fmaxf(0.f, 1.f - fabsf((x0 + k + 0.5f - cx) * isx)) : 0.f;
-      wxs += wx[k];
-    }
-    for (int y = y0; y < y1; ++y) {
-      const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
-      const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi + x0) * 3;
-      float r0 = 0.f, r1 = 0.f, r2 = 0.f;
-#pragma unroll
-      for (int k = 0; k < MAXT; ++k) {
-        if (k < nx) {
-          r0 = fmaf(wx[k], (float)row[k * 3], r0);
-          r1 = fmaf(wx[k], (float)row[k * 3 + 1], r1);
-          r2 = fmaf(wx[k], (float)row[k * 3 + 2], r2);
-        }
+  const float cy = (oy + 0.5f) * sy;
+  const int y0 = max((int)(cy - supy + 0.5f), 0), y1 = min((int)(cy + supy + 0.5f), Hi);
+  auto xwin = [&](int o, int& a, int& e, float& c) {
+    c = (o + 0.5f) * sx;
+    a = max((int)(c - supx + 0.5f), 0);
+    e = min((int)(c + supx + 0.5f), Wi);
+  };
+  // horizontal span of the CTA in input pixels, its byte range rounded out to 4-byte words of the row
+  const int o_first = blockIdx.x * blockDim.x, o_last = min(o_first + (int)blockDim.x, So) - 1;
+  int xa, xe, xt;
+  float ct;
+  xwin(o_first, xa, xt, ct);
+  xwin(o_last, xt, xe, ct);
+  float wsum = 0.f;
+  for (int y = y0; y < y1; ++y) wsum += fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
+  const int64_t row0 = ((int64_t)b * Hi) * Wi * 3;       // byte offset of the image
+  const int64_t byte_a = (int64_t)xa * 3, byte_e = (int64_t)xe * 3;
+  // word alignment is decided on absolute byte offsets (src is 16-byte aligned per frame batch; rows need not be)
+  const bool staged = (byte_e - byte_a) + 8 <= RS_SPAN;
+  const uintptr_t buf_end = reinterpret_cast<uintptr_t>(src) + (uintptr_t)gridDim.z * Hi * Wi * 3;
+  if (staged) {
+    const int nbytes = (int)(byte_e - byte_a);
+    for (int j4 = threadIdx.x * 4; j4 < nbytes + 3; j4 += blockDim.x * 4) {
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int y = y0; y < y1; ++y) {
+        const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
+        // four consecutive bytes from two aligned 32-bit words (rows are not word aligned in general); words that start
+        // past the end of the whole batch are not read
+        const int64_t off = row0 + (int64_t)y * Wi * 3 + byte_a + j4;
+        const uintptr_t ad = reinterpret_cast<uintptr_t>(src) + off;
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(ad & ~(uintptr_t)3);
+        const uint32_t w0 = reinterpret_cast<uintptr_t>(wp) < buf_end ? __ldg(wp) : 0u;
+        const uint32_t w1 = reinterpret_cast<uintptr_t>(wp + 1) < buf_end ? __ldg(wp + 1) : 0u;
+        const uint32_t four = __funnelshift_r(w0, w1, (uint32_t)(ad & 3) * 8);
+        const uint32_t v0 = four & 0xFF, v1 = (four >> 8) & 0xFF, v2 = (four >> 16) & 0xFF, v3 = four >> 24;
+        a0 = fmaf(wy, (float)v0, a0);
+        a1 = fmaf(wy, (float)v1, a1);
+        a2 = fmaf(wy, (float)v2, a2);
+        a3 = fmaf(wy, (float)v3, a3);
       }
-      acc0 = fmaf(wy, r0, acc0);
-      acc1 = fmaf(wy, r1, acc1);
-      acc2 = fmaf(wy, r2, acc2);
-      wsum += wy;
+      vbuf[j4] = a0; vbuf[j4 + 1] = a1; vbuf[j4 + 2] = a2; vbuf[j4 + 3] = a3;
+    }
+    __syncthreads();
+  }
+  if (ox >= So) return;
+  int x0, x1;
+  float cx;
+  xwin(ox, x0, x1, cx);
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, wxs = 0.f;
+  if (staged) {
+    const float* vb = vbuf + (x0 - xa) * 3;
+    for (int x = x0; x < x1; ++x, vb += 3) {
+      const float wx = fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) * isx));
+      wxs += wx;
+      acc0 = fmaf(wx, vb[0], acc0);
+      acc1 = fmaf(wx, vb[1], acc1);
+      acc2 = fmaf(wx, vb[2], acc2);
     }
   } else {
     for (int x = x0; x < x1; ++x) wxs += fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) * isx));
     for (int y = y0; y < y1; ++y) {
       const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
-      const uint8_t* row = src + (((int64_t)b * Hi + y) * Wi) * 3;
+      const uint8_t* row = src + row0 + (int64_t)y * Wi * 3;
       float r0 = 0.f, r1 = 0.f, r2 = 0.f;
       for (int x = x0; x < x1; ++x) {
         const float wx = fmaxf(0.f, 1.f - fabsf((x + 0.5f - cx) * isx));
@@ -365,7 +397,6 @@ __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restr
       acc0 = fmaf(wy, r0, acc0);
       acc1 = fmaf(wy, r1, acc1);
       acc2 = fmaf(wy, r2, acc2);
-      wsum += wy;
     }
   }
   const float inv = 1.0f / (wsum * wxs * 255.f);
