@@ -166,10 +166,37 @@ __device__ __forceinline__ void quant_mx4(const float (&v)[NL], float amax, bool
   sf_byte = byte;
 }
 
+// Correctly rounded x / d through a correctly rounded reciprocal r = RN(1/d) (Markstein: q = RN(x*r), exact remainder by
+// FMA, one correction), valid while nothing over- or underflows and the significand of d is not all ones; anything else
+// goes to __fdiv_rn.  `safe_d` says that d itself is in the safe range (checked once per tensor by the caller).
+__device__ __forceinline__ float div_exact(float x, float d, float r, bool safe_d) {
+  if (safe_d && (x == 0.f || (x > 1e-30f && x < 1e30f))) return div_by_rcp(x, d, r);
+  return __fdiv_rn(x, d);
+}
+__device__ __forceinline__ bool div_safe_divisor(float d) {
+  return d > 1e-30f && d < 1e30f && (__float_as_uint(d) & 0x7FFFFFu) != 0x7FFFFFu;
+}
+
+// Per-tensor constants of the NVFP4 quantiser, worked out once per thread: the per-tensor scale, its correctly rounded
+// reciprocal and whether the reciprocal route is exact for it.
+struct Nv4Scale {
+  float ts, rcp_ts;
+  bool safe;
+};
+__device__ __forceinline__ Nv4Scale nv4_scale(float t) {
+  Nv4Scale s;
+  s.ts = t;
+  s.rcp_ts = __frcp_rn(t);
+  s.safe = div_safe_divisor(t);
+  return s;
+}
+
 template <int NL>
-__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, float ts, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
-  float a6 = div_true ? __fdiv_rn(amax, 6.0f) : amax * (1.0f / 6.0f);
-  float t = fminf(__fdiv_rn(a6, ts), 448.f);
+__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, const Nv4Scale& sc, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
+  const float ts = sc.ts;
+  // amax / 6 and (amax / 6) / ts are IEEE divisions; 1/6 as a constant reciprocal (RN(1/6) = 0x3E2AAAAB)
+  float a6 = div_true ? div_exact(amax, 6.0f, 0.16666667163372040f, true) : amax * (1.0f / 6.0f);
+  float t = fminf(div_exact(a6, ts, sc.rcp_ts, sc.safe), 448.f);
   uint32_t sb = cvt_e4m3x2(t, 0.f) & 0xFF;
   float denom = e4m3_to_float(sb) * ts;
   bool ok = denom > 0.f;
@@ -178,7 +205,7 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, floa
   // whole block stays in the normal range (|quotient| <= amax/dd), else by __fdiv_rn.
   const float rcp = __frcp_rn(dd);
   const float qmax = amax * rcp;
-  const bool fast = dd > 1e-30f && dd < 1e30f && qmax < 1e30f;
+  const bool fast = div_safe_divisor(dd) && qmax < 1e30f;
   float q[NL];
   if (!ok) {
 #pragma unroll
@@ -197,6 +224,10 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, floa
     for (int i = 0; i < NL; i += 8) out[i / 8] = cvt_e2m1x8(q + i);
   }
   sf_byte = (int)sb;
+}
+template <int NL>
+__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, float ts, bool div_true, uint32_t* out, int& sf_byte) {
+  quant_nv4<NL>(v, amax, nv4_scale(ts), div_true, out, sf_byte);
 }
 
 // NVFP4 block quantiser for epilogues whose input is a fresh accumulator (no bit-exact counterpart exists: the

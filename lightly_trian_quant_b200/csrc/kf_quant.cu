@@ -73,7 +73,16 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
   int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool in_pad = w < items_total;          // inside the padded row range (scale bytes must be written)
   const bool valid = w < items_valid;           // a real row
-  int row = (int)(w / per_row), c16 = (int)(w - (int64_t)row * per_row);
+  // 32-bit index arithmetic (the host checks that the item count fits); a power-of-two row length needs no division
+  const uint32_t w32 = (uint32_t)w;
+  int row, c16;
+  if ((per_row & (per_row - 1)) == 0) {
+    row = (int)(w32 >> (31 - __clz(per_row)));
+    c16 = (int)(w32 & (uint32_t)(per_row - 1));
+  } else {
+    row = (int)(w32 / (uint32_t)per_row);
+    c16 = (int)(w32 - (uint32_t)row * (uint32_t)per_row);
+  }
   float v[16];
   if (valid) {
     load16<T>(x + (int64_t)row * ldx + c16 * 16, v);
@@ -81,8 +90,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
   }
-  float ts = 1.f;
-  if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
+  const Nv4Scale ts = nv4_scale(FMT == KF_FMT_NV4 ? __ldg(ts_ptr) : 1.f);
   if (flags & KF_Q_GELU) {
     if (valid) {
       const float4* b4 = reinterpret_cast<const float4*>(bias + c16 * 16);
@@ -228,8 +236,7 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
     for (int k = 0; k < LNQ_RING; ++k) issue(k);
   float ww[NV][8], bb[NV][8];
   ln_affine_load<NV>(w, b, lane, ww, bb);
-  float ts = 1.f;
-  if (FMT == KF_FMT_NV4) ts = __ldg(ts_ptr);
+  const Nv4Scale ts = nv4_scale(FMT == KF_FMT_NV4 ? __ldg(ts_ptr) : 1.f);
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   const bool rb = flags & KF_Q_ROUND_BF16;
   // persistent: warp gw of the grid takes rows gw, gw + W, gw + 2W, ... (rows M..rows_pad only get zero scale words)
@@ -350,6 +357,7 @@ static int launch_quant_rows(int fmt, const void* x, int64_t ldx, int M, int K, 
                              cudaStream_t st) {
   int64_t per_row = K / 16;
   int64_t valid = (int64_t)M * per_row, total = (int64_t)((M + 127) / 128 * 128) * per_row;
+  KF_REQUIRE(total + 256 < (1ll << 32), "kf_quant_rows: M*K/16 = %lld work items do not fit the 32-bit index", (long long)total);
   unsigned grid = (unsigned)((total + 255) / 256);
   const T* xp = static_cast<const T*>(x);
   uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
