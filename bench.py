@@ -1,4 +1,4 @@
-"""Headline benchmark: ViT-L/16 + EoMT frames/s with NVFP4 linears on B200 (BASELINE config 4).
+"""Headline benchmark: ViT-L/16 + EoMT frames/s with NVFP4 linears on B200 (the 126-frame synthetic video workload, 640x640, frames sharded over the GPUs).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--variant b200_nv4] [--impl reference]
 

@@ -10,7 +10,7 @@ Cases follow the distributions of the reference's own operator tests:
     heavy()  randn with column 5 x30, column K/3 x12, one zero row  (round14_fp4_full/tests/t_quant14.py:18-23)
     mk()     randn with every 97th column x8                         (round13_mxfp8_full/tests/test13a.py:46-50)
     normal / outlier / wide / zeros                                  (round10_lowp_probe/tests/test_quant_ref.py:29-62)
-plus the first rows of BASELINE config 1 (bf16, 1 % of channels x20) and lattice-midpoint probes.
+plus the first rows of the single-GEMM benchmark input (bf16, 1 % of channels x20) and lattice-midpoint probes.
 """
 from __future__ import annotations
 
@@ -49,7 +49,7 @@ def cases():
     x[5, 32:64] = 0
     x[6, :16] = 0
     out["zeros_16x128"] = x
-    # BASELINE config 1 recipe, first 96 rows: N(0,1), 1 % of channels x20, rounded to bf16
+    # single-GEMM benchmark input recipe, first 96 rows: N(0,1), 1 % of channels x20, rounded to bf16
     gc = torch.Generator().manual_seed(0)
     X = torch.randn(1605, 1024, generator=gc)
     ch = torch.randperm(1024, generator=gc)[:10]
@@ -131,4 +131,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: gen_golden.py <path to the reference checkout>")
+    main(sys.argv[1])

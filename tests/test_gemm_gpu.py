@@ -68,7 +68,7 @@ def test_gemm_plain_small_f32(fmt, shape):
 
 @pytest.mark.parametrize("fmt", FMTS)
 def test_gemm_c1_fc1_bias(fmt):
-    """BASELINE config 1: X bf16 [1605,1024] (1 % channels x20), W [4096,1024] ~ N(0,0.02), bias: bf16 out within 2e-3."""
+    """The single-GEMM benchmark case: X bf16 [1605,1024] (1 % channels x20), W [4096,1024] ~ N(0,0.02), bias: bf16 out within 2e-3."""
     ops = _ops()
     gc = torch.Generator().manual_seed(0)
     X = torch.randn(1605, 1024, generator=gc)

@@ -118,7 +118,7 @@ def _collect_ts(model_fn):
 def test_tiny_model_end_to_end(fmt, init):
     """Whole model_fn against the emulated model at the same format.
 
-    upstream init (the init of the BASELINE configs): cosine >= 0.9999 on mask and class logits.
+    upstream init (the init the benchmark configurations use): cosine >= 0.9999 on mask and class logits.
     stress init: class logits >= 0.9999; the mask branch of a random-init model is chaotic under quantisation (a one
     bf16-ulp change of 1 % of the input pixels moves the emulated model's own mask logits by 1-cos ~ 1e-3 (mx8) to
     1e-2 (nv4)), so the bound there is self-calibrated: the GPU path may differ from the emulation by no more than
