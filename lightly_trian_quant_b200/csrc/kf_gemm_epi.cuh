@@ -230,32 +230,45 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     }
     __syncwarp();                                             // the staging tile is reused by the next tile
   } else if (EPI == KF_EPI_RES) {
-    // two 32-column chunks, each restaged so that the fp32 residual is read and written 128 contiguous bytes per row
+    // two 32-column chunks, each restaged so that the fp32 residual is read and written 128 contiguous bytes per row.
+    // Four rounds (chunk, half of the 8 passes); the residual loads of round r + 1 are in flight while round r is worked
+    // out, so only the first round waits for its loads.
+    auto load_round = [&](int r, float4 (&rr)[4]) {
+      const int n = n0 + 32 * (r >> 1) + c4;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int n = n0 + 32 * c + c4;
-      stg_put(stg, lane, c == 0 ? r0 : r1);
-      __syncwarp();
-      const float4 b4 = g.bias ? ldg4(g.bias + n) : z4, g4 = ldg4(g.gamma + n);
-#pragma unroll
-      for (int hp = 0; hp < 2; ++hp) {                        // four passes at a time: loads first, then the math
-        float4 rr[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int m = rbase + 4 * (4 * hp + i) + rsub;
-          rr[i] = m < g.M ? ld4_stream(g.R + (size_t)m * g.N + n) : z4;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int m = rbase + 4 * (4 * hp + i) + rsub;
-          const float4 v = fma4(stg_get(stg, lane, 4 * hp + i), ts, b4);
-          if (m < g.M)
-            *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
-                make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
-        }
+      for (int i = 0; i < 4; ++i) {
+        const int m = rbase + 4 * (4 * (r & 1) + i) + rsub;
+        rr[i] = m < g.M ? ld4_stream(g.R + (size_t)m * g.N + n) : z4;
       }
-      __syncwarp();                                           // the staging tile is reused by the next chunk
-    }
+    };
+    auto do_round = [&](int r, const float4 (&rr)[4], const float4& b4, const float4& g4) {
+      const int n = n0 + 32 * (r >> 1) + c4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = rbase + 4 * (4 * (r & 1) + i) + rsub;
+        const float4 v = fma4(stg_get(stg, lane, 4 * (r & 1) + i), ts, b4);
+        if (m < g.M)
+          *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
+              make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
+      }
+    };
+    float4 rra[4], rrb[4];
+    load_round(0, rra);
+    const float4 b40 = g.bias ? ldg4(g.bias + n0 + c4) : z4, g40 = ldg4(g.gamma + n0 + c4);
+    const float4 b41 = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4, g41 = ldg4(g.gamma + n0 + 32 + c4);
+    stg_put(stg, lane, r0);
+    __syncwarp();
+    load_round(1, rrb);
+    do_round(0, rra, b40, g40);
+    load_round(2, rra);
+    do_round(1, rrb, b40, g40);
+    __syncwarp();                                             // the staging tile is reused by the second chunk
+    stg_put(stg, lane, r1);
+    __syncwarp();
+    load_round(3, rrb);
+    do_round(2, rra, b41, g41);
+    do_round(3, rrb, b41, g41);
+    __syncwarp();                                             // ... and by the next tile
   } else if (EPI == KF_EPI_PLAIN) {
     const int m = rbase + lane;
     uint8_t* dst_row = nullptr;
