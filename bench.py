@@ -146,6 +146,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=14, help="frames per GPU per step")
     ap.add_argument("--variant", default="b200_nv4")
+    ap.add_argument("--arch", default="vit_l", choices=["vit_l", "vit_b"], help="backbone of the other benchmark configurations (default: the headline ViT-L/16)")
+    ap.add_argument("--size", type=int, default=SIZE, help="input side in pixels (default 640)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -167,11 +169,14 @@ def main():
 
     from lightly_trian_quant_b200 import modeldef, ops, sharding, stack
 
-    cfg = modeldef.VIT_L
+    cfg = modeldef.VIT_L if args.arch == "vit_l" else modeldef.VIT_B
+    size = args.size
+    if size != SIZE and "+s" not in args.variant:
+        args.variant += f"+s{size}"
     fmt = args.variant.split("+")[0].split("_")[1]
     model = modeldef.build_model(cfg, seed=0, mode="upstream", device=dev)
-    model_fn, pipe_cls = stack.make_variant("vitl", model, args.variant)
-    pipe = pipe_cls(model, model_fn, SIZE)
+    model_fn, pipe_cls = stack.make_variant(args.arch, model, args.variant)
+    pipe = pipe_cls(model, model_fn, size)
     B = args.batch
 
     # this rank's shard of the video: frames rank, rank+world, ...; grouped into micro-batches of B (cyclic)
@@ -292,14 +297,14 @@ def main():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else None
         gname = "gemm_block_" + fmt
         if gname in classes:
-            flops = block_gemm_flops(cfg, B, SIZE)
+            flops = block_gemm_flops(cfg, B, size)
             achieved = flops / (classes[gname]["ms"] * 1e-3) / 1e12
             peak = ops.tensor_peak_tflops(fmt, 256)
             nominal = {"nv4": 9000.0, "mx4": 9000.0, "mx8": 4500.0, "bf16": 2250.0}[fmt]
             # DRAM bytes per launch of the dominant kernel: ncu figure per token row (profiles/gemm_nv4_block_dram_traffic.md:
             # 4987 B per row and launch, averaged over qkv / proj / fc1 / fc2 at 22 470 rows) times the mean rows per launch here
-            rows_mean = B * ((cfg.depth - cfg.num_joint_blocks) * (5 + (SIZE // 16) ** 2) + cfg.num_joint_blocks * (5 + (SIZE // 16) ** 2 + cfg.num_queries)) / cfg.depth
-            traffic = 4987.0 * rows_mean if fmt == "nv4" else None
+            rows_mean = B * ((cfg.depth - cfg.num_joint_blocks) * (5 + (size // 16) ** 2) + cfg.num_joint_blocks * (5 + (size // 16) ** 2 + cfg.num_queries)) / cfg.depth
+            traffic = 4987.0 * rows_mean if (fmt == "nv4" and args.arch == "vit_l") else None
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                     "kernel": f"gemm_kernel<{fmt}> (qkv, proj, fc1, fc2 of all blocks; {classes[gname]['launches']} launches per step)",
                     "peak_source": f"tcgen05 {fmt} instruction-rate probe (M=128, N=256 as in the kernel, shared-memory-resident operands) measured in this run; "
@@ -315,12 +320,13 @@ def main():
     ops.check_device_error()
 
     if rank == 0:
-        line = {"metric": METRIC, "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        arch_name = "ViT-L/16" if args.arch == "vit_l" else "ViT-B/16"
+        line = {"metric": METRIC if args.arch == "vit_l" else "ViT-B/16+EoMT frames/s", "value": fps, "unit": "frames/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": {"nv4": "nvfp4 (e2m1, ue4m3 per 16, fp32 accumulate)", "mx4": "mxfp4", "mx8": "mxfp8 (e4m3, ue8m0 per 32, fp32 accumulate)", "bf16": "bf16"}[fmt],
                 "data": "synthetic",
-                "config": {"workload": f"C4: DINOv3 ViT-L/16 + EoMT (200 queries, 4 joint blocks), {fmt} linears, bf16 attention, 126-frame synthetic "
-                                       f"1900x1440 uint8 video -> 640x640, sharded by frame", "variant": args.variant, "frames_per_gpu_per_step": B,
+                "config": {"workload": f"DINOv3 {arch_name} + EoMT (200 queries, 4 joint blocks), {fmt} linears, {'f16' if 'f16attn' in args.variant else 'bf16'} attention, "
+                                       f"126-frame synthetic 1900x1440 uint8 video -> {size}x{size}, sharded by frame", "variant": args.variant, "frames_per_gpu_per_step": B,
                            "parallelism": f"dp{world} (replicated weights, no collective)", "l2": "inputs larger than L2: a different frame batch every step"},
                 "clocks": clocks,
                 "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

@@ -2,6 +2,7 @@
 larger than L2 so operands come from HBM, not from cache).
 
     python -m lightly_trian_quant_b200.microbench gemm --fmt nv4 --kind fc1 --batch 8 [--iters 20]
+    python -m lightly_trian_quant_b200.microbench lib_gemm --fmt mx8 --kind fc1 --batch 8      # cuBLASLt comparator
     python -m lightly_trian_quant_b200.microbench attn --batch 8 --tokens 1605
     python -m lightly_trian_quant_b200.microbench ln_quant --fmt mx8 --batch 8
     python -m lightly_trian_quant_b200.microbench quant_rows --fmt nv4 --batch 8 --k 1024
@@ -88,6 +89,38 @@ def bench_gemm(args):
     return {"kernel": f"gemm {fmt} {args.kind}", "M": M, "N": N, "K": K, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
 
 
+def bench_lib_gemm(args):
+    """Same-box library comparator: cuBLASLt through torch._scaled_mm (block-scaled mx8 / nv4 / mx4) or torch.matmul (bf16)
+    on operands quantised by this library (its blocked scale layout is the swizzled layout cuBLASLt expects); plain bf16
+    output, no fused epilogue.  M is rounded up to a multiple of 128."""
+    K, N = SHAPES[args.kind]
+    M = (args.tokens * args.batch + 127) // 128 * 128
+    fmt = args.fmt
+    g = torch.Generator(device="cuda").manual_seed(0)
+    copies = max(2, int(2 * 126e6 / (N * K)) + 1)
+    Ws = [ops.QWeight(torch.randn(N, K, generator=g, device="cuda") * 0.02, fmt) for _ in range(min(copies, 8))]
+    acts = [_act(M, K, fmt, s) for s in range(2)]
+    if fmt == "bf16":
+        def fn(i):
+            torch.matmul(acts[i % 2], Ws[i % len(Ws)].q.t())
+    else:
+        dt = torch.float8_e4m3fn if fmt == "mx8" else torch.float4_e2m1fn_x2
+        st = torch.float8_e4m3fn if fmt == "nv4" else torch.float8_e8m0fnu
+        A = [(a.q.view(dt), a.sf.view(st)) for a in acts]
+        Wv = [(w.q.view(dt).t(), w.sf.view(st)) for w in Ws]
+
+        def fn(i):
+            a, sa = A[i % 2]
+            w, sw = Wv[i % len(Wv)]
+            torch._scaled_mm(a, w, scale_a=sa, scale_b=sw, out_dtype=BF)
+    try:
+        t = _time(fn, args.iters)
+    except Exception as e:  # the library may not offer the format on this build
+        return {"kernel": f"library gemm {fmt} {args.kind}", "unavailable": str(e).split("\n")[0][:300]}
+    fl = 2.0 * M * N * K
+    return {"kernel": f"library gemm {fmt} {args.kind} (torch._scaled_mm / matmul, bf16 out)", "M": M, "N": N, "K": K, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
+
+
 def bench_attn(args):
     B, N, H = args.batch, args.tokens, 16
     dt = torch.float16 if args.dtype == "f16" else BF
@@ -140,7 +173,7 @@ def bench_peak(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak"])
+    ap.add_argument("what", choices=["gemm", "lib_gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak"])
     ap.add_argument("--fmt", default="nv4")
     ap.add_argument("--kind", default="fc1", choices=list(SHAPES))
     ap.add_argument("--batch", type=int, default=8)
@@ -152,7 +185,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     args = ap.parse_args()
     torch.set_grad_enabled(False)
-    fn = {"gemm": bench_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak}[args.what]
+    fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak}[args.what]
     print(json.dumps(fn(args)), flush=True)
 
 
