@@ -114,7 +114,9 @@ def run_reference(args, rank: int):
     fps = args.steps / dt
     line = {"impl": "reference", "metric": METRIC, "value": fps, "unit": "frames/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": fmt, "data": "synthetic",
-            "config": {"workload": f"C4 ViT-L/16+EoMT {fmt} 640x640, CPU emulated path, 1 frame per step"},
+            "config": {"workload": f"DINOv3 ViT-L/16 + EoMT (200 queries, 4 joint blocks), {fmt} linears, bf16 attention, 126-frame synthetic "
+                                   f"1900x1440 uint8 video -> {SIZE}x{SIZE}, sharded by frame", "variant": args.variant,
+                       "sample": "CPU emulated path on the host cores, one 640x640 frame per step (a bounded sample of the same workload)"},
             "cpu_baseline": {"value": fps, "unit": "frames/s", "cores": torch.get_num_threads(), "kind": "port",
                              "sample": "1 frame (640x640, whole model) per step; the reference's sm_120a extensions cannot run on the host, so its torch "
                                        "quantiser + dequantise-then-fp32-matmul emulation is timed through the CPU oracle port"},
