@@ -188,6 +188,8 @@ KF_API int kf_attn_fwd_quant(int dtype, const void* qkv, int B, int N, int H, fl
 
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
+ * While the word is set, the GEMM and attention kernels return at once without touching their outputs (a failed launch must not
+ * make every later launch wait out its limits too), so the outputs of launches after a failure are undefined until this call.
  * No counterpart in the reference (its mbarrier waits spin without a bound: infer-opt/round12_lowp_stack/impl/attn16o.cu:77-79). */
 KF_API int kf_check_device_error(void);
 
