@@ -152,6 +152,7 @@ def main():
     ap.add_argument("--size", type=int, default=SIZE, help="input side in pixels (default 640)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--pdl", action="store_true", help="launch the block kernels with programmatic dependent launch (default: plain stream order)")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
@@ -171,6 +172,7 @@ def main():
 
     from lightly_trian_quant_b200 import modeldef, ops, sharding, stack
 
+    ops.set_pdl(args.pdl)
     cfg = modeldef.VIT_L if args.arch == "vit_l" else modeldef.VIT_B
     size = args.size
     if size != SIZE and "+s" not in args.variant:

@@ -186,6 +186,14 @@ KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double
 KF_API int kf_attn_fwd_quant(int dtype, const void* qkv, int B, int N, int H, float pre, int out_fmt, void* Qo, void* SFo,
                              const float* tso, int flags, void* stream);
 
+/* Programmatic dependent launch for the kernels of the transformer block (LN + quant, GEMM, attention): on lets a
+ * kernel's CTAs start on the SMs its predecessor has already left (partial last wave, teardown) and overlap their set-up with
+ * it; every kernel waits for its predecessors' completion before touching global memory, so results do not change.
+ * Off by default: every kernel of the block needs its predecessor's whole output, so only the set-up overlaps, and inside a
+ * captured graph that measured slightly slower than plain stream order.
+ * Counterpart: set_pdl(bool) (infer-opt/round13_mxfp8_full/impl/mx13.cu:282). */
+KF_API int kf_set_pdl(int on);
+
 /* Reads (and clears) the device error word that kernels with bounded waits write when a wait runs out.
  * Synchronises the device.  Returns KF_OK, or KF_ERR_DEVICE_WAIT with where/block in the error string.
  * While the word is set, the GEMM and attention kernels return at once without touching their outputs (a failed launch must not

@@ -76,7 +76,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
-  if (a.err[0] != 0) return;                             // an earlier CTA or launch already failed: do not wait all over again
+  pdl_launch_dependents();                               // the next kernel of the stream may take the SMs this grid leaves
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (a.N + AT_BM - 1) / AT_BM;
   const int qt = blockIdx.x % q_tiles;
@@ -106,10 +106,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();                                            // set-up done: from here on global memory of the predecessors is read and written
   const uint32_t tmem_base = *tmem_holder;
   const WaitCtx ctx{abort_flag, a.err};
-  const bool bad_align = *abort_flag != 0;
-  if (bad_align && threadIdx.x == 0 && atomicCAS(&a.err[0], 0u, 99u) == 0u) {
+  const bool bad_align = *abort_flag != 0 || a.err[0] != 0;   // misaligned tiles, or an earlier CTA / launch already failed: skip the work
+  if (*abort_flag != 0 && threadIdx.x == 0 && atomicCAS(&a.err[0], 0u, 99u) == 0u) {
     a.err[1] = 100;
     a.err[2] = blockIdx.x;
   }
@@ -444,8 +445,8 @@ static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H,
   a.out_fmt = out_fmt; a.flags = flags; a.Qo = static_cast<uint8_t*>(Qo); a.SFo = static_cast<uint8_t*>(SFo); a.tso = tso;
   KF_REQUIRE(a.err != nullptr, "kf_attn_fwd: device error word unavailable");
   const int q_tiles = (N + AT_BM - 1) / AT_BM;
-  attn_fwd_kernel<<<B * H * q_tiles, AT_THREADS, AT_SMEM, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, a);
-  return cuda_status(cudaGetLastError(), "kf_attn_fwd launch");
+  return cuda_status(launch_maybe_pdl(attn_fwd_kernel, dim3(B * H * q_tiles), dim3(AT_THREADS), (size_t)AT_SMEM, static_cast<cudaStream_t>(stream), tq, tk, tv, a),
+                     "kf_attn_fwd launch");
 }
 
 extern "C" int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H, float pre, void* stream) {

@@ -1,6 +1,7 @@
 // Shared device/host helpers of the B200 (sm_100a) low-precision ViT path: format conversions, the 128x4 blocked
 // scale-factor addressing, status codes and the last-error string of the C-ABI.
 #pragma once
+#include <utility>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -16,6 +17,30 @@ namespace kf {
 void set_error(const char* fmt, ...);
 int cuda_status(cudaError_t e, const char* what);
 int device_sm_count(int* sms);   // multiprocessor count of the current device (cached)
+bool pdl_enabled();              // kf_set_pdl: launch the block kernels with programmatic dependent launch
+
+// Programmatic dependent launch: a kernel lets its successor's CTAs start on SMs it no longer occupies (its partial last
+// wave, its teardown) and the successor runs its prologue (barrier set-up, TMEM allocation, descriptor prefetch) there; the
+// successor must not touch global memory before pdl_wait(), which returns when every predecessor grid has completed
+// and its writes are visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// <<<grid, block, smem, stream>>> with the programmatic-stream-serialization attribute when PDL is enabled
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_maybe_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 #define KF_REQUIRE(cond, ...)            \
   do {                                   \

@@ -49,7 +49,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
-  if (g.err[0] != 0) return;                             // an earlier CTA or launch already failed: do not wait all over again
+  pdl_launch_dependents();                               // the next kernel of the stream may take the SMs this grid leaves
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -74,11 +74,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();                                            // set-up done: from here on global memory of the predecessors is read and written
   const uint32_t tmem_base = *tmem_holder;
   const WaitCtx ctx{abort_flag, g.err};
   const int total_tiles = g.m_tiles * g.n_tiles;
-  const bool bad_align = *abort_flag != 0;
-  if (bad_align && threadIdx.x == 0 && atomicCAS(&g.err[0], 0u, (unsigned)(-KF_ERR_DEVICE_WAIT)) == 0u) {
+  const bool bad_align = *abort_flag != 0 || g.err[0] != 0;   // misaligned tiles, or an earlier CTA / launch already failed: skip the work
+  if (*abort_flag != 0 && threadIdx.x == 0 && atomicCAS(&g.err[0], 0u, (unsigned)(-KF_ERR_DEVICE_WAIT)) == 0u) {
     g.err[1] = 100;
     g.err[2] = blockIdx.x;
   }
@@ -296,8 +297,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  gemm_kernel<KIND, EPI><<<grid, GEMM_THREADS, Pipe<EPI>::SMEM, st>>>(tmA, tmW, g);
-  return cuda_status(cudaGetLastError(), "kf_gemm_bs launch");
+  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), Pipe<EPI>::SMEM, st, tmA, tmW, g), "kf_gemm_bs launch");
 }
 
 template <int KIND>

@@ -217,12 +217,14 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
   float* ring = reinterpret_cast<float*>(lsm) + (size_t)warp * LNQ_RING * D;
   uint64_t* bars = reinterpret_cast<uint64_t*>(lsm + (size_t)4 * LNQ_RING * D * 4) + warp * LNQ_RING;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(lsm + (size_t)4 * LNQ_RING * D * 4 + 4 * LNQ_RING * 8);
+  pdl_launch_dependents();                        // the next kernel of the stream may take the SMs this grid leaves
   if (threadIdx.x == 0) *abort_flag = 0;
   if (lane == 0) {
     for (int i = 0; i < LNQ_RING; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_wait();                                     // from here on global memory of the predecessors is read and written
   const WaitCtx ctx{abort_flag, err};
   const int W = gridDim.x * 4, gw = blockIdx.x * 4 + warp;
   auto issue = [&](int k) {                       // lane 0: start the copy of this warp's k-th row into slot k % RING
@@ -382,8 +384,7 @@ static int launch_ln_quant(int fmt, const float* x, const float* w, const float*
   auto go = [&](auto kern) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_quant_kernel)");
-    kern<<<grid, 128, smem, st>>>(x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg, err);
-    return cuda_status(cudaGetLastError(), "kf_ln_quant launch");
+    return cuda_status(launch_maybe_pdl(kern, dim3(grid), dim3(128), smem, st, x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg, err), "kf_ln_quant launch");
   };
   if (fmt == KF_FMT_MX8) return go(ln_quant_kernel<NV, KF_FMT_MX8>);
   if (fmt == KF_FMT_NV4) return go(ln_quant_kernel<NV, KF_FMT_NV4>);

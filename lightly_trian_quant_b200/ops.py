@@ -167,6 +167,12 @@ ln_bf16 = ln_rows
 
 
 # ------------------------------------------------------------------------------------------------ weights and GEMMs
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the block kernels (off by default); results are the same either way.
+    Counterpart: set_pdl (infer-opt/round13_mxfp8_full/impl/mx13.cu:282)."""
+    check(_lib.lib().kf_set_pdl(1 if on else 0), "kf_set_pdl")
+
+
 def check_device_error() -> None:
     """synchronises and raises if a kernel's bounded wait ran out (no reference counterpart)."""
     check(_lib.lib().kf_check_device_error(), "kf_check_device_error")

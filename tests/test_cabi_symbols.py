@@ -50,3 +50,10 @@ def test_ops_refuse_cpu_tensors(built_lib):
     buf = ops.ActBuf(4, 128, "mx8", device="cpu")
     with pytest.raises(KfError):
         ops.quant_rows(torch.zeros(4, 128), buf)
+
+
+def test_set_pdl_switch(built_lib):
+    from lightly_trian_quant_b200 import ops
+
+    ops.set_pdl(True)
+    ops.set_pdl(False)

@@ -224,6 +224,27 @@ def test_cuda_graph_replay_is_bitwise_eager():
     assert torch.equal(out[0], eager[0]) and torch.equal(out[1], eager[1])
 
 
+def test_dependent_launch_does_not_change_results():
+    """the block kernels launched with programmatic dependent launch give the bits of plain stream order, many
+    times over (an early start that touched global memory before its predecessors finished would show as a race)."""
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.EoMTConfig(**TINY)
+    gmodel = modeldef.build_model(cfg, 0, "stress", "cuda")
+    fn, _ = stack.make_variant("tiny", gmodel, "b200_nv4+s64")
+    x = torch.rand(6, 3, 64, 64, generator=torch.Generator().manual_seed(8)).to(BF).cuda()
+    try:
+        ops.set_pdl(False)
+        ref = [t.clone() for t in fn(x)]
+        ops.set_pdl(True)
+        for _ in range(20):
+            out = fn(x)
+            assert torch.equal(out[0], ref[0]) and torch.equal(out[1], ref[1])
+    finally:
+        ops.set_pdl(False)
+    torch.cuda.synchronize()
+    ops.check_device_error()
+
+
 @pytest.mark.parametrize("fmt", ["mx8", "nv4"])
 def test_linear_swap_enable_disable(fmt):
     """the Linear swap patches the model's own forward: quantised units track the unpatched model, and disable()
