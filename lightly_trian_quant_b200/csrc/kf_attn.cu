@@ -51,11 +51,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float y;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
-  return y;
-}
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
   if (f16) {
@@ -210,27 +205,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto exp_row = [&](auto is_f16, auto track, float mneg, float (&mx4)[4]) -> float {
         constexpr int F = decltype(is_f16)::value;
         constexpr bool TRACK = decltype(track)::value != 0;
-        float s0 = 0.f, s1 = 0.f;
+        // the exponent arguments and the row sum run as packed pairs: half the issue slots of the scalar form
+        const float2 sc2 = splat2(sc), mn2 = splat2(mneg);
+        float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            float p[8];
+            float2 p[4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) p[k] = ex2(fmaf(__uint_as_float(r[c][8 * i + k]), sc, mneg));
+            for (int k = 0; k < 4; ++k) {
+              const float2 t = fma2(make_float2(__uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1])), sc2, mn2);
+              p[k] = make_float2(ex2(t.x), ex2(t.y));
+            }
             if (TRACK) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1]));
             }
-            s0 += (p[0] + p[1]) + (p[2] + p[3]);
-            s1 += (p[4] + p[5]) + (p[6] + p[7]);
+            s0 = add2(s0, add2(p[0], p[1]));
+            s1 = add2(s1, add2(p[2], p[3]));
 #pragma unroll
-            for (int k = 0; k < 4; ++k) w[4 * i + k] = pack16(p[2 * k], p[2 * k + 1], F);
+            for (int k = 0; k < 4; ++k) w[4 * i + k] = pack16(p[k].x, p[k].y, F);
           }
           tmem_st16(t_p + 16 * c, w);
         }
-        return s0 + s1;
+        return (s0.x + s0.y) + (s1.x + s1.y);
       };
       auto run = [&](auto track, float mneg, float (&mx4)[4]) -> float {
         return a.f16 ? exp_row(std::integral_constant<int, 1>{}, track, mneg, mx4) : exp_row(std::integral_constant<int, 0>{}, track, mneg, mx4);

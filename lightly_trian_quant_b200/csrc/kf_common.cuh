@@ -109,6 +109,20 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Packed fp32 pairs (the two-wide FFMA2 / FADD2 / FMUL2 of sm_100): each component is the IEEE round-to-nearest result of
+// the scalar operation, at one issue slot per pair.  The CUDA-core-bound kernels here are short of issue slots, not of
+// FMA lanes.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 splat2(float x) { return make_float2(x, x); }
+// both values rounded to bf16 and widened again: one packed conversion and two bit operations
+__device__ __forceinline__ float2 bf16_round2(float2 v) {
+  const __nv_bfloat162 h = __float22bfloat162_rn(v);
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
 // GELU with the exact (erf) definition 0.5*x*(1 + erf(x/sqrt(2))).  erfc(t) for t >= 0 is evaluated as
 // poly5(k) * exp(-t^2), k = 1/(1 + p*t) (Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7, the same class as fp32 erff)
 // and the two signs are assembled without cancellation as relu(x) - 0.5*|x|*erfc(t).
@@ -127,6 +141,36 @@ __device__ __forceinline__ float gelu_erf(float x) {
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-u * u));
   return fmaxf(x, 0.f) - (0.5f * ax) * (p * e);         // relu(x) - 0.5*|x|*erfc(|x|/sqrt2), both signs without cancellation
+}
+
+// GELU (exact-erf definition) of two values for the fused GEMM epilogues, which are short of XU (MUFU) throughput: one
+// exponential per value and no reciprocal.  gelu(x) = relu(x) - |x| * Phi(-|x|) with the normal tail written as
+// Phi(-a) = 2^(-a^2 * log2(e)/2 + Q(a)); Q is smooth and logarithm-like (Q(0) = -1) and a degree-7 least-squares fit on
+// Chebyshev nodes of [0, 6] keeps the exponent within 5.7e-6, |gelu error| <= 6.1e-7 (the class of fp32 erff); past 6 the
+// quadratic term has pushed the product below 1e-8 and soon to an exact 0.  Evaluated on n = -|x| (odd coefficients
+// negated) as packed pairs: 12 packed + 6 scalar instructions per pair.
+__device__ __forceinline__ float2 gelu_erf2(float2 x) {
+  const float2 n = make_float2(-fabsf(x.x), -fabsf(x.y));
+  float2 q = fma2(n, splat2(1.8896262190537527e-06f), splat2(6.268139986786991e-05f));
+  q = fma2(q, n, splat2(0.0009388679172843695f));
+  q = fma2(q, n, splat2(0.00853946153074503f));
+  q = fma2(q, n, splat2(0.05402068793773651f));
+  q = fma2(q, n, splat2(0.2629377543926239f));
+  q = fma2(q, n, splat2(1.1512691974639893f));
+  q = fma2(q, n, splat2(-0.9999943375587463f));
+  const float2 p = fma2(mul2(n, n), splat2(-0.72134752044448170368f), q);
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(p.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(p.y));
+  const float2 relu = make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f));
+  return fma2(n, e, relu);
+}
+
+// max(a, b, c) in one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
 }
 
 // Correctly rounded x / d from a correctly rounded reciprocal r = RN(1/d) (one per block): q = RN(x*r), the exact
@@ -167,7 +211,8 @@ __device__ __forceinline__ void quant_mx8(const float (&v)[NL], float amax, bool
 #pragma unroll
   for (int i = 0; i < NL; i += 4) {
     // the clamp to +-448 of the reference is what cvt.rn.satfinite does
-    out[i / 4] = cvt_e4m3x4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+    const float2 a = mul2(make_float2(v[i], v[i + 1]), splat2(inv)), b = mul2(make_float2(v[i + 2], v[i + 3]), splat2(inv));
+    out[i / 4] = cvt_e4m3x4(a.x, a.y, b.x, b.y);
   }
   sf_byte = byte;
 }
@@ -236,8 +281,15 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, cons
 #pragma unroll
     for (int j = 0; j < NL; ++j) q[j] = 0.f;
   } else if (fast) {
+    const float2 r2 = splat2(rcp), nd2 = splat2(-dd);
 #pragma unroll
-    for (int j = 0; j < NL; ++j) q[j] = div_by_rcp(v[j], dd, rcp);
+    for (int j = 0; j < NL; j += 2) {         // div_by_rcp on packed pairs
+      const float2 x = make_float2(v[j], v[j + 1]);
+      const float2 q0 = mul2(x, r2);
+      const float2 q1 = fma2(fma2(nd2, q0, x), r2, q0);
+      q[j] = q1.x;
+      q[j + 1] = q1.y;
+    }
   } else {
 #pragma unroll
     for (int j = 0; j < NL; ++j) q[j] = __fdiv_rn(v[j], dd);
@@ -268,8 +320,13 @@ __device__ __forceinline__ void quant_nv4_fast(const float (&v)[NL], float amax,
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(denom));
   rcp = denom > 0.f ? rcp : 0.f;
   float q[NL];
+  const float2 r2 = splat2(rcp);
 #pragma unroll
-  for (int j = 0; j < NL; ++j) q[j] = v[j] * rcp;
+  for (int j = 0; j < NL; j += 2) {
+    const float2 t = mul2(make_float2(v[j], v[j + 1]), r2);
+    q[j] = t.x;
+    q[j + 1] = t.y;
+  }
 #pragma unroll
   for (int i = 0; i < NL; i += 8) out[i / 8] = cvt_e2m1x8(q + i);
   sf_byte = (int)sb;

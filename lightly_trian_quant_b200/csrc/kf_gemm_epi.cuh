@@ -76,8 +76,18 @@ __device__ __forceinline__ float4 ld4_stream(const float* p) {   // read once: d
   asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
   return v;
 }
+// four-wide helpers on packed pairs (two issue slots per float4)
+__device__ __forceinline__ float4 join4(float2 a, float2 b) { return make_float4(a.x, a.y, b.x, b.y); }
 __device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
-  return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w));
+  const float2 s2 = splat2(s);
+  return join4(fma2(make_float2(a.x, a.y), s2, make_float2(b.x, b.y)), fma2(make_float2(a.z, a.w), s2, make_float2(b.z, b.w)));
+}
+__device__ __forceinline__ float4 fma4v(float4 a, float4 b, float4 c) {      // a * b + c
+  return join4(fma2(make_float2(a.x, a.y), make_float2(b.x, b.y), make_float2(c.x, c.y)),
+               fma2(make_float2(a.z, a.w), make_float2(b.z, b.w), make_float2(c.z, c.w)));
+}
+__device__ __forceinline__ float4 mul4v(float4 a, float4 b) {
+  return join4(mul2(make_float2(a.x, a.y), make_float2(b.x, b.y)), mul2(make_float2(a.z, a.w), make_float2(b.z, b.w)));
 }
 __device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
   uint2 o;
@@ -102,20 +112,27 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
 #pragma unroll
   for (int q4 = 0; q4 < 8; ++q4) {
     const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    v[4 * q4] = gelu_erf(fmaf(__uint_as_float(r[4 * q4]), ts, bb.x));
-    v[4 * q4 + 1] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 1]), ts, bb.y));
-    v[4 * q4 + 2] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 2]), ts, bb.z));
-    v[4 * q4 + 3] = gelu_erf(fmaf(__uint_as_float(r[4 * q4 + 3]), ts, bb.w));
+    const float2 ts2 = splat2(ts);
+    const float2 a = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1])), ts2, make_float2(bb.x, bb.y)));
+    const float2 b = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4 + 2]), __uint_as_float(r[4 * q4 + 3])), ts2, make_float2(bb.z, bb.w)));
+    v[4 * q4] = a.x;
+    v[4 * q4 + 1] = a.y;
+    v[4 * q4 + 2] = b.x;
+    v[4 * q4 + 3] = b.y;
   }
   if (g.flags & KF_Q_ROUND_BF16) {
 #pragma unroll
-    for (int k = 0; k < 32; ++k) v[k] = bf16_round(v[k]);
+    for (int k = 0; k < 32; k += 2) {
+      const float2 t = bf16_round2(make_float2(v[k], v[k + 1]));
+      v[k] = t.x;
+      v[k + 1] = t.y;
+    }
   }
   float am0 = 0.f, am1 = 0.f;
 #pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    am0 = fmaxf(am0, fabsf(v[k]));
-    am1 = fmaxf(am1, fabsf(v[16 + k]));
+  for (int k = 0; k < 16; k += 2) {
+    am0 = max3(am0, fabsf(v[k]), fabsf(v[k + 1]));
+    am1 = max3(am1, fabsf(v[16 + k]), fabsf(v[17 + k]));
   }
   const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
   const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
@@ -220,8 +237,8 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
           const float* tabc = g.cos + (size_t)(t - g.prefix) * 64 + c4;
           const float4 sl = ldg4(tab), cl = ldg4(tabc), sh = ldg4(tab + 32), ch = ldg4(tabc + 32);
           // lo' = lo*cos - hi*sin (tables of columns 0..31), hi' = hi*cos + lo*sin (tables of columns 32..63)
-          ol = make_float4(lo[i].x * cl.x - hi.x * sl.x, lo[i].y * cl.y - hi.y * sl.y, lo[i].z * cl.z - hi.z * sl.z, lo[i].w * cl.w - hi.w * sl.w);
-          oh = make_float4(hi.x * ch.x + lo[i].x * sh.x, hi.y * ch.y + lo[i].y * sh.y, hi.z * ch.z + lo[i].z * sh.z, hi.w * ch.w + lo[i].w * sh.w);
+          ol = fma4v(hi, make_float4(-sl.x, -sl.y, -sl.z, -sl.w), mul4v(lo[i], cl));
+          oh = fma4v(hi, ch, mul4v(lo[i], sh));
         }
         uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + c4) * 2;
         *reinterpret_cast<uint2*>(dst) = pack4(ol, g.out_dtype);
@@ -249,7 +266,7 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
         const float4 v = fma4(stg_get(stg, lane, 4 * (r & 1) + i), ts, b4);
         if (m < g.M)
           *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
-              make_float4(fmaf(g4.x, v.x, rr[i].x), fmaf(g4.y, v.y, rr[i].y), fmaf(g4.z, v.z, rr[i].z), fmaf(g4.w, v.w, rr[i].w));
+              fma4v(g4, v, rr[i]);
       }
     };
     float4 rra[4], rrb[4];

@@ -154,34 +154,42 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
       }
       // ---- depthwise 3x3 of the two pixels: taps accumulate in (ky, kx) order for each of them; the 3 x 8 tap weights of
       // a kernel row are fetched when that row is due (72 weights at once would not fit the register budget)
-      float acc0[8], acc1[8];
+      // (packed pairs: a 16-bit pair unpacks into the two halves of one operand, and one FFMA2 serves two channels)
+      float2 acc0[4], acc1[4];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc0[k] = acc1[k] = 0.f;
+      for (int k = 0; k < 4; ++k) acc0[k] = acc1[k] = make_float2(0.f, 0.f);
 #pragma unroll
       for (int ky = 0; ky < 3; ++ky) {
-        float w[3][8];
+        float2 w[3][4];
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
           const float4* wp = reinterpret_cast<const float4*>(dww + (ky * 3 + k) * C + ch + grp * 8);
           const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
-          w[k][0] = w0.x; w[k][1] = w0.y; w[k][2] = w0.z; w[k][3] = w0.w; w[k][4] = w1.x; w[k][5] = w1.y; w[k][6] = w1.z; w[k][7] = w1.w;
+          w[k][0] = make_float2(w0.x, w0.y); w[k][1] = make_float2(w0.z, w0.w); w[k][2] = make_float2(w1.x, w1.y); w[k][3] = make_float2(w1.z, w1.w);
         }
 #pragma unroll
         for (int cx = 0; cx < 4; ++cx) {
-          float f[8];
-          bf16x8_to_f32(act[((oy + ky) * (DW_TW + 2) + ox0 + cx) * 16 + grp], f);
+          const uint4 a = act[((oy + ky) * (DW_TW + 2) + ox0 + cx) * 16 + grp];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+          float2 f[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) f[k] = make_float2(__uint_as_float(aw[k] << 16), __uint_as_float(aw[k] & 0xFFFF0000u));
           if (cx < 3) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc0[k] = fmaf(f[k], w[cx][k], acc0[k]);
+            for (int k = 0; k < 4; ++k) acc0[k] = fma2(f[k], w[cx][k], acc0[k]);
           }
           if (cx > 0) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc1[k] = fmaf(f[k], w[cx - 1][k], acc1[k]);
+            for (int k = 0; k < 4; ++k) acc1[k] = fma2(f[k], w[cx - 1][k], acc1[k]);
           }
         }
       }
-      res[(oy * DW_TW + ox0) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc0);
-      res[(oy * DW_TW + ox0 + 1) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(acc1);
+      {
+        const float o0[8] = {acc0[0].x, acc0[0].y, acc0[1].x, acc0[1].y, acc0[2].x, acc0[2].y, acc0[3].x, acc0[3].y};
+        const float o1[8] = {acc1[0].x, acc1[0].y, acc1[1].x, acc1[1].y, acc1[2].x, acc1[2].y, acc1[3].x, acc1[3].y};
+        res[(oy * DW_TW + ox0) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(o0);
+        res[(oy * DW_TW + ox0 + 1) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(o1);
+      }
       if (++c_slot == DW_RING) c_slot = 0;
     }
     __syncthreads();                                          // all conv results of the tile are in res
@@ -191,30 +199,40 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
       const int py = px / DW_TW, pxx = px - py * DW_TW;
       const int Y = T.Y0 + py, X = T.X0 + pxx;
       const uint4* r = res + px * C8;
-      float v[4][8];
-      float s = 0.f;
+      float2 v[4][4];                                         // packed pairs: one instruction per two channels
+      float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (k < nk) {
-          bf16x8_to_f32(r[lane + 32 * k], v[k]);
+          const uint4 a = r[lane + 32 * k];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-          for (int e = 0; e < 8; ++e) s += v[k][e];
+          for (int e = 0; e < 4; ++e) {
+            v[k][e] = make_float2(__uint_as_float(aw[e] << 16), __uint_as_float(aw[e] & 0xFFFF0000u));
+            s2 = add2(s2, v[k][e]);
+          }
         }
       }
+      float s = s2.x + s2.y;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       const float mean = s * invC;
-      float ss = 0.f;
+      const float2 nmean = splat2(-mean);
+      float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (k < nk) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) ss = fmaf(v[k][e] - mean, v[k][e] - mean, ss);
+          for (int e = 0; e < 4; ++e) {
+            v[k][e] = add2(v[k][e], nmean);
+            q2 = fma2(v[k][e], v[k][e], q2);
+          }
         }
       }
+      float ss = q2.x + q2.y;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float rstd = rsqrtf(ss * invC + eps);
+      const float2 rstd = splat2(rsqrtf(ss * invC + eps));
       if (Y < Ho && X < Wo) {
         uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)T.b * Ho + Y) * Wo + X) * C);
 #pragma unroll
@@ -223,10 +241,15 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
             const int i = lane + 32 * k;
             const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
             const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
-            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w}, cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float2 ww[4] = {make_float2(w0.x, w0.y), make_float2(w0.z, w0.w), make_float2(w1.x, w1.y), make_float2(w1.z, w1.w)};
+            const float2 cc[4] = {make_float2(c0.x, c0.y), make_float2(c0.z, c0.w), make_float2(c1.x, c1.y), make_float2(c1.z, c1.w)};
             float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = (v[k][e] - mean) * rstd * ww[e] + cc[e];
+            for (int e = 0; e < 4; ++e) {
+              const float2 y = fma2(mul2(v[k][e], rstd), ww[e], cc[e]);
+              f[2 * e] = y.x;
+              f[2 * e + 1] = y.y;
+            }
             dst[i] = f32_to_bf16x8(f);
           }
         }

@@ -175,30 +175,43 @@ __device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8]
       for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
     }
   }
+  // statistics and affine step on packed pairs, the sums in one chain per 256-element group
   constexpr float inv_d = 1.0f / (NV * 256);
+  float2 sp[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    sp[i] = add2(add2(make_float2(v[i][0], v[i][1]), make_float2(v[i][2], v[i][3])), add2(make_float2(v[i][4], v[i][5]), make_float2(v[i][6], v[i][7])));
+  }
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) s += v[i][j];
+  for (int i = 0; i < NV; ++i) s += sp[i].x + sp[i].y;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   const float mean = s * inv_d;
+  const float2 nmean = splat2(-mean);
+  float2 c[NV][4], qp[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[i][j] = add2(make_float2(v[i][2 * j], v[i][2 * j + 1]), nmean);
+    qp[i] = mul2(c[i][0], c[i][0]);
+#pragma unroll
+    for (int j = 1; j < 4; ++j) qp[i] = fma2(c[i][j], c[i][j], qp[i]);
+  }
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float c = v[i][j] - mean;
-      ss = fmaf(c, c, ss);
-    }
+  for (int i = 0; i < NV; ++i) ss += qp[i].x + qp[i].y;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float rstd = rsqrtf(ss * inv_d + eps);
+  const float2 rstd = splat2(rsqrtf(ss * inv_d + eps));
 #pragma unroll
   for (int i = 0; i < NV; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[i][j] = (v[i][j] - mean) * rstd * ww[i][j] + bb[i][j];
+    for (int j = 0; j < 4; ++j) {
+      const float2 y = fma2(mul2(c[i][j], rstd), make_float2(ww[i][2 * j], ww[i][2 * j + 1]), make_float2(bb[i][2 * j], bb[i][2 * j + 1]));
+      v[i][2 * j] = y.x;
+      v[i][2 * j + 1] = y.y;
+    }
 }
 
 // Rows are streamed through shared memory: each warp owns a ring of LNQ_RING row buffers filled by 1-D bulk copies
@@ -258,7 +271,11 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
   for (int i = 0; i < NV; ++i) {
     if (rb) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = bf16_round(v[i][j]);
+      for (int j = 0; j < 8; j += 2) {
+        const float2 t = bf16_round2(make_float2(v[i][j], v[i][j + 1]));
+        v[i][j] = t.x;
+        v[i][j + 1] = t.y;
+      }
     }
     if (y_dbg && valid) {
       float4* yp = reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + i * 256 + lane * 8);
@@ -267,7 +284,7 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
     }
     float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    for (int j = 0; j < 8; j += 2) amax = max3(amax, fabsf(v[i][j]), fabsf(v[i][j + 1]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     if (FMT != KF_FMT_NV4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     int byte;
