@@ -30,7 +30,7 @@ constexpr int AT_THREADS = 192;
 constexpr int AT_KV = 4;                               // K / V ring depth
 constexpr int AT_QTILE = AT_BM * AT_D * 2;             // 16 KB
 constexpr int AT_KTILE = AT_BN * AT_D * 2;             // 8 KB
-constexpr int AT_OFF_Q = 0, AT_OFF_K = AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_BAR = AT_OFF_V + AT_KV * AT_KTILE;
+constexpr int AT_OFF_Q = 0, AT_OFF_K = 2 * AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_BAR = AT_OFF_V + AT_KV * AT_KTILE;
 constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
 constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128, AT_COL_P = 192;   // S buffers at columns 0 and 64, P (16-bit pairs) at 192 and 224
 
@@ -66,21 +66,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const AttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AT_OFF_BAR);
-  uint64_t *q_full = bars, *k_full = bars + 1, *v_full = k_full + AT_KV, *kv_empty = v_full + AT_KV, *s_full = kv_empty + AT_KV, *p_full = s_full + 2,
-           *o_full = p_full + 2;
+  uint64_t *q_full = bars, *q_empty = bars + 2, *k_full = bars + 4, *v_full = k_full + AT_KV, *kv_empty = v_full + AT_KV, *s_full = kv_empty + AT_KV,
+           *p_full = s_full + 2, *o_full = p_full + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   pdl_launch_dependents();                               // the next kernel of the stream may take the SMs this grid leaves
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Persistent: this CTA works through the (image, head, query tile) items blockIdx.x, blockIdx.x + gridDim.x, ...  All
+  // barriers keep running across items: K / V ring stages, S / P buffers and the O barrier are indexed by the CTA's global
+  // key-tile count G, the two Q buffers by the item count, so the loads and the first S products of the next item are
+  // under way while the current one finishes and writes its output.
   const int q_tiles = (a.N + AT_BM - 1) / AT_BM;
-  const int qt = blockIdx.x % q_tiles;
-  const int bh = blockIdx.x / q_tiles;
-  const int h = bh % a.H, b = bh / a.H;
   const int n_kt = (a.N + AT_BN - 1) / AT_BN;
+  const int items = a.B * a.H * q_tiles;
+  const int n_my = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  struct Item {
+    int qt, h, b;
+  };
+  auto item_of = [&](int it) {
+    const int item = blockIdx.x + it * gridDim.x;
+    Item r;
+    r.qt = item % q_tiles;
+    const int bh = item / q_tiles;
+    r.h = bh % a.H;
+    r.b = bh / a.H;
+    return r;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
     for (int i = 0; i < AT_KV; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
@@ -118,15 +136,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
-      mbar_expect_tx(q_full, AT_QTILE);
-      tma_load_4d(smem + AT_OFF_Q, &tmQ, 0, h, qt * AT_BM, b, q_full);
-      for (int j = 0; j < n_kt; ++j) {
-        const int st = j % AT_KV;
-        if (!mbar_wait(&kv_empty[st], ((j / AT_KV) & 1) ^ 1, ctx, 11)) break;
-        mbar_expect_tx(&k_full[st], AT_KTILE);
-        tma_load_4d(smem + AT_OFF_K + st * AT_KTILE, &tmK, 0, h, j * AT_BN, b, &k_full[st]);
-        mbar_expect_tx(&v_full[st], AT_KTILE);
-        tma_load_4d(smem + AT_OFF_V + st * AT_KTILE, &tmV, 0, h, j * AT_BN, b, &v_full[st]);
+      uint32_t G = 0;
+      bool ok = true;
+      for (int it = 0; it < n_my && ok; ++it) {
+        const Item I = item_of(it);
+        const int qb = it & 1;
+        if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1) ^ 1, ctx, 10)) break;          // the S products of item it - 2 are done with this buffer
+        mbar_expect_tx(&q_full[qb], AT_QTILE);
+        tma_load_4d(smem + AT_OFF_Q + qb * AT_QTILE, &tmQ, 0, I.h, I.qt * AT_BM, I.b, &q_full[qb]);
+        for (int j = 0; j < n_kt; ++j, ++G) {
+          const int st = G % AT_KV;
+          if (!mbar_wait(&kv_empty[st], ((G / AT_KV) & 1) ^ 1, ctx, 11)) { ok = false; break; }
+          mbar_expect_tx(&k_full[st], AT_KTILE);
+          tma_load_4d(smem + AT_OFF_K + st * AT_KTILE, &tmK, 0, I.h, j * AT_BN, I.b, &k_full[st]);
+          mbar_expect_tx(&v_full[st], AT_KTILE);
+          tma_load_4d(smem + AT_OFF_V + st * AT_KTILE, &tmV, 0, I.h, j * AT_BN, I.b, &v_full[st]);
+        }
       }
     }
     __syncwarp();
@@ -136,41 +161,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t fmt = a.f16 ? 0u : 1u;
       const uint32_t idesc_s = idesc_f16(fmt, AT_BN);
       const uint32_t idesc_o = idesc_f16(fmt, AT_D) | (1u << 16);          // B (= V) is MN-major
-      const uint64_t qdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_Q));
       const uint32_t t_o = tmem_base + AT_COL_O;
-      auto issue_s = [&](int t) {                                         // S(t) = Q K(t)^T into S buffer t & 1
-        const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + (t % AT_KV) * AT_KTILE));
-        const uint32_t t_s = tmem_base + AT_COL_S + (t & 1) * AT_BN;
+      const uint32_t total = (uint32_t)n_my * (uint32_t)n_kt;                // key-tile steps of this CTA over all its items
+      bool ok = true;
+      auto issue_s = [&](uint32_t G) {                                    // S(G) = Q K^T into S buffer G & 1
+        const uint32_t it = G / (uint32_t)n_kt, j = G - it * (uint32_t)n_kt;
+        if (j == 0 && !mbar_wait(&q_full[it & 1], (it >> 1) & 1, ctx, 12)) { ok = false; return; }
+        if (!mbar_wait(&k_full[G % AT_KV], (G / AT_KV) & 1, ctx, 13)) { ok = false; return; }
+        tc_fence_after();
+        const uint64_t qdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_Q + (it & 1) * AT_QTILE));
+        const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + (G % AT_KV) * AT_KTILE));
+        const uint32_t t_s = tmem_base + AT_COL_S + (G & 1) * AT_BN;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
-        tc_commit(&s_full[t & 1]);
+        tc_commit(&s_full[G & 1]);
+        if (j == (uint32_t)n_kt - 1) tc_commit(&q_empty[it & 1]);        // the item's last S product: its Q buffer is free once it completes
       };
-      bool ok = mbar_wait(q_full, 0, ctx, 12);
-      for (int t = 0; t < 2 && t < n_kt && ok; ++t) {
-        ok = mbar_wait(&k_full[t % AT_KV], (t / AT_KV) & 1, ctx, 13);
-        if (ok) {
-          tc_fence_after();
-          issue_s(t);
-        }
-      }
-      for (int j = 0; j < n_kt && ok; ++j) {
-        const int st = j % AT_KV;
-        if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, ctx, 14)) break;
-        if (!mbar_wait(&v_full[st], (j / AT_KV) & 1, ctx, 15)) break;
+      for (uint32_t t = 0; t < 2 && t < total && ok; ++t) issue_s(t);
+      uint32_t j = 0;
+      for (uint32_t G = 0; G < total && ok; ++G) {
+        const uint32_t st = G % AT_KV;
+        if (!mbar_wait(&p_full[G & 1], (G >> 1) & 1, ctx, 14)) break;
+        if (!mbar_wait(&v_full[st], (G / AT_KV) & 1, ctx, 15)) break;
         tc_fence_after();
-        const uint32_t t_p = tmem_base + AT_COL_P + (j & 1) * (AT_BN / 2);
+        const uint32_t t_p = tmem_base + AT_COL_P + (G & 1) * (AT_BN / 2);
         const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_KTILE));
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 8 TMEM columns of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
-          mma_f16_ta(t_o, t_p + 8 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | kk) != 0);
+          mma_f16_ta(t_o, t_p + 8 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | (uint32_t)kk) != 0);
         tc_commit(o_full);
         tc_commit(&kv_empty[st]);
-        if (j + 2 < n_kt) {                  // the softmax of tile j has consumed S buffer j & 1 (it arrived on p_full): refill it
-          const int t = j + 2;
-          if (!mbar_wait(&k_full[t % AT_KV], (t / AT_KV) & 1, ctx, 16)) break;
-          tc_fence_after();
-          issue_s(t);
-        }
+        // the softmax of step G has consumed S buffer G & 1 (it arrived on p_full): refill it, with the next item's
+        // first tiles when this item is running out
+        if (G + 2 < total) issue_s(G + 2);
+        if (++j == (uint32_t)n_kt) j = 0;
       }
     }
     __syncwarp();
@@ -180,11 +204,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float sc = a.scale_log2;
     const float thr = 8.0f / sc;
-    float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kt; ++j) {
-      const int sb = j & 1;
-      if (!mbar_wait(&s_full[sb], (j >> 1) & 1, ctx, 17)) { ok = false; break; }
+    uint32_t G = 0;                                              // key-tile steps of this CTA so far, over all its items
+    for (int it = 0; it < n_my && ok; ++it) {
+    const Item I = item_of(it);
+    const int qt = I.qt, h = I.h, b = I.b;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int j = 0; j < n_kt; ++j, ++G) {
+      const int sb = G & 1;
+      if (!mbar_wait(&s_full[sb], (G >> 1) & 1, ctx, 17)) { ok = false; break; }
       tc_fence_after();
       const int kbase = j * AT_BN;
       uint32_t r[2][32];
@@ -262,10 +290,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const uint32_t any = j > 0 ? any_need : 0u;
       l_run = l_run * alpha + sum;
-      // Every phase of o_full is consumed in order (a parity wait is only meaningful when the waiter is at most one
-      // phase behind); PV(j-1) was issued a whole softmax ago, so this wait is normally already satisfied.
-      if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, ctx, 18)) { ok = false; break; }
-      if (any) {                                                 // some row of this warp raised its maximum: rescale O in TMEM
+      // O is only touched when a row of this warp raised its maximum: PV(G-1) must have landed first.  The parity wait is
+      // unambiguous without consuming every phase of o_full: S(G), which this step began by waiting for, was issued
+      // behind PV(G-2) by the same thread and the tensor pipe completes in order, and PV(G) is not issued before this
+      // thread's arrival below, so the barrier has completed exactly G-1 or G phases here.  (The same argument makes the
+      // P buffer of this step safe to overwrite: PV(G-2) has read it.)  The item's last step always waits, so that the
+      // wait for the last product after the loop is at most one phase behind as well.
+      if ((any || j == n_kt - 1) && j > 0 && !mbar_wait(o_full, (G - 1) & 1, ctx, 18)) { ok = false; break; }
+      if (any) {                                                 // rescale O in TMEM
         tc_fence_after();
         tmem_ld32(t_lane + AT_COL_O, r[0]);
         tmem_ld32(t_lane + AT_COL_O + 32, r[1]);
@@ -283,7 +315,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       mbar_arrive(&p_full[sb]);
     }
-    if (ok) ok = mbar_wait(o_full, (n_kt - 1) & 1, ctx, 19);
+    if (ok) ok = mbar_wait(o_full, (G - 1) & 1, ctx, 19);     // the item's last PV product
     const int n = qt * AT_BM + row;
     if (ok) {
       tc_fence_after();
@@ -363,6 +395,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       }
     }
+    }   // items
   }
 
   tc_fence_before();
@@ -445,7 +478,14 @@ static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H,
   a.out_fmt = out_fmt; a.flags = flags; a.Qo = static_cast<uint8_t*>(Qo); a.SFo = static_cast<uint8_t*>(SFo); a.tso = tso;
   KF_REQUIRE(a.err != nullptr, "kf_attn_fwd: device error word unavailable");
   const int q_tiles = (N + AT_BM - 1) / AT_BM;
-  return cuda_status(launch_maybe_pdl(attn_fwd_kernel, dim3(B * H * q_tiles), dim3(AT_THREADS), (size_t)AT_SMEM, static_cast<cudaStream_t>(stream), tq, tk, tv, a),
+  const long long items = (long long)B * H * q_tiles;
+  KF_REQUIRE(items < (1ll << 30), "kf_attn_fwd: too many (image, head, query tile) items");
+  int sms = 0;
+  const int sst = device_sm_count(&sms);
+  if (sst != KF_OK) return sst;
+  const int slots = 2 * sms;                                  // two CTAs are resident per SM
+  const int grid = items < slots ? (int)items : slots;
+  return cuda_status(launch_maybe_pdl(attn_fwd_kernel, dim3(grid), dim3(AT_THREADS), (size_t)AT_SMEM, static_cast<cudaStream_t>(stream), tq, tk, tv, a),
                      "kf_attn_fwd launch");
 }
 
