@@ -261,26 +261,41 @@ __device__ __forceinline__ Nv4Scale nv4_scale(float t) {
   return s;
 }
 
-template <int NL>
-__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, const Nv4Scale& sc, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
+// The scalars of one NVFP4 block, worked out from its maximum alone: the e4m3 scale byte, the element divisor
+// dd = e4m3(scale) * ts, its correctly rounded reciprocal and how the elements are to be divided (0: the block is all
+// zeros, 1: through the reciprocal, 2: by __fdiv_rn).  Lanes that share a block, or a lane that owns several, can work
+// these out once and pass them on.
+struct Nv4Block {
+  float dd, rcp;
+  uint32_t sb;
+  int mode;
+};
+__device__ __forceinline__ Nv4Block nv4_block(float amax, const Nv4Scale& sc, bool div_true) {
   const float ts = sc.ts;
   // amax / 6 and (amax / 6) / ts are IEEE divisions; 1/6 as a constant reciprocal (RN(1/6) = 0x3E2AAAAB)
   float a6 = div_true ? div_exact(amax, 6.0f, 0.16666667163372040f, true) : amax * (1.0f / 6.0f);
   float t = fminf(div_exact(a6, ts, sc.rcp_ts, sc.safe), 448.f);
-  uint32_t sb = cvt_e4m3x2(t, 0.f) & 0xFF;
-  float denom = e4m3_to_float(sb) * ts;
+  Nv4Block b;
+  b.sb = cvt_e4m3x2(t, 0.f) & 0xFF;
+  float denom = e4m3_to_float(b.sb) * ts;
   bool ok = denom > 0.f;
-  float dd = ok ? denom : 1.0f;
+  b.dd = ok ? denom : 1.0f;
   // IEEE division of every element by the block's denominator: through one correctly rounded reciprocal when the
   // whole block stays in the normal range (|quotient| <= amax/dd), else by __fdiv_rn.
-  const float rcp = __frcp_rn(dd);
-  const float qmax = amax * rcp;
-  const bool fast = div_safe_divisor(dd) && qmax < 1e30f;
+  b.rcp = __frcp_rn(b.dd);
+  const float qmax = amax * b.rcp;
+  const bool fast = div_safe_divisor(b.dd) && qmax < 1e30f;
+  b.mode = !ok ? 0 : fast ? 1 : 2;
+  return b;
+}
+template <int NL>
+__device__ __forceinline__ void nv4_codes(const float (&v)[NL], const Nv4Block& b, uint32_t* out /* NL/8 words */) {
+  const float dd = b.dd, rcp = b.rcp;
   float q[NL];
-  if (!ok) {
+  if (b.mode == 0) {
 #pragma unroll
     for (int j = 0; j < NL; ++j) q[j] = 0.f;
-  } else if (fast) {
+  } else if (b.mode == 1) {
     const float2 r2 = splat2(rcp), nd2 = splat2(-dd);
 #pragma unroll
     for (int j = 0; j < NL; j += 2) {         // div_by_rcp on packed pairs
@@ -300,7 +315,12 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, cons
 #pragma unroll
     for (int i = 0; i < NL; i += 8) out[i / 8] = cvt_e2m1x8(q + i);
   }
-  sf_byte = (int)sb;
+}
+template <int NL>
+__device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, const Nv4Scale& sc, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
+  const Nv4Block b = nv4_block(amax, sc, div_true);
+  nv4_codes<NL>(v, b, out);
+  sf_byte = (int)b.sb;
 }
 template <int NL>
 __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, float ts, bool div_true, uint32_t* out, int& sf_byte) {

@@ -221,7 +221,7 @@ __device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8]
 constexpr int LNQ_RING = 3;
 
 template <int NV, int FMT>
-__global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+__global__ void __launch_bounds__(128, (FMT == KF_FMT_NV4 && NV == 4) ? 4 : 1) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                                        int M, int rows_pad, const float* __restrict__ ts_ptr, int flags, uint8_t* __restrict__ q,
                                                        uint8_t* __restrict__ sf, float* __restrict__ y_dbg, unsigned int* err) {
   constexpr int D = NV * 256;
@@ -267,6 +267,65 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
     fence_proxy_async_smem();
     issue(k + LNQ_RING);
   }
+  if constexpr (FMT == KF_FMT_NV4 && NV == 4) {
+    // d = 1024 in NVFP4 (the block path of the model).  A 16-value block is shared by a lane pair, and each lane meets
+    // four of them (one per 256-column chunk): the even lane works out the block scalars of chunks 0 and 2, the odd
+    // lane those of chunks 1 and 3, and the pair swaps them, instead of both doing all four.  The four scale bytes a
+    // lane ends up with are one byte of four different scale words; a 4 x 4 byte transpose over the lanes
+    // {0, 2, 4, 6} + 8g (two shuffles, two byte permutes) gives every even lane one complete word to store.
+    float amax[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (rb) {
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float2 t = bf16_round2(make_float2(v[i][j], v[i][j + 1]));
+          v[i][j] = t.x;
+          v[i][j + 1] = t.y;
+        }
+      }
+      if (y_dbg && valid) {
+        float4* yp = reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + i * 256 + lane * 8);
+        yp[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        yp[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      }
+      float am = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) am = max3(am, fabsf(v[i][j]), fabsf(v[i][j + 1]));
+      amax[i] = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    }
+    const int par = lane & 1;
+    Nv4Block own[2], oth[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      own[h] = nv4_block(par ? amax[2 * h + 1] : amax[2 * h], ts, div_true);
+      oth[h].dd = __shfl_xor_sync(0xffffffffu, own[h].dd, 1);
+      oth[h].rcp = __shfl_xor_sync(0xffffffffu, own[h].rcp, 1);
+      const uint32_t pk = __shfl_xor_sync(0xffffffffu, own[h].sb | ((uint32_t)own[h].mode << 8), 1);
+      oth[h].sb = pk & 0xFF;
+      oth[h].mode = (int)(pk >> 8);
+    }
+    uint32_t mine = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const bool is_own = (i & 1) == par;
+      Nv4Block b;
+      b.dd = is_own ? own[i >> 1].dd : oth[i >> 1].dd;
+      b.rcp = is_own ? own[i >> 1].rcp : oth[i >> 1].rcp;
+      b.sb = is_own ? own[i >> 1].sb : oth[i >> 1].sb;
+      b.mode = is_own ? own[i >> 1].mode : oth[i >> 1].mode;
+      uint32_t o[1];
+      nv4_codes<8>(v[i], b, o);
+      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + ((i * 256 + lane * 8) >> 1)) = o[0];
+      mine |= (valid ? b.sb : 0u) << (8 * i);
+    }
+    const int p = (lane >> 1) & 3, grp = lane >> 3;
+    const uint32_t y1 = __shfl_xor_sync(0xffffffffu, mine, 2);
+    const uint32_t n1 = __byte_perm(mine, y1, (p & 1) ? 0x3715 : 0x6240);
+    const uint32_t y2 = __shfl_xor_sync(0xffffffffu, n1, 4);
+    const uint32_t word = __byte_perm(n1, y2, (p & 2) ? 0x3276 : 0x5410);      // chunk p, k-blocks 4 * grp .. + 3 of it
+    if (par == 0) *reinterpret_cast<uint32_t*>(sf + sf_offset(row, 16 * p + 4 * grp, D >> 6)) = word;
+  } else {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (rb) {
@@ -310,6 +369,7 @@ __global__ void __launch_bounds__(128) ln_quant_kernel(const float* __restrict__
       constexpr int nkb4 = (FMT == KF_FMT_NV4) ? (D >> 6) : (D >> 7);
       *reinterpret_cast<uint32_t*>(sf + sf_offset(row, kb, nkb4)) = word;
     }
+  }
   }
   }
 }
