@@ -221,7 +221,7 @@ __device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8]
 constexpr int LNQ_RING = 3;
 
 template <int NV, int FMT>
-__global__ void __launch_bounds__(128, (FMT == KF_FMT_NV4 && NV == 4) ? 4 : 1) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
+__global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                                        int M, int rows_pad, const float* __restrict__ ts_ptr, int flags, uint8_t* __restrict__ q,
                                                        uint8_t* __restrict__ sf, float* __restrict__ y_dbg, unsigned int* err) {
   constexpr int D = NV * 256;
@@ -453,7 +453,6 @@ static int launch_ln_quant(int fmt, const float* x, const float* w, const float*
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
   unsigned grid = (unsigned)((rows_pad + 3) / 4);
-  if (grid > (unsigned)sms * 4) grid = (unsigned)sms * 4;          // persistent: about 4 CTAs of 4 warps per SM
   uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
   unsigned int* err = dev_error_ptr();
   KF_REQUIRE(err != nullptr, "kf_ln_quant: device error word unavailable");
@@ -461,6 +460,14 @@ static int launch_ln_quant(int fmt, const float* x, const float* w, const float*
   auto go = [&](auto kern) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_quant_kernel)");
+    // persistent: as many CTAs of 4 warps as are resident at once (4 per SM up to d = 1024, fewer for wider rows); a
+    // grid beyond that would run its surplus as a second, nearly empty wave
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem);
+    if (e != cudaSuccess) return cuda_status(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(ln_quant_kernel)");
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    if (grid > (unsigned)(sms * per_sm)) grid = (unsigned)(sms * per_sm);
     return cuda_status(launch_maybe_pdl(kern, dim3(grid), dim3(128), smem, st, x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg, err), "kf_ln_quant launch");
   };
   if (fmt == KF_FMT_MX8) return go(ln_quant_kernel<NV, KF_FMT_MX8>);
