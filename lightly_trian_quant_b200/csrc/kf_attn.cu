@@ -329,26 +329,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float inv = 1.0f / l_run;
         const bool div_true = !(a.flags & KF_Q_RECIP_DIV);
         float v[64];
+        const float2 inv2 = splat2(inv);
+        auto norm_round = [&](auto is_f16) {                       // O / l rounded to the 16-bit type, as packed pairs
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v[i] = __uint_as_float(r0[i]) * inv;
-          v[32 + i] = __uint_as_float(r1[i]) * inv;
-        }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) v[i] = a.f16 ? __half2float(__float2half_rn(v[i])) : bf16_round(v[i]);
+          for (int i = 0; i < 32; i += 2) {
+            float2 x = mul2(make_float2(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1])), inv2);
+            float2 y = mul2(make_float2(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1])), inv2);
+            if (decltype(is_f16)::value) {
+              x = __half22float2(__float22half2_rn(x));
+              y = __half22float2(__float22half2_rn(y));
+            } else {
+              x = bf16_round2(x);
+              y = bf16_round2(y);
+            }
+            v[i] = x.x;
+            v[i + 1] = x.y;
+            v[32 + i] = y.x;
+            v[33 + i] = y.y;
+          }
+        };
+        if (a.f16) norm_round(std::integral_constant<int, 1>{});
+        else norm_round(std::integral_constant<int, 0>{});
         const size_t m = (size_t)b * a.N + n;
         const int d = a.H * AT_D;
         if (a.out_fmt == KF_FMT_NV4) {
-          const float tso = __ldg(a.tso);
+          const Nv4Scale tsc = nv4_scale(__ldg(a.tso));        // per-tensor scale, its reciprocal and range check once per row
           uint32_t o[8], word = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const float(&blk)[16] = *reinterpret_cast<const float(*)[16]>(&v[16 * k]);
             float am = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(blk[i]));
+            for (int i = 0; i < 16; i += 2) am = max3(am, fabsf(blk[i]), fabsf(blk[i + 1]));
             int by;
-            quant_nv4<16>(blk, am, tso, div_true, o + 2 * k, by);
+            quant_nv4<16>(blk, am, tsc, div_true, o + 2 * k, by);
             word |= (uint32_t)by << (8 * k);
           }
           uint4* dst = reinterpret_cast<uint4*>(a.Qo + m * (d >> 1) + h * 32);
@@ -363,7 +377,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[32 * k + 16]);
             float am = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(v[32 * k + i]));
+            for (int i = 0; i < 32; i += 2) am = max3(am, fabsf(v[32 * k + i]), fabsf(v[32 * k + i + 1]));
             int by;
             if (a.out_fmt == KF_FMT_MX8) {
               uint32_t o[8];

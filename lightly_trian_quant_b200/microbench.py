@@ -126,9 +126,17 @@ def bench_attn(args):
     dt = torch.float16 if args.dtype == "f16" else BF
     qkvs = [torch.randn(3, B, N, H, 64, device="cuda").to(dt) for _ in range(2)]
     outs = [torch.empty(B, N, H * 64, device="cuda", dtype=dt) for _ in range(2)]
-    t = _time(lambda i: ops.attn_fwd(qkvs[i % 2], out=outs[i % 2]), args.iters)
+    if args.quant_out:                      # the form the block uses: O quantised into the proj GEMM's operand
+        bufs = [ops.ActBuf(B * N, H * 64, args.fmt, device="cuda") for _ in range(2)]
+        for b in bufs:
+            if b.ts is not None:
+                b.ts.fill_(0.01)
+        t = _time(lambda i: ops.attn_fwd_quant(qkvs[i % 2], bufs[i % 2]), args.iters)
+    else:
+        t = _time(lambda i: ops.attn_fwd(qkvs[i % 2], out=outs[i % 2]), args.iters)
     fl = 4.0 * B * H * N * N * 64
-    return {"kernel": f"attn_fwd {args.dtype}", "B": B, "N": N, "H": H, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
+    tag = f" + {args.fmt} quantise-out" if args.quant_out else ""
+    return {"kernel": f"attn_fwd {args.dtype}{tag}", "B": B, "N": N, "H": H, "us": t * 1e6, "TFLOP/s": fl / t / 1e12}
 
 
 def bench_ln_quant(args):
@@ -183,6 +191,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cold", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
+    ap.add_argument("--quant-out", action="store_true", help="attn: fused quantisation of the output in --fmt")
     args = ap.parse_args()
     torch.set_grad_enabled(False)
     fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak}[args.what]
