@@ -3,18 +3,23 @@
 //
 //   input    qkv [3, B, N, H, 64] bf16 | f16 (the physical layout the qkv GEMM epilogue writes)
 //   output   O [B, N, H*64] bf16 | f16, or directly the quantised operand of the proj GEMM (kf_attn_fwd_quant)
-//   CTA      128 query rows of one (batch, head); key tiles of 64; two CTAs per SM
+//   CTA      persistent, two per SM; an item is 128 query rows of one (batch, head), key tiles of 64; a CTA takes the
+//            items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps every barrier phase running across them
 //   roles    warps 0..3: softmax, one query row per thread (tcgen05.ld of the S row, running max / sum in fp32,
-//            P -> 16 bit -> swizzled smem); warp 4: TMA producer (Q once, K / V in a 3-deep ring, 4-D tensor maps
-//            so rows past N read zero); warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16; O += P V: 4 MMAs of K=16 with
-//            V as the MN-major operand)
-//   pipeline S is double buffered in TMEM and P in shared memory: S(j+1) is computed while the softmax of tile j
-//            runs, so the softmax warps - whose exp2 work on the MUFU unit is the bound of this kernel - never wait
-//            for a tensor-core round trip.  O accumulates in TMEM over all key tiles; the running maximum is raised
-//            only when a tile maximum exceeds it by more than 2^8 in the exponent domain, so the rescale of O (TMEM
-//            load, multiply, store) happens on the first tiles and then almost never.
-//   numerics softmax scale 1/8 folded into exp2 (fp32, one MUFU operation per element; the packed f16x2 exp2 was
-//            measured slower); m, l, O in fp32; P rounded to the input 16-bit type.  Every mbarrier wait is bounded.
+//            P -> 16 bit -> tensor memory by tcgen05.st); warp 4: TMA producer (Q in two buffers, K / V in a 4-deep
+//            ring, 4-D tensor maps so rows past N read zero); warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16 from
+//            shared memory; O += P V: 4 MMAs of K=16 with P as the A operand from tensor memory and V as the MN-major
+//            B operand)
+//   pipeline S and P are double buffered in TMEM: S(j+2) is issued as soon as the softmax of tile j has handed P(j)
+//            over, also across the end of an item (the next item's Q and first K tiles are loaded by then), so the
+//            softmax warps - whose dependent chain of S load, exponentials, P store and hand-over is the bound of this
+//            kernel - do not wait for a tensor-core round trip.  O accumulates in TMEM over all key tiles; the running
+//            maximum is raised only when a tile maximum exceeds it by more than 2^8 in the exponent domain, so the
+//            rescale of O (TMEM load, multiply, store) happens on the first tiles and then almost never, and the O
+//            barrier is waited only then and at the end of an item.
+//   numerics softmax scale 1/8 folded into exp2 (fp32, one MUFU operation per element; the exponent arguments and
+//            the row sums as packed fp32 pairs; the packed f16x2 exp2 was measured slower); m, l, O in fp32; P rounded
+//            to the input 16-bit type.  Every mbarrier wait is bounded.
 //
 // Replaces a16::fwd_kernel / attn16_fwd (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404; mma.sync m16n8k16 +
 // TMA on sm_120).  The power-of-two Q pre-scale `pre` of the reference protects its fp16 accumulators
