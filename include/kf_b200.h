@@ -177,6 +177,13 @@ KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H,
  * Counterpart: the mma.sync probe infer-opt/round10_lowp_probe/peak_extra.cu. */
 KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream);
 
+/* Shared-memory fill-rate probe: every SM streams `iters` stages of `stage_bytes` (a multiple of 1024, <= 65536) from the
+ * `span` bytes at `src` into a three-stage shared-memory ring with bulk copies and consumes nothing; *bytes_per_launch
+ * receives the bytes one launch moves.  With a span that fits L2 this is the L2 -> shared-memory rate that feeds a GEMM main
+ * loop whose operands are re-read from L2 (the CTAs' walks over the span overlap, so a larger span is not an HBM figure).
+ * The caller times the launch.  No reference counterpart. */
+KF_API int kf_fill_rate_probe(const void* src, long long span, int stage_bytes, int iters, double* bytes_per_launch, void* stream);
+
 /* The same attention forward with the quantisation of its output fused into the epilogue: the O row of every head is
  * rounded to the 16-bit input type and written as codes + blocked scales of the [B*N, H*64] operand the proj GEMM
  * reads (format out_fmt, nv4 with the static per-tensor scale tso).  Scale rows B*N..pad128(B*N) are not touched.

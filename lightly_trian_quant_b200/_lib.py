@@ -63,6 +63,7 @@ def lib() -> C.CDLL:
             "kf_check_device_error": [],
             "kf_attn_fwd": [i32, vp, vp, i32, i32, i32, f32, vp],
             "kf_tensor_peak_probe": [i32, i32, i32, i32, C.POINTER(C.c_double), vp],
+            "kf_fill_rate_probe": [vp, C.c_int64, i32, i32, C.POINTER(C.c_double), vp],
             "kf_attn_fwd_quant": [i32, vp, i32, i32, i32, f32, i32, vp, vp, vp, i32, vp],
             "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp],
             "kf_im2col_patch16": [vp, vp, i32, i32, vp],

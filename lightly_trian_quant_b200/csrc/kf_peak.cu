@@ -86,9 +86,68 @@ static int launch_peak(int n, int iters, int sf_copies, int sms, unsigned int* e
   return n == 256 ? go(peak_kernel<KIND, 256>) : n == 128 ? go(peak_kernel<KIND, 128>) : go(peak_kernel<KIND, 64>);
 }
 
+// ------------------------------------------------------------------------------------------------ fill-rate probe
+// What a GEMM main loop can be fed: every SM streams `iters` stages of `stage_bytes` from global memory into a
+// three-stage shared-memory ring with 1-D bulk copies (16 KB pieces, completion on an mbarrier), refilling a stage as
+// soon as it has landed; nothing consumes the data.  The source window of `span` bytes is walked by all CTAs at
+// staggered offsets (the walks overlap): with a window that fits L2 this is the L2 -> shared-memory rate.
+constexpr int FILL_STAGES = 3, FILL_MAX_STAGE = 65536, FILL_SMEM = FILL_STAGES * FILL_MAX_STAGE + 64;
+
+__global__ void __launch_bounds__(128, 1) fill_kernel(const uint8_t* __restrict__ src, size_t span, int stage_bytes, int iters, unsigned int* err) {
+  extern __shared__ __align__(128) uint8_t fsm[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fsm + FILL_STAGES * FILL_MAX_STAGE);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + FILL_STAGES);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < FILL_STAGES; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const WaitCtx ctx{abort_flag, err};
+    const size_t slots = span / (size_t)stage_bytes;            // the host guarantees slots >= 1
+    size_t slot = ((size_t)blockIdx.x * 7919u) % slots;
+    bool ok = true;
+    for (int it = 0; it < iters + FILL_STAGES && ok; ++it) {
+      const int s = it % FILL_STAGES;
+      if (it >= FILL_STAGES) ok = mbar_wait(&bars[s], ((it / FILL_STAGES) - 1) & 1, ctx, 40);   // the stage's previous fill has landed
+      if (ok && it < iters) {
+        mbar_expect_tx(&bars[s], (uint32_t)stage_bytes);
+        const uint8_t* g = src + slot * (size_t)stage_bytes;
+        for (int off = 0; off < stage_bytes; off += 16384) {
+          const int n = stage_bytes - off < 16384 ? stage_bytes - off : 16384;
+          bulk_load_1d(fsm + (size_t)s * FILL_MAX_STAGE + off, g + off, (uint32_t)n, &bars[s]);
+        }
+        if (++slot == slots) slot = 0;
+      }
+    }
+    if (!ok) {                                                    // a wait ran out: give copies in flight time to land
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+  }
+  __syncthreads();
+}
+
 }  // namespace kf
 
 using namespace kf;
+
+extern "C" int kf_fill_rate_probe(const void* src, long long span, int stage_bytes, int iters, double* bytes_per_launch, void* stream) {
+  KF_REQUIRE(src && (reinterpret_cast<uintptr_t>(src) & 15) == 0, "kf_fill_rate_probe: src must be non-null and 16-byte aligned");
+  KF_REQUIRE(stage_bytes >= 1024 && stage_bytes <= FILL_MAX_STAGE && stage_bytes % 1024 == 0, "kf_fill_rate_probe: stage_bytes must be a multiple of 1024 up to 65536");
+  KF_REQUIRE(span >= stage_bytes, "kf_fill_rate_probe: span must hold at least one stage");
+  KF_REQUIRE(iters > 0 && iters <= (1 << 22), "kf_fill_rate_probe: iters out of range");
+  int sms = 0;
+  int st = device_sm_count(&sms);
+  if (st != KF_OK) return st;
+  unsigned int* err = dev_error_ptr();
+  KF_REQUIRE(err != nullptr, "kf_fill_rate_probe: device error word unavailable");
+  cudaError_t e = cudaFuncSetAttribute(fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FILL_SMEM);
+  if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(fill_kernel)");
+  if (bytes_per_launch) *bytes_per_launch = (double)stage_bytes * iters * sms;
+  fill_kernel<<<sms, 128, FILL_SMEM, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(src), (size_t)span, stage_bytes, iters, err);
+  return cuda_status(cudaGetLastError(), "kf_fill_rate_probe launch");
+}
 
 extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream) {
   KF_REQUIRE(fmt >= KF_FMT_MX8 && fmt <= KF_FMT_BF16, "kf_tensor_peak_probe: unknown format %d", fmt);

@@ -179,9 +179,17 @@ def bench_peak(args):
     return out
 
 
+def bench_fill(args):
+    out = {"kernel": "shared-memory fill-rate probe (bulk copies, 3-stage ring, 148 SMs)"}
+    for span_mb in (4, 32, 96):            # windows that stay in L2 (126 MB): the rate a main loop re-reading its operands sees
+        for stage in (16384, 32768, 49152, 65536):
+            out[f"GB/s_span{span_mb}MB_stage{stage // 1024}KB"] = round(ops.smem_fill_rate_gbs(span_mb << 20, stage), 1)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "lib_gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak"])
+    ap.add_argument("what", choices=["gemm", "lib_gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak", "fill"])
     ap.add_argument("--fmt", default="nv4")
     ap.add_argument("--kind", default="fc1", choices=list(SHAPES))
     ap.add_argument("--batch", type=int, default=8)
@@ -194,7 +202,7 @@ def main():
     ap.add_argument("--quant-out", action="store_true", help="attn: fused quantisation of the output in --fmt")
     args = ap.parse_args()
     torch.set_grad_enabled(False)
-    fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak}[args.what]
+    fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak, "fill": bench_fill}[args.what]
     print(json.dumps(fn(args)), flush=True)
 
 

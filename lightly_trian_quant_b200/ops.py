@@ -424,3 +424,23 @@ def tensor_peak_tflops(fmt: str, n: int = 256, iters: int = 4096, reps: int = 5,
         e1.synchronize()
         best = max(best, fl.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
     return best
+
+
+def smem_fill_rate_gbs(span_bytes: int, stage_bytes: int = 49152, iters: int = 2048, reps: int = 5) -> float:
+    """measured rate (GB/s, all SMs together) at which bulk copies fill shared memory from a window of span_bytes of
+    global memory that fits L2 (best of reps)."""
+    import ctypes as C
+
+    src = torch.empty(span_bytes, dtype=torch.uint8, device="cuda").zero_()
+    nb = C.c_double(0.0)
+    L = _lib.lib()
+    best = 0.0
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(L.kf_fill_rate_probe(src.data_ptr(), span_bytes, stage_bytes, iters, C.byref(nb), _stream()), "kf_fill_rate_probe")
+        e1.record()
+        e1.synchronize()
+        best = max(best, nb.value / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    check_device_error()
+    return best

@@ -231,3 +231,15 @@ def test_gemm_pair_kernel_is_bitwise_the_one_cta_kernel(fmt, monkeypatch):
     wd = w.float().numpy() if fmt == "bf16" else go.dequant_operand(W.q.cpu().numpy(), W.sf.cpu().numpy(), W.ts.cpu().numpy() if W.ts is not None else None, fmt, N, K)
     ref = go.matmul_ref(ad, wd) + bias.cpu().numpy().astype(np.float64)
     assert go.rel_fro(two["plain"].float().cpu().numpy(), ref) < 2e-3
+
+
+def test_rate_probes_run_and_report_work():
+    """the tensor-core instruction-rate probe and the shared-memory fill-rate probe (roofline denominators and the feed
+    ceiling of the GEMM main loop) run to completion, leave no device error and report a plausible rate."""
+    ops = _ops()
+    for fmt in ("nv4", "mx8", "bf16"):
+        tf = ops.tensor_peak_tflops(fmt, 256, iters=512, reps=1)
+        assert 100.0 < tf < 20000.0, (fmt, tf)
+    gbs = ops.smem_fill_rate_gbs(8 << 20, 49152, iters=256, reps=1)
+    assert 500.0 < gbs < 100000.0, gbs
+    ops.check_device_error()
