@@ -197,7 +197,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 64-column group)
     const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     const int cg = (warp - 2) >> 2;               // which 64-column group of the 256-column tile
-    float* stg = Pipe<EPI>::STAGING ? reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * STG_WARP_BYTES) : nullptr;
+    float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * Pipe<EPI>::STG_STRIDE);   // staging tile, or the warp's bias slice
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
@@ -208,6 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int rbase = m_blk * BM + quarter * 32;
       const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
       uint32_t r0[32], r1[32];
+      epilogue_bias_stage<EPI>(g, n0, stg, lane);
       if (!mbar_wait(tfull, lt & 1, ctx, 4)) break;
       tc_fence_after();
       tmem_ld32(taddr, r0);

@@ -25,7 +25,10 @@ constexpr int TMEM_SF_COL = 256;                       // accumulator: columns [
 template <int EPI>
 struct Pipe {
   static constexpr bool STAGING = EPI == KF_EPI_RES || EPI == KF_EPI_ROPE;
-  static constexpr int STG_BYTES = STAGING ? EPI_WARPS * STG_WARP_BYTES : 0;
+  // per epilogue warp: a 32 x 32 fp32 staging tile (RES / ROPE), else the 64 bias values of the warp's columns (the
+  // kernel's shared memory leaves little L1, so bias loads inside the chunk loops would each wait on L2)
+  static constexpr int STG_STRIDE = STAGING ? STG_WARP_BYTES : 256;
+  static constexpr int STG_BYTES = EPI_WARPS * STG_STRIDE;
   static constexpr int STAGES = 3;
   static constexpr size_t SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + STG_BYTES + 256;
 };
@@ -105,13 +108,13 @@ __device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
 
 // QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
 // or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
-__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, int m, int n0) {
+__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, int m, int n0, const float* bsm /* the chunk's 32 bias values in shared memory */) {
   const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
   const bool ok = m < g.M;
   float v[32];
 #pragma unroll
   for (int q4 = 0; q4 < 8; ++q4) {
-    const float4 bb = g.bias ? ldg4(g.bias + n0 + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
     const float2 ts2 = splat2(ts);
     const float2 a = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1])), ts2, make_float2(bb.x, bb.y)));
     const float2 b = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4 + 2]), __uint_as_float(r[4 * q4 + 3])), ts2, make_float2(bb.z, bb.w)));
@@ -167,13 +170,13 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
 }
 
 // PLAIN epilogue of one 32-column chunk in the row layout: the thread writes 64 (16-bit) or 128 (fp32) contiguous bytes.
-__device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, uint8_t* dst_row, int n0) {
+__device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, uint8_t* dst_row, int n0, const float* bsm /* the chunk's 32 bias values in shared memory */) {
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     float v[8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const float4 bb = g.bias ? ldg4(g.bias + n0 + 8 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + 8 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
       const float b4[4] = {bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -193,6 +196,21 @@ __device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&
         const uint2 lo = pack4(make_float4(v[0], v[1], v[2], v[3]), g.out_dtype), hi = pack4(make_float4(v[4], v[5], v[6], v[7]), g.out_dtype);
         *reinterpret_cast<uint4*>(dst_row + (size_t)(n0 + 8 * q) * 2) = make_uint4(lo.x, lo.y, hi.x, hi.y);
       }
+    }
+  }
+}
+
+// PLAIN / QUANT: the 64 bias values of the warp's columns go to its shared-memory slice (one coalesced load per tile,
+// issued before the wait for the accumulator so that its L2 latency runs under that wait); the chunk loops then read
+// them as broadcast float4s.
+template <int EPI>
+__device__ __forceinline__ void epilogue_bias_stage(const GemmArgs& g, int n0, float* stg, int lane) {
+  if constexpr (!Pipe<EPI>::STAGING) {
+    if (g.bias && n0 < g.N) {
+      const float2 b2 = __ldg(reinterpret_cast<const float2*>(g.bias + n0) + lane);
+      __syncwarp();                                // every lane has finished reading the previous tile's values
+      reinterpret_cast<float2*>(stg)[lane] = b2;
+      __syncwarp();
     }
   }
 }
@@ -293,11 +311,11 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
       const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
       dst_row = static_cast<uint8_t*>(g.C) + (size_t)orow * g.N * (g.out_dtype == KF_F32 ? 4 : 2);
     }
-    plain_chunk(g, r0, ts, dst_row, n0);
-    plain_chunk(g, r1, ts, dst_row, n0 + 32);
+    plain_chunk(g, r0, ts, dst_row, n0, stg);
+    plain_chunk(g, r1, ts, dst_row, n0 + 32, stg + 32);
   } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-    quant_chunk(g, r0, ts, rbase + lane, n0);
-    quant_chunk(g, r1, ts, rbase + lane, n0 + 32);
+    quant_chunk(g, r0, ts, rbase + lane, n0, stg);
+    quant_chunk(g, r1, ts, rbase + lane, n0 + 32, stg + 32);
   }
 }
 
