@@ -211,6 +211,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float thr = 8.0f / sc;
     bool ok = true;
     uint32_t G = 0;                                              // key-tile steps of this CTA so far, over all its items
+    // per-tensor scale of an NVFP4 output, its reciprocal and range check: one L2 round trip per CTA, not per item
+    const Nv4Scale tsc = nv4_scale(a.out_fmt == KF_FMT_NV4 ? __ldg(a.tso) : 1.f);
     for (int it = 0; it < n_my && ok; ++it) {
     const Item I = item_of(it);
     const int qt = I.qt, h = I.h, b = I.b;
@@ -358,7 +360,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const size_t m = (size_t)b * a.N + n;
         const int d = a.H * AT_D;
         if (a.out_fmt == KF_FMT_NV4) {
-          const Nv4Scale tsc = nv4_scale(__ldg(a.tso));        // per-tensor scale, its reciprocal and range check once per row
           uint32_t o[8], word = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {

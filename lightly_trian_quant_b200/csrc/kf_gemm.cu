@@ -201,6 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
+    const float tso = (EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f;   // once per CTA: every global load here is an L2 round trip
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
@@ -209,6 +210,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
       uint32_t r0[32], r1[32];
       epilogue_bias_stage<EPI>(g, n0, stg, lane);
+      EpiPre pre;
+      epilogue_prefetch<EPI>(g, n0, lane, pre);
       if (!mbar_wait(tfull, lt & 1, ctx, 4)) break;
       tc_fence_after();
       tmem_ld32(taddr, r0);
@@ -219,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
       if (n0 >= g.N) continue;                                   // column group past N in the last column tile
 
-      epilogue_math<EPI>(g, r0, r1, ts, rbase, n0, stg, lane);
+      epilogue_math<EPI>(g, r0, r1, ts, tso, rbase, n0, stg, lane, pre);
     }
   }
 

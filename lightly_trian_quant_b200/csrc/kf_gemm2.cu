@@ -212,6 +212,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
+    const float tso = (EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f;   // once per CTA: every global load here is an L2 round trip
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     const uint32_t leader_tempty = map_to_rank(tempty, 0);
     uint32_t lt = 0;
@@ -221,6 +222,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = n_blk * BN + cg * 64;
       uint32_t r0[32], r1[32];
       epilogue_bias_stage<EPI>(g, n0, stg, lane);
+      EpiPre pre;
+      epilogue_prefetch<EPI>(g, n0, lane, pre);
       if (!mbar_wait_cluster(tfull, lt & 1, ctx, 4)) break;
       tc_fence_after();
       tmem_ld32(taddr, r0);
@@ -230,7 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_tempty);          // the accumulator is in registers: hand TMEM back (to the leader's MMA warp)
       if (n0 >= g.N || rbase >= g.m_tiles * 128) continue;        // column group past N, or the follower's row block past the last one
-      epilogue_math<EPI>(g, r0, r1, ts, rbase, n0, stg, lane);
+      epilogue_math<EPI>(g, r0, r1, ts, tso, rbase, n0, stg, lane, pre);
     }
   }
 

@@ -108,7 +108,8 @@ __device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
 
 // QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
 // or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
-__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, int m, int n0, const float* bsm /* the chunk's 32 bias values in shared memory */) {
+__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, float tso /* per-tensor scale of an nv4 output */, int m, int n0,
+                                            const float* bsm /* the chunk's 32 bias values in shared memory */) {
   const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
   const bool ok = m < g.M;
   float v[32];
@@ -142,7 +143,7 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
   int by0, by1;
   if (g.out_fmt == KF_FMT_NV4) {
     uint32_t o[4];
-    const float tso = __ldg(g.tso), rcp_tso = __frcp_rn(tso);
+    const float rcp_tso = __frcp_rn(tso);
     quant_nv4_fast<16>(va, am0, tso, rcp_tso, o, by0);
     quant_nv4_fast<16>(vb, am1, tso, rcp_tso, o + 2, by1);
     if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -218,8 +219,27 @@ __device__ __forceinline__ void epilogue_bias_stage(const GemmArgs& g, int n0, f
 // ------------------------------------------------------------------------------------------------ the fused epilogues
 // One epilogue warp's share of a tile: rows rbase..rbase+31 (thread `lane` holds row rbase + lane of the accumulator),
 // columns n0..n0+63 (r0 = first 32, r1 = last 32).  `stg` is the warp's private 32 x 32 fp32 staging tile.
+// What an epilogue can fetch before its accumulator exists: ROPE takes its two bias vectors, which then land during the
+// wait for the accumulator instead of in front of the first arithmetic (qkv 90 -> 86 us).  The same for the first round
+// of residual loads of RES was measured slower (proj 55 -> 59 us): 24 more registers live across the accumulator load
+// spill under the 96-register cap of the 608-thread CTA.
+struct EpiPre {
+  float4 b0, b1;
+};
 template <int EPI>
-__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, int rbase, int n0, float* stg, int lane) {
+__device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int n0, int lane, EpiPre& p) {
+  if constexpr (EPI == KF_EPI_ROPE) {
+    const int c4 = 4 * (lane & 7);
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n0 >= g.N) return;
+    p.b0 = g.bias ? ldg4(g.bias + n0 + c4) : z4;
+    p.b1 = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
+  }
+}
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, float tso, int rbase, int n0, float* stg,
+                                              int lane, const EpiPre& pre) {
   const int c4 = 4 * (lane & 7);                // coalesced layout: this lane's 4 columns inside a 32-column chunk
   const int rsub = lane >> 3;                   // coalesced layout: row 4*i + rsub in pass i
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -230,7 +250,7 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
     const int nbatch = g.M / g.Ntok;
     const int b0 = rbase / g.Ntok, t0 = rbase - b0 * g.Ntok;   // one division per tile; rows advance from here
-    const float4 b_lo = g.bias ? ldg4(g.bias + n0 + c4) : z4, b_hi = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
+    const float4 b_lo = pre.b0, b_hi = pre.b1;
     float4 lo[8];
     stg_put(stg, lane, r0);
     __syncwarp();
@@ -314,8 +334,8 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     plain_chunk(g, r0, ts, dst_row, n0, stg);
     plain_chunk(g, r1, ts, dst_row, n0 + 32, stg + 32);
   } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-    quant_chunk(g, r0, ts, rbase + lane, n0, stg);
-    quant_chunk(g, r1, ts, rbase + lane, n0 + 32, stg + 32);
+    quant_chunk(g, r0, ts, tso, rbase + lane, n0, stg);
+    quant_chunk(g, r1, ts, tso, rbase + lane, n0 + 32, stg + 32);
   }
 }
 
