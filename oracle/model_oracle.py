@@ -8,9 +8,12 @@ and the rounding points of its right-hand dataflow: the LN output, the attention
 rounded to bf16 before they are quantised-dequantised; q, k, v are bf16; the residual stream is fp32; weights are the
 bf16-rounded module weights quantised-dequantised once.  The input size is a parameter (the reference hard-codes 512).
 
-EmuNet itself cannot run outside an sm_120a GPU (emu.py:25-33), so this restatement is pinned only through the
-quantiser oracle it calls (bit-exact against the reference's quant_ref.py) and through the torch definition of the
-model; "parity unpinned" for the model-level numbers beyond that.
+Pinning: the model semantics (token order, RoPE tables and placement, qkv split, K-masked bias, LayerScale / residual
+order, ScaleBlock layout) are pinned to the reference's own DinoVisionTransformer / SelfAttentionBlock / ScaleBlock through
+tests/golden/model_golden.npz (tests/test_model_pin_cpu.py runs this file's block at format "bf16" against the reference
+block's output); the quantiser it calls is bit-exact against the reference's quant_ref.py.  EmuNet itself cannot run
+outside an sm_120a GPU (emu.py:25-33), so the PLACEMENT of its rounding points (which tensors are rounded to bf16 and
+quantised-dequantised, emu.py:260-333) is restated from the source and is the one part that stays "parity unpinned".
 """
 from __future__ import annotations
 
