@@ -2,8 +2,8 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream (as void*), launches on that stream and
  * returns without synchronising: 0 = ok, negative = bad argument (see kf_last_error_string), positive = the
- * cudaError_t of a failed launch.  The caller owns every buffer; nothing here allocates (the one exception is
- * documented on the entry point).  One thread per device may call concurrently.
+ * cudaError_t of a failed launch.  The caller owns every buffer and nothing here allocates device memory.  One thread
+ * per device may call concurrently.
  *
  * Each declaration cites the reference interface it replaces (paths relative to the reference checkout).
  */
@@ -44,6 +44,9 @@ extern "C" {
 #define KF_Q_GELU 1        /* x <- gelu_erf(x + bias[col]) before quantising                         */
 #define KF_Q_ROUND_BF16 2  /* round the (LN / GELU) value to bf16 before quantising                  */
 #define KF_Q_RECIP_DIV 4   /* amax/448, amax/6 as multiply by the fp32 reciprocal (torch-on-CUDA rule) */
+#define KF_Q_FAST_NV4 64   /* QUANT epilogue to nv4 only: block scale and element division through approximate
+                              reciprocals instead of the IEEE divisions of the bit specification (opt-in; a code moves
+                              only where the exact quotient lies within an ulp of a rounding boundary) */
 
 /* GEMM epilogues */
 #define KF_EPI_PLAIN 0 /* C = act(acc*ts + bias)                      f32 | bf16 | f16 [M,N]         */
@@ -51,7 +54,7 @@ extern "C" {
 #define KF_EPI_ROPE 2  /* bias + RoPE on q,k + relayout               bf16 | f16 [3,B,Ntok,H,64]     */
 #define KF_EPI_QUANT 3 /* gelu(acc*ts + bias) quantised to out_fmt    codes [M,N] + blocked scales   */
 
-/* GEMM flags (share the flag word with KF_Q_ROUND_BF16 / KF_Q_RECIP_DIV, which act on the QUANT epilogue) */
+/* GEMM flags (share the flag word with KF_Q_ROUND_BF16 / KF_Q_RECIP_DIV / KF_Q_FAST_NV4, which act on the QUANT epilogue) */
 #define KF_G_GELU 8        /* PLAIN: apply gelu_erf after the bias */
 #define KF_G_ROUND_BF16 16 /* PLAIN: round the value to bf16 before storing (matters for an f32 output) */
 #define KF_G_PRE_ROUND_BF16 32 /* PLAIN: round acc*ts to bf16 BEFORE the bias is added (a bf16 GEMM followed by bias + GELU) */
@@ -118,6 +121,10 @@ typedef struct kf_gemm_params {
   /* PLAIN only: output row of GEMM row m is (m / group) * stride + offset + m % group; group 0 = identity.
    * Lets the patch-embed GEMM write straight into the token stream behind each image's cls / register rows. */
   int out_row_group, out_row_stride, out_row_offset;
+  /* QUANT only, optional (NULL = off): fp32 [M, N] that receives the values the epilogue quantised, i.e.
+   * gelu(acc*ts + bias) after the optional bf16 rounding.  For parity tests: the written codes and scales are the bit
+   * specification's quantisation of exactly these values (mirrors y_dbg of kf_ln_quant). */
+  float* y_dbg;
 } kf_gemm_params;
 
 /* Block-scaled GEMM on tcgen05 with a fused epilogue.
@@ -176,13 +183,6 @@ KF_API int kf_attn_fwd(int dtype, const void* qkv, void* O, int B, int N, int H,
  * The caller times the launch to obtain the FP8 / FP4 / bf16 instruction-rate ceiling of the part.
  * Counterpart: the mma.sync probe infer-opt/round10_lowp_probe/peak_extra.cu. */
 KF_API int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, double* flops_per_launch, void* stream);
-
-/* Shared-memory fill-rate probe: every SM streams `iters` stages of `stage_bytes` (a multiple of 1024, <= 65536) from the
- * `span` bytes at `src` into a three-stage shared-memory ring with bulk copies and consumes nothing; *bytes_per_launch
- * receives the bytes one launch moves.  With a span that fits L2 this is the L2 -> shared-memory rate that feeds a GEMM main
- * loop whose operands are re-read from L2 (the CTAs' walks over the span overlap, so a larger span is not an HBM figure).
- * The caller times the launch.  No reference counterpart. */
-KF_API int kf_fill_rate_probe(const void* src, long long span, int stage_bytes, int iters, double* bytes_per_launch, void* stream);
 
 /* The same attention forward with the quantisation of its output fused into the epilogue: the O row of every head is
  * rounded to the 16-bit input type and written as codes + blocked scales of the [B*N, H*64] operand the proj GEMM

@@ -12,10 +12,11 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "libkf_b200.so"
 HEADER = PKG.parent / "include" / "kf_b200.h"
+HEADERS = sorted((PKG.parent / "include").glob("*.h"))
 
 KF_FMT = {"mx8": 0, "nv4": 1, "mx4": 2, "bf16": 3}
 KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
-KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV = 1, 2, 4
+KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV, KF_Q_FAST_NV4 = 1, 2, 4, 64
 
 KF_EPI = {"plain": 0, "res": 1, "rope": 2, "quant": 3}
 KF_G_GELU, KF_G_ROUND_BF16, KF_G_PRE_ROUND_BF16 = 8, 16, 32
@@ -28,7 +29,7 @@ class GemmParams(C.Structure):
                 ("A", C.c_void_p), ("SFA", C.c_void_p), ("W", C.c_void_p), ("SFW", C.c_void_p), ("ts_a", C.c_void_p),
                 ("ts_w", C.c_void_p), ("bias", C.c_void_p), ("gamma", C.c_void_p), ("R", C.c_void_p), ("sin", C.c_void_p),
                 ("cos", C.c_void_p), ("C", C.c_void_p), ("Qo", C.c_void_p), ("SFo", C.c_void_p), ("tso", C.c_void_p),
-                ("out_row_group", C.c_int), ("out_row_stride", C.c_int), ("out_row_offset", C.c_int)]
+                ("out_row_group", C.c_int), ("out_row_stride", C.c_int), ("out_row_offset", C.c_int), ("y_dbg", C.c_void_p)]
 
 
 _lib = None
@@ -39,8 +40,8 @@ class KfError(RuntimeError):
 
 
 def declared_symbols() -> list[str]:
-    """every function name include/kf_b200.h declares."""
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    """every function name the headers under include/ declare."""
+    text = re.sub(r"/\*.*?\*/", "", "\n".join(h.read_text() for h in HEADERS), flags=re.S)
     return sorted(set(re.findall(r"\b(kf_[a-z0-9_]+)\s*\(", text)))
 
 

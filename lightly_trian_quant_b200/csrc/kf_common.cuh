@@ -291,29 +291,29 @@ __device__ __forceinline__ Nv4Block nv4_block(float amax, const Nv4Scale& sc, bo
 template <int NL>
 __device__ __forceinline__ void nv4_codes(const float (&v)[NL], const Nv4Block& b, uint32_t* out /* NL/8 words */) {
   const float dd = b.dd, rcp = b.rcp;
-  float q[NL];
-  if (b.mode == 0) {
+  constexpr int G = NL < 8 ? NL : 8;            // quotients are converted group by group so that few of them are live at once
 #pragma unroll
-    for (int j = 0; j < NL; ++j) q[j] = 0.f;
-  } else if (b.mode == 1) {
-    const float2 r2 = splat2(rcp), nd2 = splat2(-dd);
+  for (int i = 0; i < NL; i += G) {
+    float q[G];
+    if (b.mode == 1) {
+      const float2 r2 = splat2(rcp), nd2 = splat2(-dd);
 #pragma unroll
-    for (int j = 0; j < NL; j += 2) {         // div_by_rcp on packed pairs
-      const float2 x = make_float2(v[j], v[j + 1]);
-      const float2 q0 = mul2(x, r2);
-      const float2 q1 = fma2(fma2(nd2, q0, x), r2, q0);
-      q[j] = q1.x;
-      q[j + 1] = q1.y;
+      for (int j = 0; j < G; j += 2) {          // div_by_rcp on packed pairs
+        const float2 x = make_float2(v[i + j], v[i + j + 1]);
+        const float2 q0 = mul2(x, r2);
+        const float2 q1 = fma2(fma2(nd2, q0, x), r2, q0);
+        q[j] = q1.x;
+        q[j + 1] = q1.y;
+      }
+    } else if (b.mode == 0) {
+#pragma unroll
+      for (int j = 0; j < G; ++j) q[j] = 0.f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < G; ++j) q[j] = __fdiv_rn(v[i + j], dd);
     }
-  } else {
-#pragma unroll
-    for (int j = 0; j < NL; ++j) q[j] = __fdiv_rn(v[j], dd);
-  }
-  if constexpr (NL == 4) {
-    out[0] = cvt_e2m1x4(q);                     // 16 bits
-  } else {
-#pragma unroll
-    for (int i = 0; i < NL; i += 8) out[i / 8] = cvt_e2m1x8(q + i);
+    if constexpr (NL == 4) out[0] = cvt_e2m1x4(q);   // 16 bits
+    else out[i / 8] = cvt_e2m1x8(q);
   }
 }
 template <int NL>

@@ -201,7 +201,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
-    const float tso = (EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f;   // once per CTA: every global load here is an L2 round trip
+    const Nv4Scale sco = nv4_scale((EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f);   // once per CTA: every global load here is an L2 round trip
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
@@ -222,7 +222,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
       if (n0 >= g.N) continue;                                   // column group past N in the last column tile
 
-      epilogue_math<EPI>(g, r0, r1, ts, tso, rbase, n0, stg, lane, pre);
+      epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, stg, lane, pre);
     }
   }
 
@@ -359,6 +359,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
     KF_REQUIRE(p->out_fmt == KF_FMT_MX8 || p->out_fmt == KF_FMT_NV4 || p->out_fmt == KF_FMT_MX4, "kf_gemm_bs: bad quantise-out format %d", p->out_fmt);
     KF_REQUIRE(p->Qo && p->SFo && al16(p->Qo) && al16(p->SFo), "kf_gemm_bs: QUANT needs 16-byte aligned Qo and SFo");
     KF_REQUIRE(p->out_fmt != KF_FMT_NV4 || p->tso, "kf_gemm_bs: nv4 quantise-out needs the per-tensor scale tso");
+    KF_REQUIRE(!p->y_dbg || al16(p->y_dbg), "kf_gemm_bs: y_dbg must be 16-byte aligned");
   }
   const uint64_t kbytes = fmt == KF_FMT_MX8 ? (uint64_t)p->K : (fmt == KF_FMT_BF16 ? 2ull * p->K : (uint64_t)p->K / 2);
   CUtensorMap tmA, tmW;
@@ -378,6 +379,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = (p->N + BN - 1) / BN; g.k_tiles = (int)(kbytes / BKB);
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
   g.row_group = p->out_row_group; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
+  g.y_dbg = epi == KF_EPI_QUANT ? p->y_dbg : nullptr;
   g.err = dev_error_ptr();
   KF_REQUIRE(g.err != nullptr, "kf_gemm_bs: device error word unavailable");
   int sms = 0;

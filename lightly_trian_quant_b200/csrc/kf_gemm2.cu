@@ -212,7 +212,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     float ts = 1.f;
     if (g.ts_a) ts *= __ldg(g.ts_a);
     if (g.ts_w) ts *= __ldg(g.ts_w);
-    const float tso = (EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f;   // once per CTA: every global load here is an L2 round trip
+    const Nv4Scale sco = nv4_scale((EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f);   // once per CTA: every global load here is an L2 round trip
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
     const uint32_t leader_tempty = map_to_rank(tempty, 0);
     uint32_t lt = 0;
@@ -233,7 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(leader_tempty);          // the accumulator is in registers: hand TMEM back (to the leader's MMA warp)
       if (n0 >= g.N || rbase >= g.m_tiles * 128) continue;        // column group past N, or the follower's row block past the last one
-      epilogue_math<EPI>(g, r0, r1, ts, tso, rbase, n0, stg, lane, pre);
+      epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, stg, lane, pre);
     }
   }
 

@@ -44,6 +44,7 @@ struct GemmArgs {
   int out_dtype, flags, out_fmt;
   int m_tiles, n_tiles, k_tiles, nkb4;
   int row_group, row_stride, row_offset;   // PLAIN: output row = (m / group) * stride + offset + m % group (group 0: identity)
+  float* y_dbg;                            // QUANT: optional export of the values that were quantised (fp32 [M, N])
   unsigned int* err;
 };
 
@@ -108,50 +109,64 @@ __device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
 
 // QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
 // or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
-__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, float tso /* per-tensor scale of an nv4 output */, int m, int n0,
-                                            const float* bsm /* the chunk's 32 bias values in shared memory */) {
-  const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
-  const bool ok = m < g.M;
-  float v[32];
+// The codes and scale bytes are the bit specification's quantisation (IEEE divisions, as in the row quantiser) of the
+// values gelu(acc*ts + bias), optionally rounded to bf16, which y_dbg exports for the parity tests.
+
+// values 16*h .. 16*h+15 of the chunk: bias + GELU (+ bf16 rounding), exported when asked; returns their maximum magnitude
+__device__ __forceinline__ float quant_values16(const GemmArgs& g, const uint32_t (&r)[32], int h, float ts, const float* bsm, float* dbg, float (&v)[16]) {
+  const float2 ts2 = splat2(ts);
 #pragma unroll
-  for (int q4 = 0; q4 < 8; ++q4) {
-    const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + 4 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float2 ts2 = splat2(ts);
-    const float2 a = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1])), ts2, make_float2(bb.x, bb.y)));
-    const float2 b = gelu_erf2(fma2(make_float2(__uint_as_float(r[4 * q4 + 2]), __uint_as_float(r[4 * q4 + 3])), ts2, make_float2(bb.z, bb.w)));
+  for (int q4 = 0; q4 < 4; ++q4) {
+    const int k = 16 * h + 4 * q4;
+    const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float2 a = gelu_erf2(fma2(make_float2(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), ts2, make_float2(bb.x, bb.y)));
+    float2 b = gelu_erf2(fma2(make_float2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3])), ts2, make_float2(bb.z, bb.w)));
+    if (g.flags & KF_Q_ROUND_BF16) {
+      a = bf16_round2(a);
+      b = bf16_round2(b);
+    }
     v[4 * q4] = a.x;
     v[4 * q4 + 1] = a.y;
     v[4 * q4 + 2] = b.x;
     v[4 * q4 + 3] = b.y;
+    if (dbg) *reinterpret_cast<float4*>(dbg + k) = make_float4(a.x, a.y, b.x, b.y);
   }
-  if (g.flags & KF_Q_ROUND_BF16) {
+  float am = 0.f;
 #pragma unroll
-    for (int k = 0; k < 32; k += 2) {
-      const float2 t = bf16_round2(make_float2(v[k], v[k + 1]));
-      v[k] = t.x;
-      v[k + 1] = t.y;
-    }
-  }
-  float am0 = 0.f, am1 = 0.f;
-#pragma unroll
-  for (int k = 0; k < 16; k += 2) {
-    am0 = max3(am0, fabsf(v[k]), fabsf(v[k + 1]));
-    am1 = max3(am1, fabsf(v[16 + k]), fabsf(v[17 + k]));
-  }
-  const float(&va)[16] = *reinterpret_cast<const float(*)[16]>(&v[0]);
-  const float(&vb)[16] = *reinterpret_cast<const float(*)[16]>(&v[16]);
+  for (int k = 0; k < 16; k += 2) am = max3(am, fabsf(v[k]), fabsf(v[k + 1]));
+  return am;
+}
+
+__device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, const Nv4Scale& sco /* per-tensor scale of an nv4 output */, int m, int n0,
+                                            const float* bsm /* the chunk's 32 bias values in shared memory */) {
+  const bool div_true = !(g.flags & KF_Q_RECIP_DIV);
+  const bool ok = m < g.M;
+  float* dbg = (g.y_dbg != nullptr && ok) ? g.y_dbg + (size_t)m * g.N + n0 : nullptr;
   int by0, by1;
   if (g.out_fmt == KF_FMT_NV4) {
+    // one 16-value block at a time: the exact division keeps a quotient per value live
     uint32_t o[4];
-    const float rcp_tso = __frcp_rn(tso);
-    quant_nv4_fast<16>(va, am0, tso, rcp_tso, o, by0);
-    quant_nv4_fast<16>(vb, am1, tso, rcp_tso, o + 2, by1);
+    {
+      float v[16];
+      const float am = quant_values16(g, r, 0, ts, bsm, dbg, v);
+      if (g.flags & KF_Q_FAST_NV4) quant_nv4_fast<16>(v, am, sco.ts, sco.rcp_ts, o, by0);
+      else quant_nv4<16>(v, am, sco, div_true, o, by0);
+    }
+    {
+      float v[16];
+      const float am = quant_values16(g, r, 1, ts, bsm, dbg, v);
+      if (g.flags & KF_Q_FAST_NV4) quant_nv4_fast<16>(v, am, sco.ts, sco.rcp_ts, o + 2, by1);
+      else quant_nv4<16>(v, am, sco, div_true, o + 2, by1);
+    }
     if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
     // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
     *reinterpret_cast<uint16_t*>(g.SFo + sf_offset(m, n0 >> 4, g.N >> 6)) = ok ? (uint16_t)(by0 | (by1 << 8)) : (uint16_t)0;
-  } else if (g.out_fmt == KF_FMT_MX8) {
+    return;
+  }
+  float va[16], vb[16];
+  const float am = fmaxf(quant_values16(g, r, 0, ts, bsm, dbg, va), quant_values16(g, r, 1, ts, bsm, dbg, vb));
+  if (g.out_fmt == KF_FMT_MX8) {
     uint32_t o[8];
-    const float am = fmaxf(am0, am1);
     quant_mx8<16>(va, am, div_true, o, by0);
     quant_mx8<16>(vb, am, div_true, o + 4, by0);
     if (ok) {
@@ -162,7 +177,6 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
     g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
   } else {
     uint32_t o[4];
-    const float am = fmaxf(am0, am1);
     quant_mx4<16>(va, am, div_true, o, by0);
     quant_mx4<16>(vb, am, div_true, o + 2, by0);
     if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -238,7 +252,7 @@ __device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int n0, int
 }
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, float tso, int rbase, int n0, float* stg,
+__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0, float* stg,
                                               int lane, const EpiPre& pre) {
   const int c4 = 4 * (lane & 7);                // coalesced layout: this lane's 4 columns inside a 32-column chunk
   const int rsub = lane >> 3;                   // coalesced layout: row 4*i + rsub in pass i
@@ -334,8 +348,8 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     plain_chunk(g, r0, ts, dst_row, n0, stg);
     plain_chunk(g, r1, ts, dst_row, n0 + 32, stg + 32);
   } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-    quant_chunk(g, r0, ts, tso, rbase + lane, n0, stg);
-    quant_chunk(g, r1, ts, tso, rbase + lane, n0 + 32, stg + 32);
+    quant_chunk(g, r0, ts, sco, rbase + lane, n0, stg);
+    quant_chunk(g, r1, ts, sco, rbase + lane, n0 + 32, stg + 32);
   }
 }
 

@@ -5,6 +5,7 @@
 // N = 64 shows what the attention products (64 keys or 64 head columns per MMA) can reach: 1.30 of 2.2 PFLOP/s for bf16.
 // Same idea as the reference's register-resident mma.sync probe (infer-opt/round10_lowp_probe/peak_extra.cu).
 #include "kf_sm100.cuh"
+#include "../../include/kf_b200_dev.h"
 
 namespace kf {
 

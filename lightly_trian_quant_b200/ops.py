@@ -210,7 +210,8 @@ MXW = QWeight
 
 
 def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
-          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block", pre_round=False):
+          out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block", pre_round=False,
+          fast_nv4=False, y_dbg=None):
     p = GemmParams()
     if isinstance(a, ActBuf):
         if a.fmt != W.fmt or a.K != W.K:
@@ -227,10 +228,11 @@ def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin
     p.W, p.SFW, p.ts_w = W.q.data_ptr(), _ptr(W.sf), _ptr(W.ts)
     p.out_dtype = _DT[out_dtype]
     p.flags = (KF_G_GELU if gelu else 0) | (KF_Q_ROUND_BF16 if round_bf16 else 0) | (KF_Q_RECIP_DIV if recip_div else 0) \
-        | (_lib.KF_G_PRE_ROUND_BF16 if pre_round else 0)
+        | (_lib.KF_G_PRE_ROUND_BF16 if pre_round else 0) | (_lib.KF_Q_FAST_NV4 if fast_nv4 else 0)
     p.Ntok, p.prefix, p.H = Ntok, prefix, H
-    _need_cuda(bias, gamma, R, C, sin, cos)
+    _need_cuda(bias, gamma, R, C, sin, cos, y_dbg)
     p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
+    p.y_dbg = _ptr(y_dbg)
     if out is not None:
         p.out_fmt, p.Qo, p.SFo, p.tso = KF_FMT[out.fmt], out.q.data_ptr(), out.sf.data_ptr(), _ptr(out.ts)
     _run(f"gemm_{tag}_{W.fmt}", lambda: _lib.lib().kf_gemm_bs(p, _stream()))
@@ -281,13 +283,17 @@ def qkv_rope(a, W: QWeight, bias, sin, cos, Ntok: int, prefix: int, H: int, out_
     return out
 
 
-def gemm_gelu_q(a, W: QWeight, bias, out: ActBuf, *, round_bf16: bool = False, recip_div: bool = False) -> ActBuf:
-    """out = quantise(gelu(a @ W^T (* ts) + bias)) in out.fmt: fc1 writes fc2's operand and blocked scales directly."""
+def gemm_gelu_q(a, W: QWeight, bias, out: ActBuf, *, round_bf16: bool = False, recip_div: bool = False, fast_nv4: bool = False,
+                y_dbg: Optional[torch.Tensor] = None) -> ActBuf:
+    """out = quantise(gelu(a @ W^T (* ts) + bias)) in out.fmt: fc1 writes fc2's operand and blocked scales directly.
+    The quantisation follows the bit specification (IEEE divisions); fast_nv4=True selects approximate reciprocals for an
+    nv4 output.  y_dbg (fp32 [M, N], optional) receives the values that were quantised."""
     M = a.M if isinstance(a, ActBuf) else a.shape[0]
     _f32c(bias, W.N, "bias")
     if (out.M, out.K) != (M, W.N):
         raise KfError(f"gemm_gelu_q: out must be [{M}, {W.N}], got [{out.M}, {out.K}]")
-    _gemm(a, W, "quant", bias=bias, out=out, round_bf16=round_bf16, recip_div=recip_div)
+    _f32c(y_dbg, M * W.N, "y_dbg")
+    _gemm(a, W, "quant", bias=bias, out=out, round_bf16=round_bf16, recip_div=recip_div, fast_nv4=fast_nv4, y_dbg=y_dbg)
     return out
 
 

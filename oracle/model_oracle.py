@@ -49,8 +49,9 @@ class EmuModel:
     {(layer, site) -> float32 [1]} of static NVFP4 activation scales ("ln1", "o", "ln2", "g"; ("head", j) for the
     ConvTranspose inputs); missing entries are measured on the first call with headroom 2."""
 
-    def __init__(self, model, fmt: str, head_fmt=None, ts=None, round_bf16: bool = True):
+    def __init__(self, model, fmt: str, head_fmt=None, ts=None, round_bf16: bool = True, attn_dtype=BF):
         self.m, self.fmt, self.head_fmt = model, fmt, head_fmt or fmt
+        self.attn_dtype = attn_dtype                  # 16-bit type of q, k, v and of the attention output (bf16 | f16)
         self.ts = dict(ts or {})
         self.round = round_bf16
         self._w = {}
@@ -90,9 +91,10 @@ class EmuModel:
             rot = torch.cat([-r[..., 32:], r[..., :32]], dim=-1)
             return torch.cat((t[:, :, :prefix], r * cos + rot * sin), dim=2)
 
-        q, k, v = _bf(rope(q)), _bf(rope(k)), _bf(v)
+        r16 = lambda t: t.to(self.attn_dtype).float()  # noqa: E731
+        q, k, v = r16(rope(q)), r16(rope(k)), r16(v)
         s = (q @ k.transpose(-1, -2)) * 0.125
-        o = _bf((torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(B * N, d))
+        o = r16((torch.softmax(s, dim=-1) @ v).transpose(1, 2).reshape(B * N, d))
         y = self._lin((i, "proj"), "o", o, blk.attn.proj, self.fmt, _bf(blk.attn.proj.bias.detach()))
         x = x + (y * blk.ls1.gamma).reshape(B, N, d)
         h = rp(F.layer_norm(x, (d,), blk.norm2.weight, blk.norm2.bias, blk.norm2.eps)).reshape(B * N, d)

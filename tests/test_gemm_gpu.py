@@ -126,50 +126,80 @@ def test_gemm_qkv_rope(fmt, out_dtype):
     assert out.shape == (3, B, Ntok, H, 64)
     y = go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)
     ref = go.epi_rope(y, sin.numpy(), cos.numpy(), Ntok, prefix, H)
-    tol = 2.5e-3 if out_dtype == torch.bfloat16 else 4e-4
-    assert go.rel_fro(out.float().cpu().numpy(), ref) < tol
+    tol = 2e-3 if out_dtype == torch.bfloat16 else 4e-4     # the stated 16-bit bound; bf16 output rounding alone is ~1.7e-3
+    err = go.rel_fro(out.float().cpu().numpy(), ref)
+    print(f"qkv+RoPE {fmt} {out_dtype}: rel. Frobenius {err:.3e}")
+    assert err < tol
     # prefix rows and v are not rotated
     ref_v = y.reshape(B, Ntok, 3, H, 64)[:, :, 2]
     assert go.rel_fro(out[2].float().cpu().numpy(), ref_v) < tol
 
 
-@pytest.mark.parametrize("fmt", FMTS)
-@pytest.mark.parametrize("round_bf16", [False, True])
-def test_gemm_fc1_gelu_quant_out(fmt, round_bf16):
-    """fc1 with bias + GELU + quantise-out: the written operand must be the oracle quantisation of the kernel's own
-    pre-quantisation values up to the ulp noise of accumulation order; compared through the dequantised operand."""
+def _fc1_case(fmt, round_bf16, M=300, N=512, K=1024, **kw):
+    """runs the fc1 epilogue (bias + GELU + quantise-out) with the debug export; returns everything the gates need."""
     ops = _ops()
-    M, N, K = 300, 512, 1024
     x, w = _mk_x(M, K, 9), _mk_w(N, K, 10, std=0.03)
     g = torch.Generator().manual_seed(11)
     bias = torch.randn(N, generator=g) * 0.1
     a, W, ad, wd = _quant_pair(x, w, fmt)
     pre = go.gelu_erf(go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)).astype(np.float32)
-    if round_bf16:
-        pre = qo.bf16_round(pre)
     out = ops.ActBuf(M, N, fmt, device="cuda")
     out.q.fill_(0xAA)
     out.sf.fill_(0xAA)
     tso = None
     if fmt == "nv4":
-        tso = qo.nv4_ts(pre) * np.float32(2.0)
+        tso = qo.nv4_ts(qo.bf16_round(pre) if round_bf16 else pre) * np.float32(2.0)
         out.ts.copy_(torch.from_numpy(tso))
-    ops.gemm_gelu_q(a, W, bias.cuda(), out, round_bf16=round_bf16)
+    y = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_gelu_q(a, W, bias.cuda(), out, round_bf16=round_bf16, y_dbg=y, **kw)
     ops.check_device_error()
-    eq, es, _ = qo.quantize(pre, fmt, tso)
+    return pre, y.cpu().numpy(), out.q.cpu().numpy(), out.sf.cpu().numpy(), tso
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("round_bf16", [False, True])
+def test_gemm_fc1_gelu_quant_out(fmt, round_bf16):
+    """fc1 with bias + GELU + quantise-out.  Byte gate: the written codes AND scale bytes are exactly the oracle
+    quantisation of the values the epilogue quantised (its debug export), for every format, with and without the bf16
+    rounding point.  Value gate: those exported values are gelu(acc + bias) of the float64 dequantised product."""
+    M, N = 300, 512
+    pre, y, q, sf, tso = _fc1_case(fmt, round_bf16)
+    assert np.isfinite(y).all()
+    eq, es, _ = qo.quantize(y, fmt, tso)
     esb = qo.to_blocked(es).reshape(-1)
-    q = out.q.cpu().numpy()
-    sf = out.sf.cpu().numpy()
-    assert (sf == esb).mean() > 0.995
-    assert (q == eq).mean() > (0.97 if fmt == "mx8" else 0.985)
-    got = go.dequant_operand(q, sf, tso, fmt, M, N)
-    exp = qo.dequant(eq, es, tso, fmt)
-    qerr = go.rel_fro(exp, pre)                       # the quantisation error itself
-    assert go.rel_fro(got, pre) < 1.05 * qerr + 1e-6  # the kernel's operand is as good a quantisation of the same values
+    code_eq, sf_eq = float((q == eq).mean()), float((sf == esb).mean())
+    print(f"fc1 quantise-out {fmt} round_bf16={round_bf16}: codes identical {code_eq:.6%}, scale bytes identical {sf_eq:.6%}")
+    assert np.array_equal(sf, esb), f"scale bytes differ from the oracle on {int((sf != esb).sum())} positions"
+    assert np.array_equal(q, eq), f"codes differ from the oracle on {int((q != eq).sum())} positions"
+    # the exported values against the float64 reference: fp32 accumulation + the epilogue's GELU (|error| <= 6.4e-7)
+    if round_bf16:
+        assert np.array_equal(qo.bf16_round(y), y)
+        flips = float((y != qo.bf16_round(pre)).mean())
+        print(f"  bf16 values off by one ulp from the float64 reference: {flips:.4%}")
+        assert flips < 2e-3 and go.rel_fro(y, pre) < 3e-3
+    else:
+        assert go.rel_fro(y, pre) < 2e-5 and np.abs(y - pre).max() < 2e-5
     # padded scale rows are zero
     blocked = sf.reshape(-(-M // 128), -1, 32, 4, 4)
     full = qo.from_blocked(blocked, -(-M // 128) * 128, N // qo.VEC[fmt])
     assert not full[M:].any()
+
+
+def test_gemm_fc1_quant_out_fast_nv4_agreement():
+    """the opt-in approximate-reciprocal nv4 path: agreement with the oracle on the exported values is measured, printed
+    and gated at >= 99.9 % of codes per 64-column group (a localised error cannot hide in an average) and 100 % of the
+    scale bytes up to the one-in-a-million double-rounding of amax * (1/6) * (1/ts)."""
+    M, N = 300, 512
+    _, y, q, sf, tso = _fc1_case("nv4", True, fast_nv4=True)
+    eq, es, _ = qo.quantize(y, "nv4", tso)
+    esb = qo.to_blocked(es).reshape(-1)
+    # compare nibbles, grouped by 64 output columns (32 code bytes)
+    nib = np.stack([(q & 15) == (eq & 15), (q >> 4) == (eq >> 4)], axis=-1).reshape(M, N // 64, 64)
+    per_group = nib.mean(axis=(0, 2))
+    sf_eq = float((sf == esb).mean())
+    print(f"fast nv4 quantise-out: codes identical {nib.mean():.6%} (worst 64-column group {per_group.min():.6%}), scale bytes identical {sf_eq:.6%}")
+    assert per_group.min() >= 0.999
+    assert sf_eq >= 0.9995
 
 
 @pytest.mark.parametrize("fmt", ["nv4", "mx8"])

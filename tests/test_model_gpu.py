@@ -196,6 +196,37 @@ def test_block_teacher_forced(fmt):
     assert go.rel_fro(xg.cpu().numpy(), ref.numpy()) < 1e-2
 
 
+@pytest.mark.parametrize("fmt", ["mx8", "nv4", "mx4"])
+@pytest.mark.parametrize("ntok,prefix", [(1605, 5), (1805, 205)])
+def test_block_teacher_forced_full_width(fmt, ntok, prefix):
+    """The same gate at the ViT-L block's real size: d = 1024, 16 heads, MLP 4096, 1605 tokens (prefix 5) and 1805 tokens
+    (200 queries + 5), two images, stress-style weights (LayerScale ~ U(0.5, 1.5), LN affine and biases random), an outlier
+    channel in the stream.  The block's update must agree with the emulated block within 1 % rel. Frobenius; the measured
+    value and its two halves (attention branch, MLP branch) are printed."""
+    modeldef, ops, stack = _mods()
+    cfg = modeldef.EoMTConfig(dim=1024, depth=1, heads=16, ffn=4096, num_queries=200, num_joint_blocks=1)
+    model = modeldef.build_model(cfg, 3, "stress", "cpu")
+    blk = model.backbone.blocks[0]
+    g = torch.Generator().manual_seed(17)
+    B, gh = 2, 40
+    x = torch.randn(B, ntok, cfg.dim, generator=g) * 2
+    x[:, :, 7] *= 20
+    x[:, :5] *= 4                                            # larger prefix rows, as cls / register tokens are
+    sin, cos = model.backbone.rope_embed(H=gh, W=gh)
+    L = stack.Layer(copy_to_cuda(blk), fmt)
+    xg = x.cuda().clone()
+    stack.block_fwd(xg, L, sin.cuda().contiguous(), cos.cuda().contiguous(), prefix, cfg.heads, stack.Calib(), round_bf16=True, attn_dtype=BF)
+    ops.check_device_error()
+    ts = {(0, s): getattr(L, "ts_" + s).cpu().numpy() for s in ("ln1", "o", "ln2", "g") if getattr(L, "ts_" + s) is not None}
+    ref = mo.EmuModel(model, fmt, ts=ts).block(0, blk, x, sin, cos, prefix)
+    upd, upd_ref = (xg.cpu() - x).numpy(), (ref - x).numpy()
+    err = go.rel_fro(upd, upd_ref)
+    err_pre, err_patch = go.rel_fro(upd[:, :prefix], upd_ref[:, :prefix]), go.rel_fro(upd[:, prefix:], upd_ref[:, prefix:])
+    print(f"full-width block {fmt} Ntok={ntok}: update rel. Frobenius {err:.3e} (prefix rows {err_pre:.3e}, patch rows {err_patch:.3e}), "
+          f"stream {go.rel_fro(xg.cpu().numpy(), ref.numpy()):.3e}")
+    assert err < 1e-2, err
+
+
 def copy_to_cuda(module):
     import copy
 
