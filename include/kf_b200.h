@@ -58,6 +58,9 @@ extern "C" {
 #define KF_G_GELU 8        /* PLAIN: apply gelu_erf after the bias */
 #define KF_G_ROUND_BF16 16 /* PLAIN: round the value to bf16 before storing (matters for an f32 output) */
 #define KF_G_PRE_ROUND_BF16 32 /* PLAIN: round acc*ts to bf16 BEFORE the bias is added (a bf16 GEMM followed by bias + GELU) */
+#define KF_G_ROPE_HALF 128 /* ROPE: the caller guarantees that columns 32..63 of sin / cos repeat columns 0..31 (the axial
+                              tables of DINOv3 are the angle vector concatenated with itself); lets the kernel keep the table
+                              rows of a tile in shared memory.  Without the flag both halves are read as given. */
 
 /* Library version and the SM architecture the kernels were built for ("sm_100a"). */
 KF_API const char* kf_version(void);

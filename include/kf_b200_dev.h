@@ -16,6 +16,12 @@ extern "C" {
  * The caller times the launch.  No reference counterpart. */
 KF_API int kf_fill_rate_probe(const void* src, long long span, int stage_bytes, int iters, double* bytes_per_launch, void* stream);
 
+/* Self-test of the three-instruction correctly rounded reciprocal the NVFP4 quantisers use for their block divisors:
+ * sweeps all 2^23 - 1 significands (all ones excluded: outside the routine's contract) of the binade 2^exponent, both
+ * signs, against __frcp_rn and adds the number of differing results to *mismatches (a zero-initialised device counter).
+ * No reference counterpart. */
+KF_API int kf_selftest_rcp(int exponent, unsigned int* mismatches, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

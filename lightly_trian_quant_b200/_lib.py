@@ -19,7 +19,7 @@ KF_DT = {"f32": 0, "bf16": 1, "f16": 2}
 KF_Q_GELU, KF_Q_ROUND_BF16, KF_Q_RECIP_DIV, KF_Q_FAST_NV4 = 1, 2, 4, 64
 
 KF_EPI = {"plain": 0, "res": 1, "rope": 2, "quant": 3}
-KF_G_GELU, KF_G_ROUND_BF16, KF_G_PRE_ROUND_BF16 = 8, 16, 32
+KF_G_GELU, KF_G_ROUND_BF16, KF_G_PRE_ROUND_BF16, KF_G_ROPE_HALF = 8, 16, 32, 128
 
 
 class GemmParams(C.Structure):
@@ -65,6 +65,7 @@ def lib() -> C.CDLL:
             "kf_attn_fwd": [i32, vp, vp, i32, i32, i32, f32, vp],
             "kf_tensor_peak_probe": [i32, i32, i32, i32, C.POINTER(C.c_double), vp],
             "kf_fill_rate_probe": [vp, C.c_int64, i32, i32, C.POINTER(C.c_double), vp],
+            "kf_selftest_rcp": [i32, vp, vp],
             "kf_attn_fwd_quant": [i32, vp, i32, i32, i32, f32, i32, vp, vp, vp, i32, vp],
             "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp],
             "kf_im2col_patch16": [vp, vp, i32, i32, vp],

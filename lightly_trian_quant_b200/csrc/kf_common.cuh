@@ -327,6 +327,64 @@ __device__ __forceinline__ void quant_nv4(const float (&v)[NL], float amax, floa
   quant_nv4<NL>(v, amax, nv4_scale(ts), div_true, out, sf_byte);
 }
 
+// Correctly rounded 1/d from the approximate reciprocal and one Newton step (Markstein): r0 = rcp.approx(d) is within one
+// ulp of 1/d, e = RN(1 - d*r0) is exact enough and RN(r0 + r0*e) is RN(1/d) unless the significand of d is all ones;
+// valid for normal d whose reciprocal is normal (callers guarantee 1e-18 < d < 1e18).  Three instructions instead of the
+// ten of __frcp_rn; kf_selftest_rcp sweeps every significand against __frcp_rn.
+__device__ __forceinline__ float2 rcp_rn_pair(float2 d) {
+  float2 r0;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0.y) : "f"(d.y));
+  const float2 e = fma2(make_float2(-d.x, -d.y), r0, splat2(1.0f));
+  return fma2(r0, e, r0);
+}
+__device__ __forceinline__ bool mant_all_ones(float d) { return (__float_as_uint(d) & 0x7FFFFFu) == 0x7FFFFFu; }
+
+// Two NVFP4 blocks of 16 values at once (a thread of a GEMM epilogue owns both): the block scalars (amax/6, /ts, the e4m3
+// scale, the element divisor and its reciprocal) are worked out on packed pairs, one conversion instruction serves both
+// scale bytes.  Bit-identical to quant_nv4 on each block: inside the range where every step of the reciprocal route is an
+// exact IEEE division (1e-15 < amax, ts < 1e15, hence no intermediate under- or overflow; divisor significands not all
+// ones; non-zero scale) the packed route is taken, anything else goes through quant_nv4 itself.
+__device__ __forceinline__ void quant_nv4_pair16(const float (&v0)[16], float am0, const float (&v1)[16], float am1, const Nv4Scale& sc, bool div_true,
+                                                 uint32_t* out /* 4 words */, int& by0, int& by1) {
+  const float lo = fminf(am0, am1), hi = fmaxf(am0, am1);
+  if (sc.safe && sc.ts > 1e-15f && sc.ts < 1e15f && lo > 1e-15f && hi < 1e15f) {
+    const float2 am = make_float2(am0, am1);
+    float2 a6;
+    if (div_true) {                              // amax / 6 through RN(1/6) = 0x3E2AAAAB with one correction
+      const float2 r6 = splat2(0.16666667163372040f);
+      const float2 q = mul2(am, r6);
+      a6 = fma2(fma2(splat2(-6.0f), q, am), r6, q);
+    } else {
+      a6 = mul2(am, splat2(1.0f / 6.0f));
+    }
+    const float2 rts = splat2(sc.rcp_ts);
+    const float2 q = mul2(a6, rts);
+    const float2 t = fma2(fma2(splat2(-sc.ts), q, a6), rts, q);
+    const uint32_t sb2 = cvt_e4m3x2(fminf(t.x, 448.f), fminf(t.y, 448.f));   // byte 0: block 0, byte 1: block 1
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)sb2));
+    const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    const float2 dd = mul2(sf, splat2(sc.ts));
+    if (fminf(dd.x, dd.y) > 0.f && !mant_all_ones(dd.x) && !mant_all_ones(dd.y)) {
+      const float2 rcp = rcp_rn_pair(dd);
+      Nv4Block b;
+      b.mode = 1;
+      b.dd = dd.x;
+      b.rcp = rcp.x;
+      nv4_codes<16>(v0, b, out);
+      b.dd = dd.y;
+      b.rcp = rcp.y;
+      nv4_codes<16>(v1, b, out + 2);
+      by0 = (int)(sb2 & 0xFF);
+      by1 = (int)((sb2 >> 8) & 0xFF);
+      return;
+    }
+  }
+  quant_nv4<16>(v0, am0, sc, div_true, out, by0);
+  quant_nv4<16>(v1, am1, sc, div_true, out + 2, by1);
+}
+
 // NVFP4 block quantiser for epilogues whose input is a fresh accumulator (no bit-exact counterpart exists: the
 // accumulation order already differs from any other implementation in the last bits): the divisions become
 // multiplications by reciprocals (rcp_ts = 1/ts is passed in; the element divisor uses rcp.approx), which changes a code

@@ -8,9 +8,12 @@
 //              operands in the ~68 clk it executes, which alone saturates the 128 B/clk of the shared-memory array,
 //              and the TMA writes of the next stages need the same array (measured: main loop at half the instruction
 //              rate).  At 128 x 256 an MMA reads 12 KB per ~136 clk.
-//   pipeline   warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy), warp 1 = MMA issuer
-//              (4 MMAs per stage), warp 18 = scale-factor copier (tcgen05.cp atoms smem -> TMEM; the copies take
-//              tensor-pipe time but overlap the MMAs when another warp issues them), warps 2..17 = epilogue.
+//   pipeline   20 warps.  Warp group 0: warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy),
+//              warp 1 = MMA issuer (4 MMAs per stage), warp 2 = scale-factor copier (tcgen05.cp atoms smem -> TMEM; the
+//              copies take tensor-pipe time but overlap the MMAs when another warp issues them), warp 3 idle.  Warp groups
+//              1..4 = 16 epilogue warps.  Registers are re-balanced between the roles (setmaxnreg): the three single-thread
+//              roles give theirs up and every epilogue thread holds its 64 accumulator values plus loads in flight
+//              without spilling.
 //              One 256-column accumulator in TMEM: each epilogue warp takes (32-row TMEM quarter, 64 columns) into
 //              registers and hands TMEM back at once, so the next tile's main loop runs under the epilogue math;
 //              persistent CTAs, one per SM, static round-robin over tiles
@@ -18,9 +21,8 @@
 //              RES    out = R + gamma * (acc*ts + bias)              -> f32 [M,N]         (proj, fc2)
 //              ROPE   bias + rotary embedding of q,k + relayout      -> bf16 | f16 [3,B,Ntok,H,64]   (qkv)
 //              QUANT  gelu(acc*ts + bias) quantised again            -> codes [M,N] + blocked scales (fc1 -> fc2)
-//              PLAIN and QUANT work in the TMEM row layout (a thread owns 64 consecutive columns of one row);
-//              RES and ROPE restage through warp-private swizzled shared memory so that their fp32 / table traffic
-//              is coalesced.
+//              all four work in the TMEM row layout (a thread owns 64 consecutive columns of one row) and touch global
+//              memory in whole 32-byte sectors (kf_gemm_epi.cuh)
 //
 // Replaces (reference checkout paths): infer-opt/round13_mxfp8_full/impl/mgx_core.cu:118-444 (MXFP8, mma.sync) and
 // infer-opt/round14_fp4_full/impl/fp4g_core.cu:153-470 (NVFP4 / MXFP4, mma.sync); epilogue math per
@@ -31,19 +33,25 @@
 
 namespace kf {
 
+constexpr int STAGES = 3;
+template <int EPI>
+constexpr size_t gemm_smem() {                         // operand ring + scale atoms + bias slices (+ the rotary-table slabs) + barriers
+  return (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * SLICE_FLOATS * 4 + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
+}
+
 // ------------------------------------------------------------------------------------------------ the kernel
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
-  constexpr int STAGES = Pipe<EPI>::STAGES;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
-  uint8_t* stg_all = sfs + (size_t)STAGES * SF_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_all + Pipe<EPI>::STG_BYTES);
+  float* slices = reinterpret_cast<float*>(sfs + (size_t)STAGES * SF_STAGE_BYTES);
+  float* slabs = slices + EPI_WARPS * SLICE_FLOATS;                        // ROPE only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS : 0));
   uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = tfull + 1;
   uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
@@ -84,145 +92,124 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     g.err[2] = blockIdx.x;
   }
 
-  if (bad_align) {
-    // nothing was issued; fall through to the teardown
-  } else if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
-        const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;              // the last column tile may hold only 128 columns
-        const uint32_t tx = TILE_BYTES + (SCALED ? (1 + w_halves) * ATOMS * 512 : 0);
-        for (int kt = 0; kt < g.k_tiles; ++kt) {
-          if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) { ok = false; break; }
-          mbar_expect_tx(&full[s], tx);
-          uint8_t* ta = tiles + (size_t)s * TILE_BYTES;
-          tma_load_2d(ta, &tmA, kt * BKB, m_blk * BM, &full[s]);
-          tma_load_2d(ta + A_BYTES, &tmW, kt * BKB, n_blk * BN, &full[s]);   // rows past N are filled with zeros
-          if (SCALED) {
-            uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
-            bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
-            for (int h = 0; h < w_halves; ++h)
-              bulk_load_1d(sa + (1 + h) * ATOMS * 512, g.sfw + ((size_t)(2 * n_blk + h) * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
-          }
-          if (++s == STAGES) { s = 0; ph ^= 1; }
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t IDESC = KIND == KIND_BF16 ? idesc_f16(1, BN)
-                                 : KIND == KIND_MX8 ? idesc_bs(0, 1, BN)
-                                 : KIND == KIND_NV4 ? idesc_bs(1, 0, BN)
-                                                    : idesc_bs(1, 1, BN);
-      uint32_t s = 0, ph = 0, lt = 0, sb = 0, sph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
-        if (!mbar_wait(tempty, (lt & 1) ^ 1, ctx, 2)) break;                  // the epilogue has taken the previous tile out of TMEM
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base;
-        for (int kt = 0; kt < g.k_tiles; ++kt) {
-          if (!mbar_wait(&full[s], ph, ctx, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + (size_t)s * TILE_BYTES);
-          const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + A_BYTES);
-          // scale factors of this stage: A at +0 (4 columns per atom), W at +16 (8 columns per atom pair: the atom of
-          // columns 0..127 of the tile, then the atom of columns 128..255)
-          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
-          if (SCALED) {                          // copied into TMEM by the scale-copy warp, which runs ahead of the MMAs
-            if (!mbar_wait(&sf_full[sb], sph, ctx, 5)) { ok = false; break; }
-            tc_fence_after();
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {                                       // 32 K-bytes per MMA
-            const uint32_t acc = (kt | j) != 0;
-            const uint64_t ad = adesc + 2 * j, bd = bdesc + 2 * j;
-            if (KIND == KIND_BF16) {
-              mma_f16(d_tmem, ad, bd, IDESC, acc);
-            } else if (KIND == KIND_MX8) {      // one scale per row per MMA: byte j of the atom's 32-bit word
-              mma_mxf8(d_tmem, ad, bd, idesc_with_sf_id(IDESC, j, j), acc, sf_t, sf_t + 16);
-            } else if (KIND == KIND_NV4) {      // four scales per row per MMA: atom j
-              mma_nvf4(d_tmem, ad, bd, IDESC, acc, sf_t + 4 * j, sf_t + 16 + 8 * j);
-            } else {                            // two scales per row per MMA: half-word (j & 1) of atom j / 2
-              mma_mxf4(d_tmem, ad, bd, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), acc, sf_t + 4 * (j >> 1), sf_t + 16 + 8 * (j >> 1));
+  if (warp < EPI_WARP0) {
+    setmaxnreg_dec<REGS_LEAN>();
+    if (bad_align) {
+      // nothing is issued; fall through to the teardown
+    } else if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        uint32_t s = 0, ph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+          const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
+          const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;              // the last column tile may hold only 128 columns
+          const uint32_t tx = TILE_BYTES + (SCALED ? (1 + w_halves) * ATOMS * 512 : 0);
+          for (int kt = 0; kt < g.k_tiles; ++kt) {
+            if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) { ok = false; break; }
+            mbar_expect_tx(&full[s], tx);
+            uint8_t* ta = tiles + (size_t)s * TILE_BYTES;
+            tma_load_2d(ta, &tmA, kt * BKB, m_blk * BM, &full[s]);
+            tma_load_2d(ta + A_BYTES, &tmW, kt * BKB, n_blk * BN, &full[s]);   // rows past N are filled with zeros
+            if (SCALED) {
+              uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
+              bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
+              for (int h = 0; h < w_halves; ++h)
+                bulk_load_1d(sa + (1 + h) * ATOMS * 512, g.sfw + ((size_t)(2 * n_blk + h) * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
             }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
-          tc_commit(&empty[s]);
-          if (SCALED) {
-            tc_commit(&sf_empty[sb]);
-            if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
-          }
-          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        if (ok) tc_commit(tfull);
       }
-    }
-    __syncwarp();
-  } else if (warp == SF_WARP) {
-    // ------------------------------------------------------------------ scale-factor copier
-    // tcgen05.cp of one 512-byte atom costs about as much tensor-pipe time as a 128 x 128 MMA, but it overlaps with
-    // the MMAs when it is issued from another warp; issued from the MMA thread the two serialise.  This warp therefore
-    // moves the atoms of stage s (shared memory -> one of SF_BUFS TMEM buffers) as soon as the TMA has landed them and
-    // hands the buffer to the MMA warp through an mbarrier.
-    if (SCALED && lane == 0) {
-      uint32_t s = 0, ph = 0, sb = 0, sph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int n_blk = tile % g.n_tiles;
-        const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;
-        for (int kt = 0; kt < g.k_tiles; ++kt) {
-          if (!mbar_wait(&sf_empty[sb], sph ^ 1, ctx, 6)) { ok = false; break; }
-          if (!mbar_wait(&full[s], ph, ctx, 7)) { ok = false; break; }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t IDESC = KIND == KIND_BF16 ? idesc_f16(1, BN)
+                                   : KIND == KIND_MX8 ? idesc_bs(0, 1, BN)
+                                   : KIND == KIND_NV4 ? idesc_bs(1, 0, BN)
+                                                      : idesc_bs(1, 1, BN);
+        uint32_t s = 0, ph = 0, lt = 0, sb = 0, sph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++lt) {
+          if (!mbar_wait(tempty, (lt & 1) ^ 1, ctx, 2)) break;                  // the epilogue has taken the previous tile out of TMEM
           tc_fence_after();
-          const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
-          const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
+          const uint32_t d_tmem = tmem_base;
+          for (int kt = 0; kt < g.k_tiles; ++kt) {
+            if (!mbar_wait(&full[s], ph, ctx, 3)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(tiles + (size_t)s * TILE_BYTES);
+            const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(a_addr + A_BYTES);
+            // scale factors of this stage: A at +0 (4 columns per atom), W at +16 (8 columns per atom pair: the atom of
+            // columns 0..127 of the tile, then the atom of columns 128..255)
+            const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
+            if (SCALED) {                          // copied into TMEM by the scale-copy warp, which runs ahead of the MMAs
+              if (!mbar_wait(&sf_full[sb], sph, ctx, 5)) { ok = false; break; }
+              tc_fence_after();
+            }
 #pragma unroll
-          for (int a = 0; a < ATOMS; ++a) {
-            tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
-            tc_cp_sf(sf_t + 16 + 8 * a, smem_desc_sf(sa + (ATOMS + a) * 512));
-            if (w_halves == 2) tc_cp_sf(sf_t + 16 + 8 * a + 4, smem_desc_sf(sa + (2 * ATOMS + a) * 512));
+            for (int j = 0; j < 4; ++j) {                                       // 32 K-bytes per MMA
+              const uint32_t acc = (kt | j) != 0;
+              const uint64_t ad = adesc + 2 * j, bd = bdesc + 2 * j;
+              if (KIND == KIND_BF16) {
+                mma_f16(d_tmem, ad, bd, IDESC, acc);
+              } else if (KIND == KIND_MX8) {      // one scale per row per MMA: byte j of the atom's 32-bit word
+                mma_mxf8(d_tmem, ad, bd, idesc_with_sf_id(IDESC, j, j), acc, sf_t, sf_t + 16);
+              } else if (KIND == KIND_NV4) {      // four scales per row per MMA: atom j
+                mma_nvf4(d_tmem, ad, bd, IDESC, acc, sf_t + 4 * j, sf_t + 16 + 8 * j);
+              } else {                            // two scales per row per MMA: half-word (j & 1) of atom j / 2
+                mma_mxf4(d_tmem, ad, bd, idesc_with_sf_id(IDESC, 2 * (j & 1), 2 * (j & 1)), acc, sf_t + 4 * (j >> 1), sf_t + 16 + 8 * (j >> 1));
+              }
+            }
+            tc_commit(&empty[s]);
+            if (SCALED) {
+              tc_commit(&sf_empty[sb]);
+              if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
+            }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
-          tc_commit(&sf_full[sb]);
-          if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (ok) tc_commit(tfull);
         }
       }
+      __syncwarp();
+    } else if (warp == 2) {
+      // ------------------------------------------------------------------ scale-factor copier
+      // tcgen05.cp of one 512-byte atom costs about as much tensor-pipe time as a 128 x 128 MMA, but it overlaps with
+      // the MMAs when it is issued from another warp; issued from the MMA thread the two serialise.  This warp therefore
+      // moves the atoms of stage s (shared memory -> one of SF_BUFS TMEM buffers) as soon as the TMA has landed them and
+      // hands the buffer to the MMA warp through an mbarrier.
+      if (SCALED && lane == 0) {
+        uint32_t s = 0, ph = 0, sb = 0, sph = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+          const int n_blk = tile % g.n_tiles;
+          const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;
+          for (int kt = 0; kt < g.k_tiles; ++kt) {
+            if (!mbar_wait(&sf_empty[sb], sph ^ 1, ctx, 6)) { ok = false; break; }
+            if (!mbar_wait(&full[s], ph, ctx, 7)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sf_t = tmem_base + TMEM_SF_COL + sb * SF_BUF_COLS;
+            const uint32_t sa = smem_u32(sfs + (size_t)s * SF_STAGE_BYTES);
+#pragma unroll
+            for (int a = 0; a < ATOMS; ++a) {
+              tc_cp_sf(sf_t + 4 * a, smem_desc_sf(sa + a * 512));
+              tc_cp_sf(sf_t + 16 + 8 * a, smem_desc_sf(sa + (ATOMS + a) * 512));
+              if (w_halves == 2) tc_cp_sf(sf_t + 16 + 8 * a + 4, smem_desc_sf(sa + (2 * ATOMS + a) * 512));
+            }
+            tc_commit(&sf_full[sb]);
+            if (++sb == SF_BUFS) { sb = 0; sph ^= 1; }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+          }
+        }
+      }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 64-column group)
-    const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
-    const int cg = (warp - 2) >> 2;               // which 64-column group of the 256-column tile
-    float* stg = reinterpret_cast<float*>(stg_all + (size_t)(warp - 2) * Pipe<EPI>::STG_STRIDE);   // staging tile, or the warp's bias slice
-    float ts = 1.f;
-    if (g.ts_a) ts *= __ldg(g.ts_a);
-    if (g.ts_w) ts *= __ldg(g.ts_w);
-    const Nv4Scale sco = nv4_scale((EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f);   // once per CTA: every global load here is an L2 round trip
-    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
-    uint32_t lt = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++lt) {
-      const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
-      const int rbase = m_blk * BM + quarter * 32;
-      const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
-      uint32_t r0[32], r1[32];
-      epilogue_bias_stage<EPI>(g, n0, stg, lane);
-      EpiPre pre;
-      epilogue_prefetch<EPI>(g, n0, lane, pre);
-      if (!mbar_wait(tfull, lt & 1, ctx, 4)) break;
-      tc_fence_after();
-      tmem_ld32(taddr, r0);
-      tmem_ld32(taddr + 32, r1);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
-      if (n0 >= g.N) continue;                                   // column group past N in the last column tile
-
-      epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, stg, lane, pre);
+    setmaxnreg_inc<REGS_EPI>();
+    if (!bad_align) {
+      const TileSched sched{(int)blockIdx.x, (int)gridDim.x, total_tiles, g.n_tiles, -1};
+      epilogue_warps<EPI>(g, sched, tmem_base, tfull, tempty, slices, slabs, ctx, warp, lane);
     }
   }
 
@@ -254,7 +241,34 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs about a microsecond of host time; an eager caller (the Linear swap) issues the same few
+// (pointer, shape) combinations over and over, so the encoded maps are kept in a small per-thread direct-mapped cache.
+struct TmapKey {
+  const void* base;
+  uint64_t rows, row_bytes, pitch_bytes;
+  uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && row_bytes == o.row_bytes && pitch_bytes == o.pitch_bytes && box_rows == o.box_rows;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+
 int make_tmap_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t pitch_bytes, uint32_t box_rows) {
+  constexpr int SLOTS = 256;
+  static thread_local TmapSlot cache[SLOTS] = {};
+  const TmapKey key{base, rows, row_bytes, pitch_bytes, box_rows};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+  h ^= rows * 0x9E3779B97F4A7C15ull;
+  h ^= (row_bytes << 7) ^ box_rows;
+  TmapSlot& slot = cache[(h ^ (h >> 17)) % SLOTS];
+  if (slot.used && slot.key == key) {
+    *map = slot.map;
+    return KF_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -271,6 +285,9 @@ int make_tmap_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64
               (unsigned long long)row_bytes);
     return KF_ERR_BAD_ARGUMENT;
   }
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
   return KF_OK;
 }
 
@@ -297,11 +314,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Pipe<EPI>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<EPI>());
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), Pipe<EPI>::SMEM, st, tmA, tmW, g), "kf_gemm_bs launch");
+  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), gemm_smem<EPI>(), st, tmA, tmW, g), "kf_gemm_bs launch");
 }
 
 template <int KIND>
@@ -315,16 +332,7 @@ static int launch_gemm_epi(int epi, const CUtensorMap& tmA, const CUtensorMap& t
 }
 
 static bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-int launch_gemm_pair(int fmt, int epi, const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g, int sms, cudaStream_t st);   // kf_gemm2.cu
-
-// The CTA-pair kernel (256 x 256 tiles, kf_gemm2.cu) is selected with KF_GEMM_PAIR=1 in the environment (read at every
-// call, so a test can switch it).  It is off by default: its cross-CTA hand-shakes (stage landed / stage free, relayed
-// through remote mbarrier arrivals) make its main loop slower than the one-CTA kernel's at the ViT shapes.
-static bool pair_mode() {
-  const char* e = getenv("KF_GEMM_PAIR");
-  return e != nullptr && e[0] == '1';
-}
+static bool al32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; }   // 256-bit global accesses of the epilogues
 
 }  // namespace kf
 
@@ -344,20 +352,20 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   if (fmt != KF_FMT_BF16) KF_REQUIRE(p->SFA && p->SFW && al16(p->SFA) && al16(p->SFW), "kf_gemm_bs: scale tensors must be non-null and 16-byte aligned");
   KF_REQUIRE(!p->bias || al16(p->bias), "kf_gemm_bs: bias must be 16-byte aligned");
   if (epi == KF_EPI_PLAIN) {
-    KF_REQUIRE(p->C && al16(p->C), "kf_gemm_bs: PLAIN needs a 16-byte aligned output C");
+    KF_REQUIRE(p->C && al32(p->C), "kf_gemm_bs: PLAIN needs a 32-byte aligned output C");
     KF_REQUIRE(p->out_row_group >= 0 && (p->out_row_group == 0 || (p->out_row_stride >= p->out_row_group && p->out_row_offset >= 0)),
                "kf_gemm_bs: bad output row mapping group=%d stride=%d offset=%d", p->out_row_group, p->out_row_stride, p->out_row_offset);
     KF_REQUIRE(p->out_dtype == KF_F32 || p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: bad out_dtype %d", p->out_dtype);
   } else if (epi == KF_EPI_RES) {
-    KF_REQUIRE(p->C && p->R && p->gamma && al16(p->C) && al16(p->R) && al16(p->gamma), "kf_gemm_bs: RES needs 16-byte aligned C, R and gamma");
+    KF_REQUIRE(p->C && p->R && p->gamma && al32(p->C) && al32(p->R) && al16(p->gamma), "kf_gemm_bs: RES needs 32-byte aligned C and R and a 16-byte aligned gamma");
   } else if (epi == KF_EPI_ROPE) {
-    KF_REQUIRE(p->C && al16(p->C) && p->sin && p->cos && al16(p->sin) && al16(p->cos), "kf_gemm_bs: ROPE needs 16-byte aligned C, sin and cos");
+    KF_REQUIRE(p->C && al32(p->C) && p->sin && p->cos && al32(p->sin) && al32(p->cos), "kf_gemm_bs: ROPE needs 32-byte aligned C, sin and cos");
     KF_REQUIRE(p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: ROPE output must be bf16 or f16");
     KF_REQUIRE(p->H > 0 && p->N == 3 * p->H * 64, "kf_gemm_bs: ROPE needs N = 3*H*64 (N=%d, H=%d)", p->N, p->H);
     KF_REQUIRE(p->Ntok > 0 && p->M % p->Ntok == 0 && p->prefix >= 0 && p->prefix <= p->Ntok, "kf_gemm_bs: ROPE needs M %% Ntok == 0 and 0 <= prefix <= Ntok");
   } else {
     KF_REQUIRE(p->out_fmt == KF_FMT_MX8 || p->out_fmt == KF_FMT_NV4 || p->out_fmt == KF_FMT_MX4, "kf_gemm_bs: bad quantise-out format %d", p->out_fmt);
-    KF_REQUIRE(p->Qo && p->SFo && al16(p->Qo) && al16(p->SFo), "kf_gemm_bs: QUANT needs 16-byte aligned Qo and SFo");
+    KF_REQUIRE(p->Qo && p->SFo && al32(p->Qo) && al16(p->SFo), "kf_gemm_bs: QUANT needs a 32-byte aligned Qo and a 16-byte aligned SFo");
     KF_REQUIRE(p->out_fmt != KF_FMT_NV4 || p->tso, "kf_gemm_bs: nv4 quantise-out needs the per-tensor scale tso");
     KF_REQUIRE(!p->y_dbg || al16(p->y_dbg), "kf_gemm_bs: y_dbg must be 16-byte aligned");
   }
@@ -365,8 +373,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   CUtensorMap tmA, tmW;
   int st = make_tmap_2d_bytes(&tmA, p->A, (uint64_t)p->M, kbytes, kbytes, BM);
   if (st != KF_OK) return st;
-  const bool pair = pair_mode();
-  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, pair ? 128 : BN);
+  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, BN);
   if (st != KF_OK) return st;
   GemmArgs g{};
   g.sfa = static_cast<const uint8_t*>(p->SFA);
@@ -388,7 +395,6 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   const int total = g.m_tiles * g.n_tiles;
   const int grid = total < sms ? total : sms;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  if (pair) return launch_gemm_pair(fmt, epi, tmA, tmW, g, sms, cs);
   switch (fmt) {
     case KF_FMT_MX8: return launch_gemm_epi<KIND_MX8>(epi, tmA, tmW, g, grid, cs);
     case KF_FMT_NV4: return launch_gemm_epi<KIND_NV4>(epi, tmA, tmW, g, grid, cs);

@@ -1,7 +1,13 @@
-// Shared pieces of the block-scaled GEMM kernels (one-CTA tiles in kf_gemm.cu, CTA-pair tiles in kf_gemm2.cu): argument
-// block, per-format traits, and the fused epilogues (PLAIN / RES / ROPE / QUANT) as one device function that works on a
-// 32-row x 64-column piece of the accumulator held in registers.  Epilogue math per
-// infer-opt/round13_mxfp8_full/impl/mgx_core.cu:308-426 and infer-opt/round14_fp4_full/impl/fp4g_core.cu:309-382.
+// Shared pieces of the block-scaled GEMM kernels: argument block, per-format traits and the fused epilogues
+// (PLAIN / RES / ROPE / QUANT) as one device function that works on a 32-row x 64-column piece of the accumulator held in
+// registers.  Epilogue math per infer-opt/round13_mxfp8_full/impl/mgx_core.cu:308-426 and
+// infer-opt/round14_fp4_full/impl/fp4g_core.cu:309-382.
+//
+// Every epilogue works in the layout tcgen05.ld delivers: thread `lane` of a warp owns 64 consecutive columns of ONE
+// output row.  That is 128 contiguous bytes of a 16-bit output (exactly one [token, head] row of the q/k/v layout) or
+// 256 contiguous bytes of an fp32 one, which the thread moves with 256-bit global loads / stores (ld/st.global.v8): every
+// access is a whole 32-byte sector, so nothing is restaged through shared memory and the only shared memory an epilogue
+// warp uses is a small slice with the bias (and LayerScale) values of its 64 columns.
 #pragma once
 #include "kf_sm100.cuh"
 
@@ -11,27 +17,15 @@ constexpr int KIND_MX8 = KF_FMT_MX8, KIND_NV4 = KF_FMT_NV4, KIND_MX4 = KF_FMT_MX
 constexpr int BM = 128, BN = 256, BKB = 128;          // tile rows, tile columns, K bytes per stage
 constexpr int A_BYTES = BM * BKB, TILE_BYTES = (BM + BN) * BKB;   // 16 KB of A, then 32 KB of W per stage
 constexpr int SF_STAGE_BYTES = 6144;                   // up to 4 atoms for A, then up to 4 + 4 for the two 128-row halves of W
-constexpr int STG_WARP_BYTES = 32 * 32 * 4;            // per epilogue warp: one 32 x 32 fp32 staging tile
 constexpr int EPI_WARPS = 16;
-constexpr int SF_WARP = 2 + EPI_WARPS;                 // warp index of the scale-factor copier
-constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);
+constexpr int EPI_WARP0 = 4;                           // warps 0..3: TMA producer, MMA issuer, scale-factor copier, spare
+constexpr int GEMM_THREADS = 32 * (EPI_WARP0 + EPI_WARPS);
 constexpr int SF_BUFS = 4;                             // scale-factor buffers in TMEM, 48 columns each (A at +0, W at +16)
 constexpr int SF_BUF_COLS = 48;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;                       // accumulator: columns [0,256); scale factors from 256
-// Only the epilogues that restage through shared memory (RES, ROPE) reserve the 64 KB of staging tiles.  A fourth
-// pipeline stage in the space the others save was measured: no gain for the block-scaled kinds (NVFP4 plain 111 vs 104 us),
-// 5 % for bf16, so all kernels run 3 stages.
-template <int EPI>
-struct Pipe {
-  static constexpr bool STAGING = EPI == KF_EPI_RES || EPI == KF_EPI_ROPE;
-  // per epilogue warp: a 32 x 32 fp32 staging tile (RES / ROPE), else the 64 bias values of the warp's columns (the
-  // kernel's shared memory leaves little L1, so bias loads inside the chunk loops would each wait on L2)
-  static constexpr int STG_STRIDE = STAGING ? STG_WARP_BYTES : 256;
-  static constexpr int STG_BYTES = EPI_WARPS * STG_STRIDE;
-  static constexpr int STAGES = 3;
-  static constexpr size_t SMEM = (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + STG_BYTES + 256;
-};
+constexpr int SLICE_FLOATS = 128;                      // per epilogue warp: 64 bias values, then 64 LayerScale values (RES)
+constexpr int ROPE_SLAB_FLOATS = 32 * 64;              // per TMEM lane quarter: 32 rows x (32 sin | 32 cos) values of the rotary tables
 static_assert(TMEM_SF_COL + SF_BUFS * SF_BUF_COLS <= TMEM_COLS, "TMEM budget");
 
 struct GemmArgs {
@@ -59,56 +53,47 @@ struct KindTraits<KIND_MX4> { static constexpr int ATOMS = 2; };   // 256 elemen
 template <>
 struct KindTraits<KIND_BF16> { static constexpr int ATOMS = 0; };
 
-// ------------------------------------------------------------------------------------------------ epilogue pieces
-// tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns per load).  Where global memory wants a
-// warp to touch consecutive addresses (the fp32 residual stream, the rotary tables), the warp restages a 32 x 32
-// chunk through a private shared-memory tile (128 bytes per row, 16-byte pieces XOR-swizzled by the row so both
-// directions are bank-conflict free) and continues in the "coalesced" layout: in pass i (0..7) lane l owns the 4
-// columns 4*(l&7).. of row 4*i + (l>>3), so a warp instruction covers 4 rows x 128 contiguous bytes.
-__device__ __forceinline__ void stg_put(float* stg, int lane, const uint32_t (&r)[32]) {
-  uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) row[c ^ (lane & 7)] = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+// ------------------------------------------------------------------------------------------------ 256-bit global accesses
+struct F8 {
+  float v[8];
+};
+__device__ __forceinline__ F8 ldg8_stream(const float* p) {   // 32-byte aligned; read once: do not keep the line in L1
+  F8 r;
+  asm volatile("ld.global.L1::no_allocate.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+               : "l"(p));
+  return r;
 }
-__device__ __forceinline__ float4 stg_get(const float* stg, int lane, int i) {
-  const int row = 4 * i + (lane >> 3);
-  return reinterpret_cast<const float4*>(stg + row * 32)[(lane & 7) ^ (row & 7)];
+__device__ __forceinline__ F8 ldg8_nc(const float* p) {       // read-only data shared by several warps (rotary tables)
+  F8 r;
+  asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+               : "l"(p));
+  return r;
 }
-__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
-__device__ __forceinline__ float4 ld4_stream(const float* p) {   // read once: do not keep the line in L1
-  float4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
+__device__ __forceinline__ float4 ldg4_nc(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void stg8(void* p, float a, float b, float c, float d, float e, float f, float g, float h) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d), "f"(e), "f"(f), "f"(g), "f"(h)
+               : "memory");
 }
-// four-wide helpers on packed pairs (two issue slots per float4)
-__device__ __forceinline__ float4 join4(float2 a, float2 b) { return make_float4(a.x, a.y, b.x, b.y); }
-__device__ __forceinline__ float4 fma4(float4 a, float s, float4 b) {
-  const float2 s2 = splat2(s);
-  return join4(fma2(make_float2(a.x, a.y), s2, make_float2(b.x, b.y)), fma2(make_float2(a.z, a.w), s2, make_float2(b.z, b.w)));
+__device__ __forceinline__ void stg8w(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+               "r"(w[6]), "r"(w[7])
+               : "memory");
 }
-__device__ __forceinline__ float4 fma4v(float4 a, float4 b, float4 c) {      // a * b + c
-  return join4(fma2(make_float2(a.x, a.y), make_float2(b.x, b.y), make_float2(c.x, c.y)),
-               fma2(make_float2(a.z, a.w), make_float2(b.z, b.w), make_float2(c.z, c.w)));
-}
-__device__ __forceinline__ float4 mul4v(float4 a, float4 b) {
-  return join4(mul2(make_float2(a.x, a.y), make_float2(b.x, b.y)), mul2(make_float2(a.z, a.w), make_float2(b.z, b.w)));
-}
-__device__ __forceinline__ uint2 pack4(float4 v, int out_dtype) {
-  uint2 o;
+// two fp32 -> one 32-bit word of two bf16 / f16 values (first value in the low half)
+__device__ __forceinline__ uint32_t pack2(float a, float b, int out_dtype) {
   if (out_dtype == KF_BF16) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-    o.x = *reinterpret_cast<uint32_t*>(&a);
-    o.y = *reinterpret_cast<uint32_t*>(&b);
-  } else {
-    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-    o.x = *reinterpret_cast<uint32_t*>(&a);
-    o.y = *reinterpret_cast<uint32_t*>(&b);
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
   }
-  return o;
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// QUANT epilogue of one 32-column chunk in the row layout: the thread owns columns n0..n0+31 of row m = two nv4 blocks
-// or one mx block, so block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
+// ------------------------------------------------------------------------------------------------ QUANT
+// QUANT epilogue of one 32-column chunk: the thread owns columns n0..n0+31 of row m = two nv4 blocks or one mx block, so
+// block maxima need no shuffles and the per-block scale arithmetic is paid once per 16 / 32 values.
 // The codes and scale bytes are the bit specification's quantisation (IEEE divisions, as in the row quantiser) of the
 // values gelu(acc*ts + bias), optionally rounded to bf16, which y_dbg exports for the parity tests.
 
@@ -144,19 +129,14 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
   float* dbg = (g.y_dbg != nullptr && ok) ? g.y_dbg + (size_t)m * g.N + n0 : nullptr;
   int by0, by1;
   if (g.out_fmt == KF_FMT_NV4) {
-    // one 16-value block at a time: the exact division keeps a quotient per value live
     uint32_t o[4];
-    {
-      float v[16];
-      const float am = quant_values16(g, r, 0, ts, bsm, dbg, v);
-      if (g.flags & KF_Q_FAST_NV4) quant_nv4_fast<16>(v, am, sco.ts, sco.rcp_ts, o, by0);
-      else quant_nv4<16>(v, am, sco, div_true, o, by0);
-    }
-    {
-      float v[16];
-      const float am = quant_values16(g, r, 1, ts, bsm, dbg, v);
-      if (g.flags & KF_Q_FAST_NV4) quant_nv4_fast<16>(v, am, sco.ts, sco.rcp_ts, o + 2, by1);
-      else quant_nv4<16>(v, am, sco, div_true, o + 2, by1);
+    float va[16], vb[16];
+    const float am0 = quant_values16(g, r, 0, ts, bsm, dbg, va), am1 = quant_values16(g, r, 1, ts, bsm, dbg, vb);
+    if (g.flags & KF_Q_FAST_NV4) {
+      quant_nv4_fast<16>(va, am0, sco.ts, sco.rcp_ts, o, by0);
+      quant_nv4_fast<16>(vb, am1, sco.ts, sco.rcp_ts, o + 2, by1);
+    } else {
+      quant_nv4_pair16(va, am0, vb, am1, sco, div_true, o, by0, by1);
     }
     if (ok) *reinterpret_cast<uint4*>(g.Qo + (size_t)m * (g.N >> 1) + (n0 >> 1)) = make_uint4(o[0], o[1], o[2], o[3]);
     // two scale bytes of this row for the chunk (rows beyond M inside the last tile get zeros)
@@ -169,11 +149,7 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
     uint32_t o[8];
     quant_mx8<16>(va, am, div_true, o, by0);
     quant_mx8<16>(vb, am, div_true, o + 4, by0);
-    if (ok) {
-      uint4* p = reinterpret_cast<uint4*>(g.Qo + (size_t)m * g.N + n0);
-      p[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      p[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    }
+    if (ok) stg8w(g.Qo + (size_t)m * g.N + n0, o);
     g.SFo[sf_offset(m, n0 >> 5, g.N >> 7)] = ok ? (uint8_t)by0 : (uint8_t)0;
   } else {
     uint32_t o[4];
@@ -184,18 +160,19 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
   }
 }
 
-// PLAIN epilogue of one 32-column chunk in the row layout: the thread writes 64 (16-bit) or 128 (fp32) contiguous bytes.
+// ------------------------------------------------------------------------------------------------ PLAIN
+// PLAIN epilogue of one 32-column chunk: the thread writes 64 (16-bit) or 128 (fp32) contiguous bytes of its row.
 __device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&r)[32], float ts, uint8_t* dst_row, int n0, const float* bsm /* the chunk's 32 bias values in shared memory */) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float v[8];
+  for (int q = 0; q < 2; ++q) {                 // 16 columns at a time
+    float v[16];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + 8 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int h = 0; h < 4; ++h) {
+      const float4 bb = g.bias ? *reinterpret_cast<const float4*>(bsm + 16 * q + 4 * h) : make_float4(0.f, 0.f, 0.f, 0.f);
       const float b4[4] = {bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float a = __uint_as_float(r[8 * q + 4 * h + e]);
+        const float a = __uint_as_float(r[16 * q + 4 * h + e]);
         float x = (g.flags & KF_G_PRE_ROUND_BF16) ? bf16_round(a * ts) + b4[e] : fmaf(a, ts, b4[e]);   // the result may be rounded to bf16 before the bias
         if (g.flags & KF_G_GELU) x = gelu_erf(x);
         if (g.flags & KF_G_ROUND_BF16) x = bf16_round(x);
@@ -204,153 +181,236 @@ __device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&
     }
     if (dst_row) {
       if (g.out_dtype == KF_F32) {
-        float4* d = reinterpret_cast<float4*>(dst_row + (size_t)(n0 + 8 * q) * 4);
-        d[0] = make_float4(v[0], v[1], v[2], v[3]);
-        d[1] = make_float4(v[4], v[5], v[6], v[7]);
+        float* d = reinterpret_cast<float*>(dst_row) + n0 + 16 * q;
+        stg8(d, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
+        stg8(d + 8, v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15]);
       } else {
-        const uint2 lo = pack4(make_float4(v[0], v[1], v[2], v[3]), g.out_dtype), hi = pack4(make_float4(v[4], v[5], v[6], v[7]), g.out_dtype);
-        *reinterpret_cast<uint4*>(dst_row + (size_t)(n0 + 8 * q) * 2) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = pack2(v[2 * e], v[2 * e + 1], g.out_dtype);
+        stg8w(dst_row + (size_t)(n0 + 16 * q) * 2, w);
       }
     }
   }
 }
 
-// PLAIN / QUANT: the 64 bias values of the warp's columns go to its shared-memory slice (one coalesced load per tile,
-// issued before the wait for the accumulator so that its L2 latency runs under that wait); the chunk loops then read
-// them as broadcast float4s.
+// The bias values (and for RES the LayerScale values) of the warp's 64 columns go to its shared-memory slice with one
+// coalesced load per tile, issued before the wait for the accumulator so that its L2 latency runs under that wait (the
+// kernel's shared memory leaves little L1: a load inside the chunk loops would be an L2 round trip); the chunk loops then
+// read them as broadcast float4s.
 template <int EPI>
-__device__ __forceinline__ void epilogue_bias_stage(const GemmArgs& g, int n0, float* stg, int lane) {
-  if constexpr (!Pipe<EPI>::STAGING) {
-    if (g.bias && n0 < g.N) {
-      const float2 b2 = __ldg(reinterpret_cast<const float2*>(g.bias + n0) + lane);
-      __syncwarp();                                // every lane has finished reading the previous tile's values
-      reinterpret_cast<float2*>(stg)[lane] = b2;
-      __syncwarp();
+__device__ __forceinline__ void epilogue_slice_stage(const GemmArgs& g, int n0, float* slice, int lane) {
+  if (n0 >= g.N) return;
+  float2 b2 = make_float2(0.f, 0.f), g2 = make_float2(0.f, 0.f);
+  if (g.bias) b2 = __ldg(reinterpret_cast<const float2*>(g.bias + n0) + lane);
+  if (EPI == KF_EPI_RES) g2 = __ldg(reinterpret_cast<const float2*>(g.gamma + n0) + lane);
+  __syncwarp();                                // every lane has finished reading the previous tile's values
+  reinterpret_cast<float2*>(slice)[lane] = b2;
+  if (EPI == KF_EPI_RES) reinterpret_cast<float2*>(slice + 64)[lane] = g2;
+  __syncwarp();
+}
+
+// ------------------------------------------------------------------------------------------------ ROPE table slab
+// Rotary tables whose columns 32..63 repeat columns 0..31 (KF_G_ROPE_HALF; true for the axial tables of DINOv3, where the
+// angle vector is concatenated with itself): the 4 warps that share a TMEM lane quarter (the 4 heads of a 256-column tile)
+// need the same 32 table rows.  Together they fetch them with coalesced loads BEFORE the wait for the accumulator (the L2
+// latency runs under that wait, 4 float4 per thread held in registers), then park them in the quarter's slab:
+// row j = [sin 0..31 | cos 0..31] of token rbase + j, 16-byte pieces XOR-swizzled by the row so that the row-layout reads
+// of the epilogue (lane = row) are free of bank conflicts.
+struct RopeSlabRegs {
+  float4 v[4];
+};
+__device__ __forceinline__ void rope_slab_fetch(const GemmArgs& g, int rbase, int tid /* 0..127 within the quarter */, RopeSlabRegs& x) {
+  const int f = tid & 15;                                            // piece of the row: 0..7 sin, 8..15 cos
+  const float* tab = (f < 8 ? g.sin : g.cos) + ((f & 7) << 2);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int m = rbase + (tid >> 4) + 8 * u;
+    x.v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < g.M) {
+      const int t = m % g.Ntok;
+      if (t >= g.prefix) x.v[u] = __ldg(reinterpret_cast<const float4*>(tab + (size_t)(t - g.prefix) * 64));
     }
   }
 }
+__device__ __forceinline__ void rope_slab_store(float* slab, int tid, const RopeSlabRegs& x) {
+  const int f = tid & 15;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int row = (tid >> 4) + 8 * u;
+    *reinterpret_cast<float4*>(slab + row * 64 + ((f ^ (row & 7)) << 2)) = x.v[u];
+  }
+}
+__device__ __forceinline__ void quarter_barrier(int quarter) { asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory"); }
 
 // ------------------------------------------------------------------------------------------------ the fused epilogues
 // One epilogue warp's share of a tile: rows rbase..rbase+31 (thread `lane` holds row rbase + lane of the accumulator),
-// columns n0..n0+63 (r0 = first 32, r1 = last 32).  `stg` is the warp's private 32 x 32 fp32 staging tile.
-// What an epilogue can fetch before its accumulator exists: ROPE takes its two bias vectors, which then land during the
-// wait for the accumulator instead of in front of the first arithmetic (qkv 90 -> 86 us).  The same for the first round
-// of residual loads of RES was measured slower (proj 55 -> 59 us): 24 more registers live across the accumulator load
-// spill under the 96-register cap of the 608-thread CTA.
-struct EpiPre {
-  float4 b0, b1;
-};
+// columns n0..n0+63 (r0 = first 32, r1 = last 32).  `slice` is the warp's bias / LayerScale slice in shared memory.
 template <int EPI>
-__device__ __forceinline__ void epilogue_prefetch(const GemmArgs& g, int n0, int lane, EpiPre& p) {
-  if constexpr (EPI == KF_EPI_ROPE) {
-    const int c4 = 4 * (lane & 7);
-    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (n0 >= g.N) return;
-    p.b0 = g.bias ? ldg4(g.bias + n0 + c4) : z4;
-    p.b1 = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4;
-  }
-}
-
-template <int EPI>
-__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0, float* stg,
-                                              int lane, const EpiPre& pre) {
-  const int c4 = 4 * (lane & 7);                // coalesced layout: this lane's 4 columns inside a 32-column chunk
-  const int rsub = lane >> 3;                   // coalesced layout: row 4*i + rsub in pass i
-  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+__device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0,
+                                              const float* slice, const float* slab /* ROPE: the quarter's table rows in shared memory, or null */, int lane) {
+  const int m = rbase + lane;
   if (EPI == KF_EPI_ROPE) {
-    // the 64 columns of this warp are one head of q, k or v: r0 = first half, r1 = second half.  Both halves go
-    // through the staging tile into the coalesced layout (the first stays in registers, the second is read back
-    // pass by pass), where the rotary tables and the output rows are read / written 4 rows x 128 bytes at a time.
+    // the 64 columns of this warp are one head of q, k or v and the thread's 64 values are one [token, head] row of the
+    // output: r0 = first half, r1 = second half of the rotation pairs, so the rotary embedding needs no data exchange:
+    //   lo' = lo*cos_lo - hi*sin_lo (tables of columns 0..31), hi' = hi*cos_hi + lo*sin_hi (tables of columns 32..63).
+    // With KF_G_ROPE_HALF the table row of every token of the warp's quarter is already in shared memory (rope_slab_*).
+    if (m >= g.M) return;
     const int which = n0 / g.d, h = (n0 - which * g.d) >> 6;
+    const int b = m / g.Ntok, t = m - b * g.Ntok;
     const int nbatch = g.M / g.Ntok;
-    const int b0 = rbase / g.Ntok, t0 = rbase - b0 * g.Ntok;   // one division per tile; rows advance from here
-    const float4 b_lo = pre.b0, b_hi = pre.b1;
-    float4 lo[8];
-    stg_put(stg, lane, r0);
-    __syncwarp();
+    const bool rot = which < 2 && t >= g.prefix;
+    const float* sn = g.sin + (size_t)(rot ? t - g.prefix : 0) * 64;
+    const float* cs = g.cos + (size_t)(rot ? t - g.prefix : 0) * 64;
+    const float* srow = slab + lane * 64;
+    uint8_t* dst = static_cast<uint8_t*>(g.C) + ((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 128;
+    uint32_t wlo[8], whi[8];                    // 16 output columns of each half: stored as soon as they are complete
+    const float2 ts2 = splat2(ts);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) lo[i] = fma4(stg_get(stg, lane, i), ts, b_lo);
-    __syncwarp();
-    stg_put(stg, lane, r1);
-    __syncwarp();
+    for (int c = 0; c < 8; ++c) {               // 4 rotation pairs at a time (few values live: the thread already holds 64 accumulators)
+      float2 lo[2], hi[2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int m = rbase + 4 * i + rsub;
-      if (m < g.M) {
-        int b = b0, t = t0 + 4 * i + rsub;
-        while (t >= g.Ntok) {
-          t -= g.Ntok;
-          ++b;
+      for (int e = 0; e < 2; ++e) {
+        const int j = 4 * c + 2 * e;
+        lo[e] = fma2(make_float2(__uint_as_float(r0[j]), __uint_as_float(r0[j + 1])), ts2, *reinterpret_cast<const float2*>(slice + j));
+        hi[e] = fma2(make_float2(__uint_as_float(r1[j]), __uint_as_float(r1[j + 1])), ts2, *reinterpret_cast<const float2*>(slice + 32 + j));
+      }
+      float2 ol[2] = {lo[0], lo[1]}, oh[2] = {hi[0], hi[1]};
+      if (rot) {
+        float4 s4, c4;                          // sin / cos of the 4 pairs: first for the lo outputs, then for the hi outputs
+        if (slab != nullptr) {                  // both halves of the tables are the same 32 values
+          s4 = *reinterpret_cast<const float4*>(srow + ((c ^ (lane & 7)) << 2));
+          c4 = *reinterpret_cast<const float4*>(srow + (((c + 8) ^ (lane & 7)) << 2));
+        } else {
+          s4 = ldg4_nc(sn + 4 * c);
+          c4 = ldg4_nc(cs + 4 * c);
         }
-        const float4 hi = fma4(stg_get(stg, lane, i), ts, b_hi);
-        float4 ol = lo[i], oh = hi;
-        if (which < 2 && t >= g.prefix) {
-          const float* tab = g.sin + (size_t)(t - g.prefix) * 64 + c4;
-          const float* tabc = g.cos + (size_t)(t - g.prefix) * 64 + c4;
-          const float4 sl = ldg4(tab), cl = ldg4(tabc), sh = ldg4(tab + 32), ch = ldg4(tabc + 32);
-          // lo' = lo*cos - hi*sin (tables of columns 0..31), hi' = hi*cos + lo*sin (tables of columns 32..63)
-          ol = fma4v(hi, make_float4(-sl.x, -sl.y, -sl.z, -sl.w), mul4v(lo[i], cl));
-          oh = fma4v(hi, ch, mul4v(lo[i], sh));
+        ol[0] = fma2(hi[0], make_float2(-s4.x, -s4.y), mul2(lo[0], make_float2(c4.x, c4.y)));
+        ol[1] = fma2(hi[1], make_float2(-s4.z, -s4.w), mul2(lo[1], make_float2(c4.z, c4.w)));
+        if (slab == nullptr) {
+          s4 = ldg4_nc(sn + 32 + 4 * c);
+          c4 = ldg4_nc(cs + 32 + 4 * c);
         }
-        uint8_t* dst = static_cast<uint8_t*>(g.C) + (((((size_t)which * nbatch + b) * g.Ntok + t) * g.H + h) * 64 + c4) * 2;
-        *reinterpret_cast<uint2*>(dst) = pack4(ol, g.out_dtype);
-        *reinterpret_cast<uint2*>(dst + 64) = pack4(oh, g.out_dtype);
+        oh[0] = fma2(hi[0], make_float2(c4.x, c4.y), mul2(lo[0], make_float2(s4.x, s4.y)));
+        oh[1] = fma2(hi[1], make_float2(c4.z, c4.w), mul2(lo[1], make_float2(s4.z, s4.w)));
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        wlo[2 * (c & 3) + e] = pack2(ol[e].x, ol[e].y, g.out_dtype);
+        whi[2 * (c & 3) + e] = pack2(oh[e].x, oh[e].y, g.out_dtype);
+      }
+      if ((c & 3) == 3) {
+        stg8w(dst + 32 * (c >> 2), wlo);
+        stg8w(dst + 64 + 32 * (c >> 2), whi);
       }
     }
-    __syncwarp();                                             // the staging tile is reused by the next tile
   } else if (EPI == KF_EPI_RES) {
-    // two 32-column chunks, each restaged so that the fp32 residual is read and written 128 contiguous bytes per row.
-    // Four rounds (chunk, half of the 8 passes); the residual loads of round r + 1 are in flight while round r is worked
-    // out, so only the first round waits for its loads.
-    auto load_round = [&](int r, float4 (&rr)[4]) {
-      const int n = n0 + 32 * (r >> 1) + c4;
+    // out = R + gamma * (acc*ts + bias) on the thread's 256 contiguous bytes of the fp32 residual row: eight 32-byte pieces,
+    // four residual loads in flight ahead of the arithmetic.
+    if (m >= g.M) return;
+    const float* rrow = g.R + (size_t)m * g.N + n0;
+    float* crow = static_cast<float*>(g.C) + (size_t)m * g.N + n0;
+    const float2 ts2 = splat2(ts);
+    F8 rr[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int m = rbase + 4 * (4 * (r & 1) + i) + rsub;
-        rr[i] = m < g.M ? ld4_stream(g.R + (size_t)m * g.N + n) : z4;
-      }
-    };
-    auto do_round = [&](int r, const float4 (&rr)[4], const float4& b4, const float4& g4) {
-      const int n = n0 + 32 * (r >> 1) + c4;
+    for (int c = 0; c < 4; ++c) rr[c] = ldg8_stream(rrow + 8 * c);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int m = rbase + 4 * (4 * (r & 1) + i) + rsub;
-        const float4 v = fma4(stg_get(stg, lane, 4 * (r & 1) + i), ts, b4);
-        if (m < g.M)
-          *reinterpret_cast<float4*>(static_cast<float*>(g.C) + (size_t)m * g.N + n) =
-              fma4v(g4, v, rr[i]);
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t* acc = c < 4 ? &r0[8 * c] : &r1[8 * (c - 4)];
+      const F8 cur = rr[c & 3];
+      if (c + 4 < 8) rr[c & 3] = ldg8_stream(rrow + 8 * (c + 4));
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float2 bb = *reinterpret_cast<const float2*>(slice + 8 * c + e), gg = *reinterpret_cast<const float2*>(slice + 64 + 8 * c + e);
+        const float2 v = fma2(make_float2(__uint_as_float(acc[e]), __uint_as_float(acc[e + 1])), ts2, bb);
+        const float2 w = fma2(gg, v, make_float2(cur.v[e], cur.v[e + 1]));
+        o[e] = w.x;
+        o[e + 1] = w.y;
       }
-    };
-    float4 rra[4], rrb[4];
-    load_round(0, rra);
-    const float4 b40 = g.bias ? ldg4(g.bias + n0 + c4) : z4, g40 = ldg4(g.gamma + n0 + c4);
-    const float4 b41 = g.bias ? ldg4(g.bias + n0 + 32 + c4) : z4, g41 = ldg4(g.gamma + n0 + 32 + c4);
-    stg_put(stg, lane, r0);
-    __syncwarp();
-    load_round(1, rrb);
-    do_round(0, rra, b40, g40);
-    load_round(2, rra);
-    do_round(1, rrb, b40, g40);
-    __syncwarp();                                             // the staging tile is reused by the second chunk
-    stg_put(stg, lane, r1);
-    __syncwarp();
-    load_round(3, rrb);
-    do_round(2, rra, b41, g41);
-    do_round(3, rrb, b41, g41);
-    __syncwarp();                                             // ... and by the next tile
+      stg8(crow + 8 * c, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
+    }
   } else if (EPI == KF_EPI_PLAIN) {
-    const int m = rbase + lane;
     uint8_t* dst_row = nullptr;
     if (m < g.M) {
       const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
       dst_row = static_cast<uint8_t*>(g.C) + (size_t)orow * g.N * (g.out_dtype == KF_F32 ? 4 : 2);
     }
-    plain_chunk(g, r0, ts, dst_row, n0, stg);
-    plain_chunk(g, r1, ts, dst_row, n0 + 32, stg + 32);
+    plain_chunk(g, r0, ts, dst_row, n0, slice);
+    plain_chunk(g, r1, ts, dst_row, n0 + 32, slice + 32);
   } else {   // KF_EPI_QUANT: gelu(acc*ts + bias) -> codes + blocked scales of format out_fmt
-    quant_chunk(g, r0, ts, sco, rbase + lane, n0, stg);
-    quant_chunk(g, r1, ts, sco, rbase + lane, n0 + 32, stg + 32);
+    quant_chunk(g, r0, ts, sco, m, n0, slice);
+    quant_chunk(g, r1, ts, sco, m, n0 + 32, slice + 32);
   }
 }
+
+// ------------------------------------------------------------------------------------------------ tile schedules and the epilogue warps' loop
+// The i-th tile of a persistent CTA: tiles start, start + step, ... of the row-major tile grid (n_fixed < 0), or a fixed
+// column block with the row blocks start, start + step, ... (a weight-stationary schedule).
+struct TileSched {
+  int start, step, total, n_tiles, n_fixed;     // n_fixed < 0: row-major walk over (m, n); else the column block every tile uses
+  __device__ __forceinline__ bool get(int i, int& m_blk, int& n_blk) const {
+    const int idx = start + i * step;
+    if (idx >= total) return false;
+    if (n_fixed >= 0) {
+      m_blk = idx;
+      n_blk = n_fixed;
+    } else {
+      m_blk = idx / n_tiles;
+      n_blk = idx - m_blk * n_tiles;
+    }
+    return true;
+  }
+};
+
+// Body of the 16 epilogue warps (warp = (TMEM lane quarter, 64-column group)): per tile, stage the bias slice (and fetch the
+// rotary-table rows), wait for the accumulator, take the warp's 32 x 64 piece into registers, hand TMEM back at once and
+// run the fused epilogue on the registers while the next tile's main loop fills the accumulator again.
+template <int EPI>
+__device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSched& sched, uint32_t tmem_base, uint64_t* tfull, uint64_t* tempty, float* slices,
+                                               float* slabs, const WaitCtx& ctx, int warp, int lane) {
+  const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+  const int cg = (warp - EPI_WARP0) >> 2;       // which 64-column group of the 256-column tile
+  float* slice = slices + (warp - EPI_WARP0) * SLICE_FLOATS;
+  float ts = 1.f;
+  if (g.ts_a) ts *= __ldg(g.ts_a);
+  if (g.ts_w) ts *= __ldg(g.ts_w);
+  const Nv4Scale sco = nv4_scale((EPI == KF_EPI_QUANT && g.out_fmt == KF_FMT_NV4) ? __ldg(g.tso) : 1.f);   // once per CTA: every global load here is an L2 round trip
+  const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
+  int m_blk, n_blk;
+  for (int lt = 0; sched.get(lt, m_blk, n_blk); ++lt) {
+    const int rbase = m_blk * BM + quarter * 32;
+    const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
+    uint32_t r0[32], r1[32];
+    epilogue_slice_stage<EPI>(g, n0, slice, lane);
+    // ROPE with half tables: the quarter's table rows are fetched now and parked in shared memory after the wait
+    const bool use_slab = EPI == KF_EPI_ROPE && (g.flags & KF_G_ROPE_HALF) != 0 && n_blk * BN < 2 * g.d;   // the tile holds q or k columns
+    RopeSlabRegs tab;
+    if (EPI == KF_EPI_ROPE && use_slab) rope_slab_fetch(g, rbase, cg * 32 + lane, tab);
+    if (!mbar_wait(tfull, lt & 1, ctx, 4)) break;
+    tc_fence_after();
+    tmem_ld32(taddr, r0);
+    tmem_ld32(taddr + 32, r1);
+    tmem_ld_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tempty);                       // the accumulator is in registers: hand TMEM back
+    float* slab = nullptr;
+    if (EPI == KF_EPI_ROPE && use_slab) {                      // all 4 warps of the quarter take this path together (it depends on the tile only)
+      slab = slabs + quarter * ROPE_SLAB_FLOATS;
+      quarter_barrier(quarter);                                // the previous tile's rows have been read by all four warps
+      rope_slab_store(slab, cg * 32 + lane, tab);
+      quarter_barrier(quarter);
+    }
+    if (n0 >= g.N) continue;                                   // column group past N in the last column tile
+    epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, slice, slab, lane);
+  }
+}
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+constexpr int REGS_LEAN = 40, REGS_EPI = 104;          // 128 * 40 + 512 * 104 <= 640 * 96, the allocation at launch
 
 }  // namespace kf

@@ -129,6 +129,18 @@ __global__ void __launch_bounds__(128, 1) fill_kernel(const uint8_t* __restrict_
   __syncthreads();
 }
 
+// ------------------------------------------------------------------------------------------------ reciprocal self-test
+// Every significand of one binade: the three-instruction correctly rounded reciprocal of the quantisers (rcp_rn_pair)
+// against __frcp_rn.  Significands that are all ones are outside its contract (callers route them to __fdiv_rn).
+__global__ void rcp_selftest_kernel(int exponent, unsigned int* mismatches) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;           // 2^23 threads
+  if (i >= (1u << 23) - 1u) return;
+  const float d = __uint_as_float(((uint32_t)(exponent + 127) << 23) | i);
+  const float2 r = rcp_rn_pair(make_float2(d, -d));
+  const float ref = __frcp_rn(d);
+  if (r.x != ref || r.y != -ref) atomicAdd(mismatches, 1u);
+}
+
 }  // namespace kf
 
 using namespace kf;
@@ -169,4 +181,11 @@ extern "C" int kf_tensor_peak_probe(int fmt, int n, int iters, int sf_copies, do
     case KF_FMT_MX4: return launch_peak<KF_FMT_MX4>(n, iters, sf_copies, sms, err, cs);
     default: return launch_peak<KF_FMT_BF16>(n, iters, sf_copies, sms, err, cs);
   }
+}
+
+extern "C" int kf_selftest_rcp(int exponent, unsigned int* mismatches, void* stream) {
+  KF_REQUIRE(exponent >= -59 && exponent <= 59, "kf_selftest_rcp: exponent must be within -59..59 (the range the quantisers use the routine in)");
+  KF_REQUIRE(mismatches != nullptr, "kf_selftest_rcp: null counter");
+  rcp_selftest_kernel<<<(1 << 23) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(exponent, mismatches);
+  return cuda_status(cudaGetLastError(), "kf_selftest_rcp launch");
 }

@@ -63,7 +63,8 @@ def bench_gemm(args):
     bias = torch.randn(N, device="cuda") * 0.02
     gamma = torch.rand(N, device="cuda")
     H = 16
-    sin, cos = torch.randn(args.tokens, 64, device="cuda"), torch.randn(args.tokens, 64, device="cuda")
+    ang = torch.rand(args.tokens, 32, device="cuda") * 6.28                 # second half of the tables = first half, as in the model
+    sin, cos = torch.sin(torch.cat((ang, ang), 1)).contiguous(), torch.cos(torch.cat((ang, ang), 1)).contiguous()    # [tokens, 64]: more rows than any prefix needs
     res = [torch.randn(M, N, device="cuda") for _ in range(2)] if args.kind in ("proj", "fc2") else None
     outq = ops.ActBuf(M, N, fmt if fmt != "bf16" else "mx8") if args.kind == "fc1" else None
     if outq is not None and outq.fmt == "nv4":
@@ -73,7 +74,7 @@ def bench_gemm(args):
     def fn(i):
         a, W = acts[i % 2], Ws[i % len(Ws)]
         if args.kind == "qkv":
-            ops.qkv_rope(a, W, bias, sin, cos, args.tokens, 5, H)
+            ops.qkv_rope(a, W, bias, sin, cos, args.tokens, args.prefix, H, half_tables=not args.general_tables)
         elif args.kind in ("proj", "fc2"):
             ops.gemm_res(a, W, bias, gamma, res[i % 2], out=res[i % 2])
         elif args.kind == "fc1":
@@ -200,6 +201,8 @@ def main():
     ap.add_argument("--cold", type=int, default=1)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     ap.add_argument("--quant-out", action="store_true", help="attn: fused quantisation of the output in --fmt")
+    ap.add_argument("--prefix", type=int, default=5, help="gemm qkv: tokens per image that are not rotated")
+    ap.add_argument("--general-tables", action="store_true", help="gemm qkv: rotary tables without the repeated-half promise (the slower general path)")
     args = ap.parse_args()
     torch.set_grad_enabled(False)
     fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak, "fill": bench_fill}[args.what]

@@ -211,7 +211,7 @@ MXW = QWeight
 
 def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
           out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block", pre_round=False,
-          fast_nv4=False, y_dbg=None):
+          fast_nv4=False, y_dbg=None, rope_half=False):
     p = GemmParams()
     if isinstance(a, ActBuf):
         if a.fmt != W.fmt or a.K != W.K:
@@ -228,7 +228,7 @@ def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin
     p.W, p.SFW, p.ts_w = W.q.data_ptr(), _ptr(W.sf), _ptr(W.ts)
     p.out_dtype = _DT[out_dtype]
     p.flags = (KF_G_GELU if gelu else 0) | (KF_Q_ROUND_BF16 if round_bf16 else 0) | (KF_Q_RECIP_DIV if recip_div else 0) \
-        | (_lib.KF_G_PRE_ROUND_BF16 if pre_round else 0) | (_lib.KF_Q_FAST_NV4 if fast_nv4 else 0)
+        | (_lib.KF_G_PRE_ROUND_BF16 if pre_round else 0) | (_lib.KF_Q_FAST_NV4 if fast_nv4 else 0) | (_lib.KF_G_ROPE_HALF if rope_half else 0)
     p.Ntok, p.prefix, p.H = Ntok, prefix, H
     _need_cuda(bias, gamma, R, C, sin, cos, y_dbg)
     p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
@@ -269,8 +269,15 @@ def gemm_res(a, W: QWeight, bias, gamma, res: torch.Tensor, out: Optional[torch.
     return out
 
 
-def qkv_rope(a, W: QWeight, bias, sin, cos, Ntok: int, prefix: int, H: int, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """a [M=B*Ntok, d] -> physical [3, B, Ntok, H, 64] (bias + RoPE in fp32 on q and k of tokens >= prefix)."""
+def rope_tables_are_half(sin: torch.Tensor, cos: torch.Tensor) -> bool:
+    """True when columns 32..63 of both tables repeat columns 0..31 (the axial tables of DINOv3: the angle vector concatenated
+    with itself).  A host-side check (it synchronises): call it once when the tables are built, not per launch."""
+    return bool(torch.equal(sin[:, :32], sin[:, 32:]) and torch.equal(cos[:, :32], cos[:, 32:]))
+
+
+def qkv_rope(a, W: QWeight, bias, sin, cos, Ntok: int, prefix: int, H: int, out_dtype=torch.bfloat16, half_tables: bool = False) -> torch.Tensor:
+    """a [M=B*Ntok, d] -> physical [3, B, Ntok, H, 64] (bias + RoPE in fp32 on q and k of tokens >= prefix).
+    half_tables=True promises rope_tables_are_half(sin, cos): the kernel then keeps a tile's table rows in shared memory."""
     M = a.M if isinstance(a, ActBuf) else a.shape[0]
     _f32c(bias, W.N, "bias")
     if sin.dtype != torch.float32 or cos.dtype != torch.float32 or not sin.is_contiguous() or not cos.is_contiguous() \
@@ -279,7 +286,7 @@ def qkv_rope(a, W: QWeight, bias, sin, cos, Ntok: int, prefix: int, H: int, out_
     if M % Ntok:
         raise KfError("qkv_rope: M must be a multiple of Ntok")
     out = torch.empty(3, M // Ntok, Ntok, H, 64, dtype=out_dtype, device=W.q.device)
-    _gemm(a, W, "rope", bias=bias, sin=sin, cos=cos, C=out, out_dtype=out_dtype, Ntok=Ntok, prefix=prefix, H=H)
+    _gemm(a, W, "rope", bias=bias, sin=sin, cos=cos, C=out, out_dtype=out_dtype, Ntok=Ntok, prefix=prefix, H=H, rope_half=half_tables)
     return out
 
 

@@ -97,7 +97,7 @@ class Layer:
         self.ts_ln1, self.ts_o, self.ts_ln2, self.ts_g = (_site_ts(fmt, dev) for _ in range(4))
 
 
-def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, calib: Calib, *, round_bf16: bool, attn_dtype) -> torch.Tensor:
+def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, calib: Calib, *, round_bf16: bool, attn_dtype, half_tables: bool = False) -> torch.Tensor:
     """x fp32 [B, N, d] (updated in place) -> x."""
     B, N, d = x.shape
     M = B * N
@@ -107,7 +107,7 @@ def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, cali
     x2 = x.view(M, d)
     if fmt == "bf16":
         h = ops.ln_rows(x, L.ln1_w, L.ln1_b, L.ln1_eps, BF).view(M, d)
-        qkv = ops.qkv_rope(h, L.qkv, L.bqkv, sin, cos, N, prefix, heads, out_dtype=attn_dtype)
+        qkv = ops.qkv_rope(h, L.qkv, L.bqkv, sin, cos, N, prefix, heads, out_dtype=attn_dtype, half_tables=half_tables)
         o = ops.attn_fwd(qkv).view(M, d)
         ops.gemm_res(o if o.dtype == BF else o.to(BF), L.proj, L.bproj, L.g1, x2, out=x2)
         h = ops.ln_rows(x, L.ln2_w, L.ln2_b, L.ln2_eps, BF).view(M, d)
@@ -119,7 +119,7 @@ def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, cali
         set_ts(L.ts_ln1, ops.ln_rows(x, L.ln1_w, L.ln1_b, L.ln1_eps, BF))
     a = _with_ts(ops.act_buf(M, d, fmt, x.device, 0), L.ts_ln1)
     ops.ln_quant(x, L.ln1_w, L.ln1_b, L.ln1_eps, a, round_bf16=round_bf16)
-    qkv = ops.qkv_rope(a, L.qkv, L.bqkv, sin, cos, N, prefix, heads, out_dtype=attn_dtype)
+    qkv = ops.qkv_rope(a, L.qkv, L.bqkv, sin, cos, N, prefix, heads, out_dtype=attn_dtype, half_tables=half_tables)
     # ---- attention with its output quantised in the epilogue -> proj (gamma + residual, in place on the stream)
     if cal and nv4:
         set_ts(L.ts_o, ops.attn_fwd(qkv))
@@ -235,6 +235,7 @@ def make_model_fn(model, fmt: str, *, image_size: int = 640, round_bf16: bool = 
     with torch.no_grad():
         sin, cos = bb.rope_embed(H=grid[0], W=grid[1])
     sin, cos = sin.float().contiguous(), cos.float().contiguous()
+    half_tables = ops.rope_tables_are_half(sin, cos)       # checked once here, on the host
     queries = model.queries.weight.detach().float()
     first_joint = nb - model.num_joint_blocks
     pe = PatchEmbed(bb, round_bf16)
@@ -251,7 +252,7 @@ def make_model_fn(model, fmt: str, *, image_size: int = 640, round_bf16: bool = 
         for i in range(nb):
             if i == first_joint:
                 t = torch.cat((queries[None].expand(t.shape[0], -1, -1), t), dim=1).contiguous()
-            block_fwd(t, layers[i], sin, cos, t.shape[1] - P, heads, calib, round_bf16=round_bf16, attn_dtype=attn_dtype)
+            block_fwd(t, layers[i], sin, cos, t.shape[1] - P, heads, calib, round_bf16=round_bf16, attn_dtype=attn_dtype, half_tables=half_tables)
         out = head(t, grid)
         calib.on = False
         return out

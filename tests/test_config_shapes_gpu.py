@@ -146,8 +146,10 @@ def test_vitl_end_to_end_at_config_sizes(variant, side, batch, gamma):
     """ViT-L/16 + EoMT at full width and depth against the emulated model at the same format.
     gamma None: the upstream initialisation (LayerScale 1e-5, what the benchmark configurations use): cosine >= 0.9999.
     gamma 0.1: LayerScale raised to 0.1 in every block so that the blocks' quantisation errors reach the logits (the
-    upstream value hides them); the measured cosines are printed and gated at 0.999 (class) / 0.99 (mask): two
-    implementations of the same quantised network differ there by the code flips that accumulation order causes."""
+    upstream value hides them).  Class logits: cosine >= 0.999.  Mask logits of a random-init network are chaotic under
+    quantisation, so their bound is calibrated on the emulation itself: the GPU path may differ from the emulation by no
+    more than 3x what a one-bf16-ulp change of 1 % of the input pixels does to the emulation's own mask logits.  All
+    measured values are printed."""
     import copy
 
     from lightly_trian_quant_b200 import modeldef, ops, stack
@@ -164,11 +166,20 @@ def test_vitl_end_to_end_at_config_sizes(variant, side, batch, gamma):
     ops.check_device_error()
     g = side // 4
     assert ml.shape == (batch, 200, g, g) and torch.isfinite(ml.float()).all()
-    emu = mo.EmuModel(model, fmt, ts=_collect_ts(fn), attn_dtype=torch.float16 if "f16attn" in variant else BF)
-    ml_ref, cl_ref = emu(x.float())
+    attn_dtype = torch.float16 if "f16attn" in variant else BF
+    ts = _collect_ts(fn)
+    ml_ref, cl_ref = mo.EmuModel(model, fmt, ts=ts, attn_dtype=attn_dtype)(x.float())
     c_ml, c_cl = mo.cosine(ml.float().cpu(), ml_ref), mo.cosine(cl.float().cpu(), cl_ref)
-    print(f"{variant} {side}px batch {batch} LayerScale {gamma or 1e-5}: mask-logit cosine {c_ml:.6f}, class-logit cosine {c_cl:.6f}")
+    msg = f"{variant} {side}px batch {batch} LayerScale {gamma or 1e-5}: mask-logit cosine {c_ml:.6f}, class-logit cosine {c_cl:.6f}"
     if gamma is None:
+        print(msg)
         assert c_ml >= 0.9999 and c_cl >= 0.9999, (c_ml, c_cl)
-    else:
-        assert c_ml >= 0.99 and c_cl >= 0.999, (c_ml, c_cl)
+        return
+    xp = x.float().clone()
+    m = torch.rand(xp.shape, generator=torch.Generator().manual_seed(1)) < 0.01
+    xp[m] = (xp[m] * (1 + 2 ** -8)).to(BF).float()
+    ml_p, cl_p = mo.EmuModel(model, fmt, ts=ts, attn_dtype=attn_dtype)(xp)
+    sens_ml, sens_cl = 1.0 - mo.cosine(ml_p, ml_ref), 1.0 - mo.cosine(cl_p, cl_ref)
+    print(msg + f"; the emulation's own 1-cos under a one-ulp input change: mask {sens_ml:.2e}, class {sens_cl:.2e}")
+    assert c_cl >= 0.999, (c_cl, sens_cl)
+    assert 1.0 - c_ml <= max(3.0 * sens_ml, 1e-4), (c_ml, sens_ml)

@@ -135,6 +135,31 @@ def test_gemm_qkv_rope(fmt, out_dtype):
     assert go.rel_fro(out[2].float().cpu().numpy(), ref_v) < tol
 
 
+@pytest.mark.parametrize("fmt", ["nv4", "mx8"])
+def test_gemm_qkv_rope_half_tables_in_shared_memory(fmt):
+    """tables whose second half repeats the first (the DINOv3 axial tables): the kernel keeps a tile's table rows in shared
+    memory (KF_G_ROPE_HALF).  Same bits as the general path, on a shape where images end inside a 128-row tile, the prefix
+    rows are not rotated, the last tile is partial and the head count makes the last column tile 128 wide."""
+    ops = _ops()
+    B, Ntok, prefix, H = 3, 205, 9, (8 if fmt == "nv4" else 6)      # mx8, H = 6: N = 1152 ends with a 128-column tile
+    d = H * 64
+    M = B * Ntok
+    x, w = _mk_x(M, d, 31), _mk_w(3 * d, d, 32, std=0.05)
+    g = torch.Generator().manual_seed(33)
+    bias = torch.randn(3 * d, generator=g) * 0.1
+    ang = torch.rand(Ntok - prefix, 32, generator=g) * 6.28
+    sin, cos = torch.sin(torch.cat((ang, ang), 1)).contiguous(), torch.cos(torch.cat((ang, ang), 1)).contiguous()
+    assert ops.rope_tables_are_half(sin, cos)
+    a, W, ad, wd = _quant_pair(x, w, fmt)
+    ref_path = ops.qkv_rope(a, W, bias.cuda(), sin.cuda(), cos.cuda(), Ntok, prefix, H)
+    fast_path = ops.qkv_rope(a, W, bias.cuda(), sin.cuda(), cos.cuda(), Ntok, prefix, H, half_tables=True)
+    ops.check_device_error()
+    assert torch.equal(ref_path, fast_path)
+    y = go.matmul_ref(ad, wd) + bias.numpy().astype(np.float64)
+    err = go.rel_fro(fast_path.float().cpu().numpy(), go.epi_rope(y, sin.numpy(), cos.numpy(), Ntok, prefix, H))
+    assert err < 2e-3, err
+
+
 def _fc1_case(fmt, round_bf16, M=300, N=512, K=1024, **kw):
     """runs the fc1 epilogue (bias + GELU + quantise-out) with the debug export; returns everything the gates need."""
     ops = _ops()
@@ -185,6 +210,34 @@ def test_gemm_fc1_gelu_quant_out(fmt, round_bf16):
     assert not full[M:].any()
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+def test_gemm_fc1_quant_out_zero_and_huge_blocks(fmt):
+    """the byte gate on values the common route of the block quantiser does not see: column ranges whose GELU output is
+    exactly zero (bias -60: all-zero blocks, scale byte 0), ranges of ~1e4 (the NVFP4 block scale saturates at 448) and a
+    tiny per-tensor scale of the output."""
+    ops = _ops()
+    M, N, K = 140, 512, 512
+    x, w = _mk_x(M, K, 41), _mk_w(N, K, 42, std=0.03)
+    bias = torch.zeros(N)
+    bias[32:96] = -60.0
+    bias[200:232] = 1.0e4
+    bias[300:316] = -60.0
+    a, W, _, _ = _quant_pair(x, w, fmt)
+    out = ops.ActBuf(M, N, fmt, device="cuda")
+    tso = None
+    if fmt == "nv4":
+        tso = np.array([3.0e-3], dtype=np.float32)
+        out.ts.copy_(torch.from_numpy(tso))
+    y = torch.empty(M, N, device="cuda")
+    ops.gemm_gelu_q(a, W, bias.cuda(), out, round_bf16=True, y_dbg=y)
+    ops.check_device_error()
+    yn = y.cpu().numpy()
+    assert (yn[:, 32:96] == 0).all() and yn[:, 200:232].min() > 9e3
+    eq, es, _ = qo.quantize(yn, fmt, tso)
+    assert np.array_equal(out.q.cpu().numpy(), eq)
+    assert np.array_equal(out.sf.cpu().numpy(), qo.to_blocked(es).reshape(-1))
+
+
 def test_gemm_fc1_quant_out_fast_nv4_agreement():
     """the opt-in approximate-reciprocal nv4 path: agreement with the oracle on the exported values is measured, printed
     and gated at >= 99.9 % of codes per 64-column group (a localised error cannot hide in an average) and 100 % of the
@@ -224,43 +277,6 @@ def test_gemm_vitl_shapes_batch8(fmt, kind):
     ops.quant_rows(x[:128].cuda(), a1)
     y1 = ops.gemm_plain(a1, W, out_dtype=torch.float32)
     assert torch.equal(y1, y[:128])
-
-
-@pytest.mark.parametrize("fmt", ["nv4", "mx8", "mx4", "bf16"])
-def test_gemm_pair_kernel_is_bitwise_the_one_cta_kernel(fmt, monkeypatch):
-    """The CTA-pair kernel (cta_group::2, 256 x 256 tiles, KF_GEMM_PAIR=1) accumulates in the same K order and shares
-    the epilogues: PLAIN, RES and QUANT outputs must be bit-identical to the one-CTA kernel's, on a shape with an odd
-    number of row blocks (the follower of the last pair has no rows) and a 128-column tail tile."""
-    ops = _ops()
-    M, N, K = 600, 384, 1024
-    x, w = _mk_x(M, K, 21), _mk_w(N, K, 22, std=0.05)
-    a, W, _, _ = _quant_pair(x, w, fmt)
-    g = torch.Generator().manual_seed(23)
-    bias, gamma = (torch.randn(N, generator=g) * 0.1).cuda(), torch.rand(N, generator=g).cuda()
-    res = torch.randn(M, N, generator=g).cuda()
-
-    def run():
-        out = {"plain": ops.gemm_plain(a, W, bias, out_dtype=torch.bfloat16), "res": ops.gemm_res(a, W, bias, gamma, res.clone())}
-        if fmt != "bf16":
-            q = ops.ActBuf(M, N, fmt, device="cuda")
-            if fmt == "nv4":
-                q.ts.fill_(0.01)
-            ops.gemm_gelu_q(a, W, bias, q, round_bf16=True)
-            out["q"], out["sf"] = q.q.clone(), q.sf.clone()
-        ops.check_device_error()
-        return out
-
-    monkeypatch.setenv("KF_GEMM_PAIR", "0")
-    one = run()
-    monkeypatch.setenv("KF_GEMM_PAIR", "1")
-    two = run()
-    for k in one:
-        assert torch.equal(one[k], two[k]), k
-    # and against the oracle, so that both are not wrong together
-    ad = x.float().numpy() if fmt == "bf16" else go.dequant_operand(a.q.cpu().numpy(), a.sf.cpu().numpy(), a.ts.cpu().numpy() if a.ts is not None else None, fmt, M, K)
-    wd = w.float().numpy() if fmt == "bf16" else go.dequant_operand(W.q.cpu().numpy(), W.sf.cpu().numpy(), W.ts.cpu().numpy() if W.ts is not None else None, fmt, N, K)
-    ref = go.matmul_ref(ad, wd) + bias.cpu().numpy().astype(np.float64)
-    assert go.rel_fro(two["plain"].float().cpu().numpy(), ref) < 2e-3
 
 
 def test_rate_probes_run_and_report_work():

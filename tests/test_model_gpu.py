@@ -201,8 +201,12 @@ def test_block_teacher_forced(fmt):
 def test_block_teacher_forced_full_width(fmt, ntok, prefix):
     """The same gate at the ViT-L block's real size: d = 1024, 16 heads, MLP 4096, 1605 tokens (prefix 5) and 1805 tokens
     (200 queries + 5), two images, stress-style weights (LayerScale ~ U(0.5, 1.5), LN affine and biases random), an outlier
-    channel in the stream.  The block's update must agree with the emulated block within 1 % rel. Frobenius; the measured
-    value and its two halves (attention branch, MLP branch) are printed."""
+    channel in the stream.  The block's update must agree with the emulated block within 2 % rel. Frobenius; the measured
+    value (overall, prefix rows, patch rows) is printed.  Where the slack comes from: the emulation multiplies an fp32 P by
+    bf16 V, the kernel rounds P to bf16 (attention output off by 2.3e-3 rel. Frobenius, tests/test_attn_gpu.py); that moves
+    ~2.3e-3 / 2^-4 = 4 % of the MXFP8 codes of the proj operand by one step of 2^-4 relative, i.e. ~1 % of the attention
+    branch's update (the coarser 4-bit grids flip less often).  A wrong table row, bias slice or batch offset is an O(1)
+    error on the rows it touches and fails the bound by two orders of magnitude."""
     modeldef, ops, stack = _mods()
     cfg = modeldef.EoMTConfig(dim=1024, depth=1, heads=16, ffn=4096, num_queries=200, num_joint_blocks=1)
     model = modeldef.build_model(cfg, 3, "stress", "cpu")
@@ -224,7 +228,7 @@ def test_block_teacher_forced_full_width(fmt, ntok, prefix):
     err_pre, err_patch = go.rel_fro(upd[:, :prefix], upd_ref[:, :prefix]), go.rel_fro(upd[:, prefix:], upd_ref[:, prefix:])
     print(f"full-width block {fmt} Ntok={ntok}: update rel. Frobenius {err:.3e} (prefix rows {err_pre:.3e}, patch rows {err_patch:.3e}), "
           f"stream {go.rel_fro(xg.cpu().numpy(), ref.numpy()):.3e}")
-    assert err < 1e-2, err
+    assert err < 2e-2 and err_pre < 3e-2, (err, err_pre)
 
 
 def copy_to_cuda(module):

@@ -159,3 +159,18 @@ def test_recip_div_mode_same_mx_bytes():
         a = _run_quant(x, fmt)
         b = _run_quant(x, fmt, recip_div=True)
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+def test_fast_reciprocal_is_correctly_rounded_for_every_significand():
+    """the three-instruction reciprocal the NVFP4 quantisers divide by (approximate reciprocal + one Newton step) equals
+    __frcp_rn for all 2^23 - 1 significands (all ones excluded by contract), both signs, at several exponents of its range."""
+    import ctypes as C
+
+    from lightly_trian_quant_b200 import _lib, ops
+
+    cnt = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for e in (-59, -17, -1, 0, 1, 23, 59):
+        _lib.check(_lib.lib().kf_selftest_rcp(e, C.c_void_p(cnt.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)), "kf_selftest_rcp")
+    torch.cuda.synchronize()
+    ops.check_device_error()
+    assert int(cnt.item()) == 0, f"{int(cnt.item())} significands differ from __frcp_rn"
