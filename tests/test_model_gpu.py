@@ -196,17 +196,22 @@ def test_block_teacher_forced(fmt):
     assert go.rel_fro(xg.cpu().numpy(), ref.numpy()) < 1e-2
 
 
-@pytest.mark.parametrize("fmt", ["mx8", "nv4", "mx4"])
+FULL_WIDTH_BOUND = {"bf16": 1e-2, "mx8": 2e-2, "nv4": 6e-2, "mx4": 8e-2}
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "mx8", "nv4", "mx4"])
 @pytest.mark.parametrize("ntok,prefix", [(1605, 5), (1805, 205)])
 def test_block_teacher_forced_full_width(fmt, ntok, prefix):
     """The same gate at the ViT-L block's real size: d = 1024, 16 heads, MLP 4096, 1605 tokens (prefix 5) and 1805 tokens
     (200 queries + 5), two images, stress-style weights (LayerScale ~ U(0.5, 1.5), LN affine and biases random), an outlier
-    channel in the stream.  The block's update must agree with the emulated block within 2 % rel. Frobenius; the measured
-    value (overall, prefix rows, patch rows) is printed.  Where the slack comes from: the emulation multiplies an fp32 P by
-    bf16 V, the kernel rounds P to bf16 (attention output off by 2.3e-3 rel. Frobenius, tests/test_attn_gpu.py); that moves
-    ~2.3e-3 / 2^-4 = 4 % of the MXFP8 codes of the proj operand by one step of 2^-4 relative, i.e. ~1 % of the attention
-    branch's update (the coarser 4-bit grids flip less often).  A wrong table row, bias slice or batch offset is an O(1)
-    error on the rows it touches and fails the bound by two orders of magnitude."""
+    channel in the stream.  The block's update (out - in) is compared with the emulated block's; the measured rel. Frobenius
+    error (overall, prefix rows, patch rows) is printed.
+    Bounds and where they come from.  Unquantised operands ("bf16"): 1 % (the emulation multiplies an fp32 P by V, the kernel
+    rounds P to bf16: attention output off by 2.3e-3, tests/test_attn_gpu.py).  Quantised formats: the same 2.3e-3
+    perturbation of the attention output flips codes of the proj operand; a flip is a whole grid step s (relative: 2^-4 for
+    e4m3, ~0.3 for e2m1) and happens with probability ~ delta / s, so the flip noise is sqrt(delta * s) of the operand:
+    1.2e-2 (mx8), 2.6e-2 (nv4 / mx4, before the second quantised GEMM adds its own): bounds of about twice that.  A wrong
+    table row, bias slice, head or batch offset is an O(1) error on the rows it touches and fails every one of them."""
     modeldef, ops, stack = _mods()
     cfg = modeldef.EoMTConfig(dim=1024, depth=1, heads=16, ffn=4096, num_queries=200, num_joint_blocks=1)
     model = modeldef.build_model(cfg, 3, "stress", "cpu")
@@ -219,7 +224,8 @@ def test_block_teacher_forced_full_width(fmt, ntok, prefix):
     sin, cos = model.backbone.rope_embed(H=gh, W=gh)
     L = stack.Layer(copy_to_cuda(blk), fmt)
     xg = x.cuda().clone()
-    stack.block_fwd(xg, L, sin.cuda().contiguous(), cos.cuda().contiguous(), prefix, cfg.heads, stack.Calib(), round_bf16=True, attn_dtype=BF)
+    stack.block_fwd(xg, L, sin.cuda().contiguous(), cos.cuda().contiguous(), prefix, cfg.heads, stack.Calib(), round_bf16=True, attn_dtype=BF,
+                    half_tables=ops.rope_tables_are_half(sin, cos))
     ops.check_device_error()
     ts = {(0, s): getattr(L, "ts_" + s).cpu().numpy() for s in ("ln1", "o", "ln2", "g") if getattr(L, "ts_" + s) is not None}
     ref = mo.EmuModel(model, fmt, ts=ts).block(0, blk, x, sin, cos, prefix)
@@ -228,7 +234,7 @@ def test_block_teacher_forced_full_width(fmt, ntok, prefix):
     err_pre, err_patch = go.rel_fro(upd[:, :prefix], upd_ref[:, :prefix]), go.rel_fro(upd[:, prefix:], upd_ref[:, prefix:])
     print(f"full-width block {fmt} Ntok={ntok}: update rel. Frobenius {err:.3e} (prefix rows {err_pre:.3e}, patch rows {err_patch:.3e}), "
           f"stream {go.rel_fro(xg.cpu().numpy(), ref.numpy()):.3e}")
-    assert err < 2e-2 and err_pre < 3e-2, (err, err_pre)
+    assert err < FULL_WIDTH_BOUND[fmt] and err_pre < 1.5 * FULL_WIDTH_BOUND[fmt], (err, err_pre)
 
 
 def copy_to_cuda(module):
