@@ -121,8 +121,9 @@ typedef struct kf_gemm_params {
   void* Qo;           /* QUANT: output codes [M, N] (mx8) or [M, N/2]                                          */
   void* SFo;          /* QUANT: output blocked scales of an [M, N] operand                                     */
   const float* tso;   /* QUANT to nv4: static per-tensor scale of the output                                   */
-  /* PLAIN only: output row of GEMM row m is (m / group) * stride + offset + m % group; group 0 = identity.
-   * Lets the patch-embed GEMM write straight into the token stream behind each image's cls / register rows. */
+  /* PLAIN and RES: output row of GEMM row m is (m / group) * stride + offset + m % group; group 0 = identity.
+   * Lets the patch-embed GEMM write straight into the token stream behind each image's cls / register rows, and the last
+   * fc2 before the queries join write the stream (read from R, row m) into the longer stream behind each image's query rows. */
   int out_row_group, out_row_stride, out_row_offset;
   /* QUANT only, optional (NULL = off): fp32 [M, N] that receives the values the epilogue quantised, i.e.
    * gelu(acc*ts + bias) after the optional bf16 rounding.  For parity tests: the written codes and scales are the bit
@@ -139,10 +140,19 @@ typedef struct kf_gemm_params {
 KF_API int kf_gemm_bs(const kf_gemm_params* p, void* stream);
 
 /* Final LayerNorm of the fp32 token stream x [B, Ntok, d] with the row gather of the EoMT head: query rows
- * (t < Q) -> qb bf16 [B*Q, d], patch rows (t >= Q + npre) -> xb bf16 [B*(Ntok-Q-npre), d].
- * Replaces the LN + gather part of tail_ln (infer-opt/round11_attn_tier0/impl/head_ext11.cu:252-320). */
-KF_API int kf_ln_tail(const float* x, const float* w, const float* b, float eps, int B, int Ntok, int Q, int npre, int d,
-                      void* qb, void* xb, void* stream);
+ * (t < Q) -> qb bf16 [B*Q, d], patch rows (t >= Q + npre) -> xb bf16 [B*(Ntok-Q-npre), d].  With wcls (bf16 [ncls1, d],
+ * optional) the class head runs on the query rows in the same pass: cl bf16 [B*Q, ncls1] = bf16(qb * wcls^T + bcls),
+ * fp32 accumulation, bcls fp32 [ncls1].
+ * Replaces tail_ln = LN + gather + class head in one kernel (infer-opt/round11_attn_tier0/impl/head_ext11.cu:252-320). */
+KF_API int kf_ln_tail(const float* x, const float* w, const float* b, float eps, int B, int Ntok, int Q, int npre, int d, void* qb,
+                      void* xb, const void* wcls, const float* bcls, int ncls1, void* cl, void* stream);
+
+/* Writes the same R fp32 rows into every image of a token stream: dst[b][row_offset + r][:] = src[r][:], b < B, with
+ * img_stride values between images.  The query rows joining the stream before the last blocks and the cls / register rows
+ * in front of the patch tokens.
+ * Replaces the torch.cat calls of the reference's token assembly (infer-opt/round13_mxfp8_full/impl/stack13.py:169-172;
+ * src/lightly_train/_models/dinov3/dinov3_src/models/vision_transformer.py:244-251). */
+KF_API int kf_broadcast_rows(const float* src, float* dst, int R, int d, int B, int64_t img_stride, int64_t row_offset, void* stream);
 
 /* Patch gathering for the patch-embed GEMM: x bf16 [B, 3, S, S] -> bf16 [B*(S/16)^2, 768], k = c*256 + py*16 + px.
  * Replaces the implicit im2col of patch_gemm_kernel (infer-opt/round11_attn_tier0/impl/patch_embed.cu:76-194). */

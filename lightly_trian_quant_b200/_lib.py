@@ -67,7 +67,8 @@ def lib() -> C.CDLL:
             "kf_fill_rate_probe": [vp, C.c_int64, i32, i32, C.POINTER(C.c_double), vp],
             "kf_selftest_rcp": [i32, vp, vp],
             "kf_attn_fwd_quant": [i32, vp, i32, i32, i32, f32, i32, vp, vp, vp, i32, vp],
-            "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp],
+            "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
+            "kf_broadcast_rows": [vp, vp, i32, i32, i32, i64, i64, vp],
             "kf_im2col_patch16": [vp, vp, i32, i32, vp],
             "kf_dw_ln": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, vp],
             "kf_semantic": [vp, vp, i32, i32, i32, i32, vp, vp, vp],

@@ -358,6 +358,9 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
     KF_REQUIRE(p->out_dtype == KF_F32 || p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: bad out_dtype %d", p->out_dtype);
   } else if (epi == KF_EPI_RES) {
     KF_REQUIRE(p->C && p->R && p->gamma && al32(p->C) && al32(p->R) && al16(p->gamma), "kf_gemm_bs: RES needs 32-byte aligned C and R and a 16-byte aligned gamma");
+    KF_REQUIRE(p->out_row_group >= 0 && (p->out_row_group == 0 || (p->out_row_stride >= p->out_row_group && p->out_row_offset >= 0)),
+               "kf_gemm_bs: bad output row mapping group=%d stride=%d offset=%d", p->out_row_group, p->out_row_stride, p->out_row_offset);
+    KF_REQUIRE(p->out_row_group == 0 || p->C != p->R, "kf_gemm_bs: RES with an output row mapping cannot run in place");
   } else if (epi == KF_EPI_ROPE) {
     KF_REQUIRE(p->C && al32(p->C) && p->sin && p->cos && al32(p->sin) && al32(p->cos), "kf_gemm_bs: ROPE needs 32-byte aligned C, sin and cos");
     KF_REQUIRE(p->out_dtype == KF_BF16 || p->out_dtype == KF_F16, "kf_gemm_bs: ROPE output must be bf16 or f16");
@@ -385,7 +388,8 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
   g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = (p->N + BN - 1) / BN; g.k_tiles = (int)(kbytes / BKB);
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
-  g.row_group = p->out_row_group; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
+  const bool maps_rows = epi == KF_EPI_PLAIN || epi == KF_EPI_RES;
+  g.row_group = maps_rows ? p->out_row_group : 0; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
   g.y_dbg = epi == KF_EPI_QUANT ? p->y_dbg : nullptr;
   g.err = dev_error_ptr();
   KF_REQUIRE(g.err != nullptr, "kf_gemm_bs: device error word unavailable");

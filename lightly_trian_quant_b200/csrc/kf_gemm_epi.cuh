@@ -37,7 +37,7 @@ struct GemmArgs {
   int Ntok, prefix, H, d;
   int out_dtype, flags, out_fmt;
   int m_tiles, n_tiles, k_tiles, nkb4;
-  int row_group, row_stride, row_offset;   // PLAIN: output row = (m / group) * stride + offset + m % group (group 0: identity)
+  int row_group, row_stride, row_offset;   // PLAIN, RES: output row = (m / group) * stride + offset + m % group (group 0: identity)
   float* y_dbg;                            // QUANT: optional export of the values that were quantised (fp32 [M, N])
   unsigned int* err;
 };
@@ -309,7 +309,8 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     // four residual loads in flight ahead of the arithmetic.
     if (m >= g.M) return;
     const float* rrow = g.R + (size_t)m * g.N + n0;
-    float* crow = static_cast<float*>(g.C) + (size_t)m * g.N + n0;
+    const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;   // the output may be a longer stream
+    float* crow = static_cast<float*>(g.C) + (size_t)orow * g.N + n0;
     const float2 ts2 = splat2(ts);
     F8 rr[4];
 #pragma unroll

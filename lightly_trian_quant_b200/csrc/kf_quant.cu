@@ -406,7 +406,9 @@ __global__ void __launch_bounds__(128) ln_rows_kernel(const float* __restrict__ 
 // rows in between are skipped.
 template <int NV>
 __global__ void __launch_bounds__(128) ln_tail_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float eps,
-                                                      int M, int Ntok, int Q, int npre, __nv_bfloat16* __restrict__ qb, __nv_bfloat16* __restrict__ xb) {
+                                                      int M, int Ntok, int Q, int npre, __nv_bfloat16* __restrict__ qb, __nv_bfloat16* __restrict__ xb,
+                                                      const __nv_bfloat16* __restrict__ wcls, const float* __restrict__ bcls, int ncls1,
+                                                      __nv_bfloat16* __restrict__ cl) {
   constexpr int D = NV * 256;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -425,8 +427,42 @@ __global__ void __launch_bounds__(128) ln_tail_kernel(const float* __restrict__ 
     for (int j = 0; j < 4; ++j) {
       __nv_bfloat162 h = __floats2bfloat162_rn(v[i][2 * j], v[i][2 * j + 1]);
       o[j] = *reinterpret_cast<uint32_t*>(&h);
+      const float2 r = __bfloat1622float2(h);          // the class head sees the bf16 values that were stored
+      v[i][2 * j] = r.x;
+      v[i][2 * j + 1] = r.y;
     }
     *reinterpret_cast<uint4*>(y + i * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  // class head on the query rows: logits[c] = bf16(sum_k q[k] * W[c][k] + bias[c]), fp32 accumulation
+  if (wcls != nullptr && t < Q) {
+    for (int c = 0; c < ncls1; ++c) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const uint4 wq = __ldg(reinterpret_cast<const uint4*>(wcls + (int64_t)c * D + i * 256 + lane * 8));
+        const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[j]));
+          acc = fmaf(v[i][2 * j], f.x, acc);
+          acc = fmaf(v[i][2 * j + 1], f.y, acc);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) cl[((int64_t)img * Q + t) * ncls1 + c] = __float2bfloat16_rn(acc + bcls[c]);
+    }
+  }
+}
+
+// Copies a block of fp32 rows into every image of a token stream: dst[b, row_offset + r, :] = src[r, :] for r < R.
+// The query rows that join the stream for the last blocks and the cls / register rows in front of the patch tokens.
+__global__ void __launch_bounds__(256) broadcast_rows_kernel(const float4* __restrict__ src, float4* __restrict__ dst, int R, int d4, int B, int64_t img_stride4,
+                                                             int64_t row_offset4) {
+  const int64_t n = (int64_t)R * d4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n * B; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t bimg = i / n, e = i - bimg * n;
+    dst[bimg * img_stride4 + row_offset4 + e] = __ldg(src + e);
   }
 }
 
@@ -450,23 +486,31 @@ template <int NV>
 static int launch_ln_quant(int fmt, const float* x, const float* w, const float* b, float eps, int M, const float* ts, int flags, void* q, void* sf,
                            float* y_dbg, cudaStream_t st) {
   int rows_pad = (M + 127) / 128 * 128;
-  int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  int sms = 0;
+  int rc = device_sm_count(&sms);                        // of the CURRENT device
+  if (rc != KF_OK) return rc;
+  int dev = 0;
+  cudaGetDevice(&dev);
   unsigned grid = (unsigned)((rows_pad + 3) / 4);
   uint8_t *qp = static_cast<uint8_t*>(q), *sp = static_cast<uint8_t*>(sf);
   unsigned int* err = dev_error_ptr();
   KF_REQUIRE(err != nullptr, "kf_ln_quant: device error word unavailable");
   const size_t smem = (size_t)4 * LNQ_RING * NV * 256 * 4 + 4 * LNQ_RING * 8 + 16;
+  static int per_sm_cached[3][64] = {};                  // per (format, device) of this row width
   auto go = [&](auto kern) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_quant_kernel)");
     // persistent: as many CTAs of 4 warps as are resident at once (4 per SM up to d = 1024, fewer for wider rows); a
-    // grid beyond that would run its surplus as a second, nearly empty wave
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem);
-    if (e != cudaSuccess) return cuda_status(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(ln_quant_kernel)");
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 4) per_sm = 4;
+    // grid beyond that would run its surplus as a second, nearly empty wave.  The attribute and the occupancy query are
+    // per (kernel instance, device): worked out at the first call and kept.
+    int per_sm = dev < 64 ? per_sm_cached[fmt][dev] : 0;
+    if (per_sm == 0) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(ln_quant_kernel)");
+      e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem);
+      if (e != cudaSuccess) return cuda_status(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(ln_quant_kernel)");
+      if (per_sm < 1) per_sm = 1;
+      if (per_sm > 4) per_sm = 4;
+      if (dev < 64) per_sm_cached[fmt][dev] = per_sm;
+    }
     if (grid > (unsigned)(sms * per_sm)) grid = (unsigned)(sms * per_sm);
     return cuda_status(launch_maybe_pdl(kern, dim3(grid), dim3(128), smem, st, x, w, b, eps, M, rows_pad, ts, flags, qp, sp, y_dbg, err), "kf_ln_quant launch");
   };
@@ -484,8 +528,10 @@ static int launch_ln_rows(const float* x, const float* w, const float* b, float 
 }
 
 template <int NV>
-static int launch_ln_tail(const float* x, const float* w, const float* b, float eps, int M, int Ntok, int Q, int npre, void* qb, void* xb, cudaStream_t st) {
-  ln_tail_kernel<NV><<<(unsigned)((M + 3) / 4), 128, 0, st>>>(x, w, b, eps, M, Ntok, Q, npre, static_cast<__nv_bfloat16*>(qb), static_cast<__nv_bfloat16*>(xb));
+static int launch_ln_tail(const float* x, const float* w, const float* b, float eps, int M, int Ntok, int Q, int npre, void* qb, void* xb, const void* wcls,
+                          const float* bcls, int ncls1, void* cl, cudaStream_t st) {
+  ln_tail_kernel<NV><<<(unsigned)((M + 3) / 4), 128, 0, st>>>(x, w, b, eps, M, Ntok, Q, npre, static_cast<__nv_bfloat16*>(qb), static_cast<__nv_bfloat16*>(xb),
+                                                              static_cast<const __nv_bfloat16*>(wcls), bcls, ncls1, static_cast<__nv_bfloat16*>(cl));
   return cuda_status(cudaGetLastError(), "kf_ln_tail launch");
 }
 
@@ -553,22 +599,37 @@ extern "C" int kf_ln_rows(const float* x, const float* w, const float* b, float 
 }
 
 extern "C" int kf_ln_tail(const float* x, const float* w, const float* b, float eps, int B, int Ntok, int Q, int npre, int d, void* qb, void* xb,
-                          void* stream) {
+                          const void* wcls, const float* bcls, int ncls1, void* cl, void* stream) {
   KF_REQUIRE(B >= 0 && Ntok > 0 && Q >= 0 && npre >= 0 && Q + npre <= Ntok, "kf_ln_tail: bad token counts Ntok=%d Q=%d npre=%d", Ntok, Q, npre);
   KF_REQUIRE(d > 0 && d % 256 == 0 && d <= 2048, "kf_ln_tail: d=%d must be a multiple of 256 up to 2048", d);
   if (B == 0) return KF_OK;
   KF_REQUIRE(x && w && b && xb && (qb || Q == 0), "kf_ln_tail: null tensor pointer");
   KF_REQUIRE(aligned16(x) && aligned16(w) && aligned16(b) && aligned16(qb) && aligned16(xb), "kf_ln_tail: tensors must be 16-byte aligned");
+  KF_REQUIRE(wcls == nullptr || (bcls && cl && ncls1 > 0 && ncls1 <= 64 && aligned16(wcls)), "kf_ln_tail: the class head needs wcls (16-byte aligned), bcls, cl and 1..64 logits");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int M = B * Ntok;
   switch (d / 256) {
-    case 1: return launch_ln_tail<1>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 2: return launch_ln_tail<2>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 3: return launch_ln_tail<3>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 4: return launch_ln_tail<4>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 5: return launch_ln_tail<5>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 6: return launch_ln_tail<6>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    case 7: return launch_ln_tail<7>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
-    default: return launch_ln_tail<8>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, st);
+    case 1: return launch_ln_tail<1>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 2: return launch_ln_tail<2>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 3: return launch_ln_tail<3>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 4: return launch_ln_tail<4>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 5: return launch_ln_tail<5>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 6: return launch_ln_tail<6>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    case 7: return launch_ln_tail<7>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
+    default: return launch_ln_tail<8>(x, w, b, eps, M, Ntok, Q, npre, qb, xb, wcls, bcls, ncls1, cl, st);
   }
+}
+
+extern "C" int kf_broadcast_rows(const float* src, float* dst, int R, int d, int B, int64_t img_stride, int64_t row_offset, void* stream) {
+  KF_REQUIRE(R >= 0 && B >= 0 && d > 0 && d % 4 == 0, "kf_broadcast_rows: d=%d must be a positive multiple of 4", d);
+  KF_REQUIRE(img_stride % 4 == 0 && row_offset >= 0 && row_offset + (int64_t)R <= img_stride / d, "kf_broadcast_rows: rows %lld..%lld do not fit an image of %lld values",
+             (long long)row_offset, (long long)(row_offset + R), (long long)img_stride);
+  if (R == 0 || B == 0) return KF_OK;
+  KF_REQUIRE(src && dst && aligned16(src) && aligned16(dst), "kf_broadcast_rows: tensors must be non-null and 16-byte aligned");
+  const int64_t n = (int64_t)R * (d / 4) * B;
+  int grid = (int)((n + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  broadcast_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst), R, d / 4, B, img_stride / 4,
+                                                                            row_offset * (d / 4));
+  return cuda_status(cudaGetLastError(), "kf_broadcast_rows launch");
 }

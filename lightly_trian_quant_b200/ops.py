@@ -211,7 +211,7 @@ MXW = QWeight
 
 def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin=None, cos=None, out: Optional[ActBuf] = None,
           out_dtype=torch.bfloat16, gelu=False, round_bf16=False, recip_div=False, Ntok=0, prefix=0, H=0, tag="block", pre_round=False,
-          fast_nv4=False, y_dbg=None, rope_half=False):
+          fast_nv4=False, y_dbg=None, rope_half=False, row_map=None):
     p = GemmParams()
     if isinstance(a, ActBuf):
         if a.fmt != W.fmt or a.K != W.K:
@@ -233,6 +233,8 @@ def _gemm(a, W: QWeight, epi: str, *, bias=None, gamma=None, R=None, C=None, sin
     _need_cuda(bias, gamma, R, C, sin, cos, y_dbg)
     p.bias, p.gamma, p.R, p.sin, p.cos, p.C = _ptr(bias), _ptr(gamma), _ptr(R), _ptr(sin), _ptr(cos), _ptr(C)
     p.y_dbg = _ptr(y_dbg)
+    if row_map is not None:
+        p.out_row_group, p.out_row_stride, p.out_row_offset = row_map
     if out is not None:
         p.out_fmt, p.Qo, p.SFo, p.tso = KF_FMT[out.fmt], out.q.data_ptr(), out.sf.data_ptr(), _ptr(out.ts)
     _run(f"gemm_{tag}_{W.fmt}", lambda: _lib.lib().kf_gemm_bs(p, _stream()))
@@ -257,16 +259,36 @@ def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.
 mm = gemm_plain
 
 
-def gemm_res(a, W: QWeight, bias, gamma, res: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """fp32 [M, N] = res + gamma * (a @ W^T (* ts) + bias)   (proj / fc2; gemm_res, fwd_res)."""
+def gemm_res(a, W: QWeight, bias, gamma, res: torch.Tensor, out: Optional[torch.Tensor] = None, row_map=None) -> torch.Tensor:
+    """fp32 [M, N] = res + gamma * (a @ W^T (* ts) + bias)   (proj / fc2; gemm_res, fwd_res).
+    row_map = (group, stride, offset): row m of the result goes to row (m // group) * stride + offset + m % group of `out`
+    (a longer token stream: the rows of each image land behind `offset` rows that are filled separately); not in place."""
     M = a.M if isinstance(a, ActBuf) else a.shape[0]
     _f32c(bias, W.N, "bias")
     _f32c(gamma, W.N, "gamma")
     _f32c(res, M * W.N, "res")
     if out is None:
+        if row_map is not None:
+            raise KfError("gemm_res: a row mapping needs the output tensor")
         out = torch.empty_like(res)
-    _gemm(a, W, "res", bias=bias, gamma=gamma, R=res, C=out, out_dtype=torch.float32)
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KfError("gemm_res: out must be contiguous fp32")
+    if row_map is not None:
+        group, stride, offset = row_map
+        if M % group or out.numel() != (M // group) * stride * W.N or offset + group > stride:
+            raise KfError(f"gemm_res: row mapping {row_map} does not fit M={M} rows into {out.numel() // W.N} output rows")
+    _gemm(a, W, "res", bias=bias, gamma=gamma, R=res, C=out, out_dtype=torch.float32, row_map=row_map)
     return out
+
+
+def broadcast_rows(src: torch.Tensor, dst: torch.Tensor, row_offset: int) -> torch.Tensor:
+    """dst[b, row_offset : row_offset + R, :] = src [R, d] for every image b of the fp32 token stream dst [B, Ntok, d]."""
+    _need_cuda(src, dst)
+    if src.dtype != torch.float32 or dst.dtype != torch.float32 or not src.is_contiguous() or not dst.is_contiguous() or dst.dim() != 3 or src.shape[-1] != dst.shape[2]:
+        raise KfError("broadcast_rows: src [R, d] and dst [B, Ntok, d] must be contiguous fp32")
+    R = src.numel() // dst.shape[2]
+    _run("broadcast_rows", lambda: _lib.lib().kf_broadcast_rows(src.data_ptr(), dst.data_ptr(), R, dst.shape[2], dst.shape[0], dst.shape[1] * dst.shape[2], row_offset, _stream()))
+    return dst
 
 
 def rope_tables_are_half(sin: torch.Tensor, cos: torch.Tensor) -> bool:
@@ -363,17 +385,24 @@ def im2col_patch16(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def ln_tail(x: torch.Tensor, w, b, eps: float, Q: int, npre: int):
-    """final LayerNorm + gather: x fp32 [B, Ntok, d] -> (queries bf16 [B*Q, d], patches bf16 [B*(Ntok-Q-npre), d])."""
-    _need_cuda(x, w, b)
+def ln_tail(x: torch.Tensor, w, b, eps: float, Q: int, npre: int, wcls: Optional[torch.Tensor] = None, bcls: Optional[torch.Tensor] = None):
+    """final LayerNorm + gather: x fp32 [B, Ntok, d] -> (queries bf16 [B*Q, d], patches bf16 [B*(Ntok-Q-npre), d]), and with
+    wcls bf16 [ncls1, d] / bcls fp32 [ncls1] the class logits bf16 [B*Q, ncls1] of the query rows as a third result."""
+    _need_cuda(x, w, b, wcls, bcls)
     B, Ntok, d = x.shape
     if x.dtype != torch.float32 or not x.is_contiguous():
         raise KfError("ln_tail: x must be contiguous fp32")
     qb = torch.empty(B * Q, d, dtype=torch.bfloat16, device=x.device)
     xb = torch.empty(B * (Ntok - Q - npre), d, dtype=torch.bfloat16, device=x.device)
+    cl, ncls1 = None, 0
+    if wcls is not None:
+        if wcls.dtype != torch.bfloat16 or not wcls.is_contiguous() or wcls.shape[1] != d or bcls is None or bcls.dtype != torch.float32 or bcls.numel() != wcls.shape[0]:
+            raise KfError("ln_tail: wcls must be contiguous bf16 [ncls1, d] and bcls fp32 [ncls1]")
+        ncls1 = wcls.shape[0]
+        cl = torch.empty(B * Q, ncls1, dtype=torch.bfloat16, device=x.device)
     _run("ln_tail", lambda: _lib.lib().kf_ln_tail(x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), B, Ntok, Q, npre, d, qb.data_ptr(), xb.data_ptr(),
-                                                  _stream()))
-    return qb, xb
+                                                  _ptr(wcls), _ptr(bcls), ncls1, _ptr(cl), _stream()))
+    return (qb, xb) if wcls is None else (qb, xb, cl)
 
 
 def dw_ln(g: torch.Tensor, bias, dww, lnw, lnb, B: int, Hs: int, Ws: int, eps: float, pre_act: bool = False) -> torch.Tensor:

@@ -97,8 +97,11 @@ class Layer:
         self.ts_ln1, self.ts_o, self.ts_ln2, self.ts_g = (_site_ts(fmt, dev) for _ in range(4))
 
 
-def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, calib: Calib, *, round_bf16: bool, attn_dtype, half_tables: bool = False) -> torch.Tensor:
-    """x fp32 [B, N, d] (updated in place) -> x."""
+def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, calib: Calib, *, round_bf16: bool, attn_dtype, half_tables: bool = False,
+              grow_into: torch.Tensor = None) -> torch.Tensor:
+    """x fp32 [B, N, d] (updated in place) -> x.  grow_into (fp32 [B, N + Q, d], optional): the block's result is written
+    behind the first Q rows of every image of this longer stream instead (the fc2 epilogue maps the rows), which is then
+    returned: how the query tokens join the stream without a copy of it."""
     B, N, d = x.shape
     M = B * N
     ff = L.fc1.N
@@ -112,8 +115,7 @@ def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, cali
         ops.gemm_res(o if o.dtype == BF else o.to(BF), L.proj, L.bproj, L.g1, x2, out=x2)
         h = ops.ln_rows(x, L.ln2_w, L.ln2_b, L.ln2_eps, BF).view(M, d)
         a = ops.gemm_plain(h, L.fc1, L.b1, gelu=True)
-        ops.gemm_res(a, L.fc2, L.b2, L.g2, x2, out=x2)
-        return x
+        return _fc2(a, L, x, x2, grow_into)
     # ---- LN1 + quant -> qkv (bias + RoPE + layout) -> attention
     if cal and nv4:
         set_ts(L.ts_ln1, ops.ln_rows(x, L.ln1_w, L.ln1_b, L.ln1_eps, BF))
@@ -135,8 +137,16 @@ def block_fwd(x: torch.Tensor, L: Layer, sin, cos, prefix: int, heads: int, cali
         set_ts(L.ts_g, ops.gemm_plain(a, L.fc1, L.b1, gelu=True))
     f = _with_ts(ops.act_buf(M, ff, fmt, x.device, 0), L.ts_g)
     ops.gemm_gelu_q(a, L.fc1, L.b1, f, round_bf16=round_bf16)
-    ops.gemm_res(f, L.fc2, L.b2, L.g2, x2, out=x2)
-    return x
+    return _fc2(f, L, x, x2, grow_into)
+
+
+def _fc2(f, L: Layer, x, x2, grow_into):
+    if grow_into is None:
+        ops.gemm_res(f, L.fc2, L.b2, L.g2, x2, out=x2)
+        return x
+    N, Nbig = x.shape[1], grow_into.shape[1]
+    ops.gemm_res(f, L.fc2, L.b2, L.g2, x2, out=grow_into, row_map=(N, Nbig, Nbig - N))
+    return grow_into
 
 
 # ------------------------------------------------------------------------------------------------ patch embed and head
@@ -159,7 +169,7 @@ class PatchEmbed:
         B, _, S, _ = x.shape
         P = (S // 16) ** 2
         t = torch.empty(B, self.npre + P, self.d, dtype=F32, device=x.device)
-        t[:, : self.npre] = self.prefix
+        ops.broadcast_rows(self.prefix, t, 0)
         ops.gemm_tokens(ops.im2col_patch16(x), self.W, self.bias, t, P, self.npre + P, self.npre, round_bf16=self.round_bf16)
         return t
 
@@ -179,11 +189,9 @@ class Head:
         self.C = C
         dev = bb.norm.weight.device
         ncls1 = model.class_head.out_features
-        wc = torch.zeros(128, C, dtype=BF, device=dev)
-        wc[:ncls1] = model.class_head.weight.detach().to(BF)
-        bc = torch.zeros(128, dtype=F32, device=dev)
-        bc[:ncls1] = model.class_head.bias.detach().to(BF).float()
-        self.ncls1, self.Wcls, self.bcls = ncls1, ops.QWeight(wc, "bf16"), bc
+        self.ncls1 = ncls1
+        self.Wcls = model.class_head.weight.detach().to(BF).contiguous()                 # the class head runs inside the final LayerNorm kernel
+        self.bcls = model.class_head.bias.detach().to(BF).float().contiguous()
         self.mh = [(ops.QWeight(m.weight.detach(), "bf16"), m.bias.detach().to(BF).float().contiguous())
                    for m in model.mask_head if isinstance(m, torch.nn.Linear)]
         self.stages = []
@@ -199,8 +207,8 @@ class Head:
     def __call__(self, t: torch.Tensor, grid):
         B, Ntok, C = t.shape
         Q, (Hs, Ws) = self.Q, grid
-        qb, xb = ops.ln_tail(t, self.ln_w, self.ln_b, self.ln_eps, Q, self.npre)
-        cl = ops.gemm_plain(qb, self.Wcls, self.bcls, tag="head")[:, : self.ncls1].reshape(B, Q, self.ncls1).contiguous()
+        qb, xb, cl = ops.ln_tail(t, self.ln_w, self.ln_b, self.ln_eps, Q, self.npre, self.Wcls, self.bcls)
+        cl = cl.view(B, Q, self.ncls1)
         z = xb
         for st in self.stages:
             if self.fmt == "bf16":
@@ -236,7 +244,8 @@ def make_model_fn(model, fmt: str, *, image_size: int = 640, round_bf16: bool = 
         sin, cos = bb.rope_embed(H=grid[0], W=grid[1])
     sin, cos = sin.float().contiguous(), cos.float().contiguous()
     half_tables = ops.rope_tables_are_half(sin, cos)       # checked once here, on the host
-    queries = model.queries.weight.detach().float()
+    queries = model.queries.weight.detach().float().contiguous()
+    Q = queries.shape[0]
     first_joint = nb - model.num_joint_blocks
     pe = PatchEmbed(bb, round_bf16)
     head = Head(model, head_fmt or fmt, calib)
@@ -250,9 +259,14 @@ def make_model_fn(model, fmt: str, *, image_size: int = 640, round_bf16: bool = 
             raise RuntimeError("the first call (static-scale calibration) must run eagerly, before CUDA graph capture")
         t = pe(x.contiguous())
         for i in range(nb):
-            if i == first_joint:
+            grow = None
+            if i + 1 == first_joint and first_joint < nb:     # the next block sees the queries: this block's fc2 writes the longer stream
+                grow = torch.empty(t.shape[0], Q + t.shape[1], t.shape[2], dtype=F32, device=t.device)
+                ops.broadcast_rows(queries, grow, 0)
+            elif i == first_joint == 0:                   # every block is a joint block: no fc2 in front to do the move
                 t = torch.cat((queries[None].expand(t.shape[0], -1, -1), t), dim=1).contiguous()
-            block_fwd(t, layers[i], sin, cos, t.shape[1] - P, heads, calib, round_bf16=round_bf16, attn_dtype=attn_dtype, half_tables=half_tables)
+            t = block_fwd(t, layers[i], sin, cos, t.shape[1] - P, heads, calib, round_bf16=round_bf16, attn_dtype=attn_dtype, half_tables=half_tables,
+                          grow_into=grow)
         out = head(t, grid)
         calib.on = False
         return out

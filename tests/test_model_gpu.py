@@ -52,6 +52,33 @@ def test_ln_tail_gather():
     assert (qb.float().cpu() - ref[:, :Q].reshape(-1, d).to(BF).float()).abs().max() < 0.05
     assert go.rel_fro(qb.float().cpu().numpy(), ref[:, :Q].reshape(-1, d).numpy()) < 4e-3
     assert go.rel_fro(xb.float().cpu().numpy(), ref[:, Q + npre:].reshape(-1, d).numpy()) < 4e-3
+    # with the class head fused in: logits of the stored bf16 query rows, same gathers
+    wc = (torch.randn(3, d, generator=g) * 0.05).to(BF)
+    bc = (torch.randn(3, generator=g) * 0.1).to(BF).float()
+    qb2, xb2, cl = ops.ln_tail(x.cuda(), w.cuda(), b.cuda(), 1e-5, Q, npre, wc.cuda(), bc.cuda())
+    assert torch.equal(qb2, qb) and torch.equal(xb2, xb) and cl.shape == (B * Q, 3)
+    cl_ref = qb.float().cpu() @ wc.float().t() + bc
+    assert go.rel_fro(cl.float().cpu().numpy(), cl_ref.numpy()) < 4e-3
+
+
+def test_broadcast_rows_and_residual_into_a_longer_stream():
+    """the query rows are written in front of every image and the fc2 epilogue moves the stream behind them (row mapping):
+    together they are torch.cat((queries, stream), dim=1) followed by the in-place residual GEMM."""
+    modeldef, ops, stack = _mods()
+    g = torch.Generator().manual_seed(12)
+    B, N, Q, d, K = 3, 37, 11, 256, 512
+    x = torch.randn(B, N, d, generator=g).cuda()
+    queries = torch.randn(Q, d, generator=g).cuda()
+    a = (torch.randn(B * N, K, generator=g)).to(BF).cuda()
+    W = ops.QWeight((torch.randn(d, K, generator=g) * 0.05).cuda(), "bf16")
+    bias, gamma = torch.randn(d, generator=g).cuda() * 0.1, torch.rand(d, generator=g).cuda()
+    inplace = ops.gemm_res(a, W, bias, gamma, x.view(B * N, d).clone())
+    big = torch.full((B, Q + N, d), float("nan"), device="cuda")
+    ops.broadcast_rows(queries, big, 0)
+    ops.gemm_res(a, W, bias, gamma, x.view(B * N, d), out=big, row_map=(N, Q + N, Q))
+    ops.check_device_error()
+    assert torch.equal(big[:, :Q], queries[None].expand(B, -1, -1))
+    assert torch.equal(big[:, Q:].reshape(B * N, d), inplace)
 
 
 @pytest.mark.parametrize("C", [256, 1024])
