@@ -8,8 +8,11 @@ replicated (random init, upstream recipe), no collective on the data path.  One 
 GPU through resize+normalise -> model_fn -> per-pixel labels.
 
   value  frames/s with the uint8 frames already resident in HBM (CUDA-graph replay of the step, CUDA events, max over ranks)
-  e2e    frames/s through the public pipeline with HOST frames: per step the pinned-host -> device copy of the B frames,
-         the step, and the device -> host copy of the label maps, double buffered on a copy stream
+  e2e    frames/s through the public pipeline (lightly_trian_quant_b200.pipeline.VideoPipeline) with HOST frames: per step the
+         pinned-host -> device copy of the B frames, the step, and the device -> host copy of the label maps, on separate
+         copy / compute streams over a ring of slots
+  video_126   wall-clock of THIS video: every rank runs its shard of the 126 frames once through VideoPipeline.run (the last
+         micro-batch padded), slowest rank counts: frames/s of the fixed job, i.e. strong scaling including batch padding
   roofline / kernels   per-kernel-class durations measured live with CUDA events in an instrumented eager pass over the
          same step; the dominant class (block-scaled GEMMs) is reported against the tcgen05 instruction-rate ceiling
          measured in the same run
@@ -100,6 +103,7 @@ def run_reference(args, rank: int):
     from oracle import model_oracle as mo
 
     torch.set_grad_enabled(False)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))      # rank 0 alone runs this arm (the other ranks exit): every host core
     fmt = args.variant.split("+")[0].split("_")[1]
     model = modeldef.build_model(modeldef.VIT_L, seed=0, mode="upstream", device="cpu")
     g = torch.Generator().manual_seed(0)
@@ -161,6 +165,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     torch.set_grad_enabled(False)
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))      # host threads are shared by the ranks of one box
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
@@ -190,23 +195,16 @@ def main():
     video = synth_video(N_FRAMES, dev)
     dev_batches = [video[idx].contiguous() for idx in batches]
     host_batches = [b.cpu().pin_memory() for b in dev_batches]
+    host_frames = {k: video[k].cpu() for k in shard}
     del video
 
-    # first call eager (static NVFP4 scales are calibrated on the first batch), then capture the step
-    labels = pipe(dev_batches[0])
+    # the public host pipeline: warm-up = eager calibration call (static NVFP4 scales from the first batch) + one graph per slot
+    from lightly_trian_quant_b200 import pipeline as host_pipeline
+
+    vp = host_pipeline.VideoPipeline(pipe, B, FRAME_H, FRAME_W, slots=3, inflight=2, device=dev)
+    vp.warmup(dev_batches[0])
     ops.check_device_error()
-    static_in = dev_batches[0].clone()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for _ in range(2):
-            pipe(static_in)
-    torch.cuda.current_stream().wait_stream(side)
-    ops.LAUNCHES = 0
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        static_out = pipe(static_in)
-    launches_per_step = ops.LAUNCHES
+    nslots = len(vp.slots)
 
     def barrier():
         torch.cuda.synchronize()
@@ -221,75 +219,76 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---------------------------------------------------------------- device-resident steps
+    # ---------------------------------------------------------------- device-resident steps (graph replay, inputs in HBM)
     def dev_step(i):
-        static_in.copy_(dev_batches[i % n_batches], non_blocking=True)     # device-to-device: a different batch every step
-        graph.replay()
+        slot = vp.slots[i % nslots]
+        slot.dev_in.copy_(dev_batches[i % n_batches], non_blocking=True)     # device-to-device: a different batch every step
+        slot.graph.replay()
 
-    for i in range(args.warmup):
-        dev_step(i)
+    with torch.cuda.stream(vp.comp):
+        for i in range(args.warmup):
+            dev_step(i)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        dev_step(args.warmup + i)
-    e1.record()
+    with torch.cuda.stream(vp.comp):
+        e0.record()
+        for i in range(args.steps):
+            dev_step(args.warmup + i)
+        e1.record()
     barrier()
     ms_total = reduce_max(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
     fps = sharding.aggregate_fps(B, world, args.steps, ms_total)
 
-    # ---------------------------------------------------------------- end to end with host frames (double buffered)
-    copy_s = torch.cuda.Stream()
-    in_bufs = [torch.empty_like(static_in) for _ in range(2)]
-    out_host = [torch.empty(static_out.shape, dtype=torch.uint8).pin_memory() for _ in range(2)]
-    comp = torch.cuda.current_stream()
-
+    # ---------------------------------------------------------------- end to end with host frames through VideoPipeline.submit
     def e2e_run(n_steps, start):
-        ev_in = [torch.cuda.Event() for _ in range(2)]
-        ev_free = [torch.cuda.Event() for _ in range(2)]
-        ev_out = [torch.cuda.Event() for _ in range(2)]
-        with torch.cuda.stream(copy_s):
-            in_bufs[0].copy_(host_batches[start % n_batches], non_blocking=True)
-            ev_in[0].record(copy_s)
         for i in range(n_steps):
-            k = i & 1
-            comp.wait_event(ev_in[k])
-            static_in.copy_(in_bufs[k], non_blocking=True)
-            ev_free[k].record(comp)
-            graph.replay()
-            ev_out[k].record(comp)
-            with torch.cuda.stream(copy_s):
-                if i + 1 < n_steps:
-                    if i >= 1:
-                        copy_s.wait_event(ev_free[k ^ 1])
-                    in_bufs[k ^ 1].copy_(host_batches[(start + i + 1) % n_batches], non_blocking=True)
-                    ev_in[k ^ 1].record(copy_s)
-                copy_s.wait_event(ev_out[k])
-                out_host[k].copy_(static_out, non_blocking=True)
-            comp.wait_stream(copy_s) if i + 1 == n_steps else None
+            vp.submit(i % nslots, src=host_batches[(start + i) % n_batches])
 
     e2e_run(args.warmup, 0)
     barrier()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
+    s0.record(vp.h2d)                                   # the first copy of the timed region is enqueued behind it
     e2e_run(args.steps, args.warmup)
-    s1.record()
+    vp.d2h.wait_stream(vp.comp)
+    s1.record(vp.d2h)                                   # behind the last device -> host copy
     barrier()
     e2e_ms = reduce_max(s0.elapsed_time(s1))
     e2e_fps = sharding.aggregate_fps(B, world, args.steps, e2e_ms)
-    h2d, d2h = static_in.numel(), static_out.numel()
+    h2d, d2h = vp.slots[0].dev_in.numel(), vp.slots[0].pinned_out.numel()
+
+    # ---------------------------------------------------------------- the 126-frame video once, sharded, tail batch included
+    uniq = [shard[j:j + B] for j in range(0, len(shard), B)]
+    video_batches = []
+    for idx in uniq:
+        pad = idx + [idx[-1]] * (B - len(idx))
+        video_batches.append((torch.stack([host_frames[k] for k in pad]).pin_memory(), len(idx)))
+    barrier()
+    t0 = time.perf_counter()
+    vstats = vp.run(iter(video_batches)) if video_batches else {"frames": 0, "batches": 0}
+    torch.cuda.synchronize()
+    v_ms = reduce_max((time.perf_counter() - t0) * 1e3)
+    v_frames = vstats["frames"]
+    if dist is not None:
+        tf = torch.tensor([v_frames], device=dev, dtype=torch.float64)
+        dist.all_reduce(tf)
+        v_frames = int(tf.item())
+    video_126 = {"frames": v_frames, "seconds": v_ms * 1e-3, "frames_per_s": v_frames / (v_ms * 1e-3), "scaling": "strong",
+                 "frames_on_rank0": len(shard), "batches_on_rank0": len(uniq),
+                 "note": "host wall clock around VideoPipeline.run of each rank's shard (pinned frames in, labels out), slowest rank; the last micro-batch is padded to the static batch"}
 
     # ---------------------------------------------------------------- per-kernel-class timing (instrumented eager pass)
     kern = None
     roof = None
     if rank == 0:
         ops.TIMING, ops.BYTES = {}, {}
+        ops.LAUNCHES = 0
         pipe(dev_batches[1 % n_batches])
         torch.cuda.synchronize()
+        launches_per_step = ops.LAUNCHES
         classes = {}
         for name, evs in ops.TIMING.items():
             classes[name] = {"launches": len(evs), "ms": sum(a.elapsed_time(b) for a, b in evs)}
@@ -305,10 +304,14 @@ def main():
             achieved = flops / (classes[gname]["ms"] * 1e-3) / 1e12
             peak = ops.tensor_peak_tflops(fmt, 256)
             nominal = {"nv4": 9000.0, "mx4": 9000.0, "mx8": 4500.0, "bf16": 2250.0}[fmt]
-            # DRAM bytes per launch of the dominant kernel: ncu figure per token row (profiles/gemm_nv4_block_dram_traffic.md:
-            # 4987 B per row and launch, averaged over qkv / proj / fc1 / fc2 at 22 470 rows) times the mean rows per launch here
+            # DRAM bytes per launch of the dominant kernel: a profiled figure per token row, kept as data beside the profile
+            # summaries, times the mean rows per launch of this run; None when this configuration has not been profiled
             rows_mean = B * ((cfg.depth - cfg.num_joint_blocks) * (5 + (size // 16) ** 2) + cfg.num_joint_blocks * (5 + (size // 16) ** 2 + cfg.num_queries)) / cfg.depth
-            traffic = 4987.0 * rows_mean if (fmt == "nv4" and args.arch == "vit_l") else None
+            traffic = None
+            tfile = ROOT / "profiles" / "dram_traffic.json"
+            if tfile.exists():
+                per_row = json.loads(tfile.read_text()).get(f"gemm_block_{fmt}_{args.arch}", {}).get("dram_bytes_per_row_per_launch")
+                traffic = per_row * rows_mean if per_row else None
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                     "kernel": f"gemm_kernel<{fmt}> (qkv, proj, fc1, fc2 of all blocks; {classes[gname]['launches']} launches per step)",
                     "peak_source": f"tcgen05 {fmt} instruction-rate probe (M=128, N=256 as in the kernel, shared-memory-resident operands) measured in this run; "
@@ -334,7 +337,7 @@ def main():
                            "parallelism": f"dp{world} (replicated weights, no collective)", "l2": "inputs larger than L2: a different frame batch every step"},
                 "clocks": clocks,
                 "e2e": {"value": e2e_fps, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "gpu_launches": launches_per_step * args.steps, "roofline": roof, "kernels": kern}
+                "gpu_launches": launches_per_step * args.steps, "roofline": roof, "kernels": kern, "video_126": video_126}
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline_sample(fmt)
         print(json.dumps(line), flush=True)

@@ -118,9 +118,10 @@ class VideoPipeline:
 
     # ------------------------------------------------------------------ streaming driver
     def run(self, source: Iterable, consumer: Optional[Callable] = None) -> dict:
-        """source yields uint8 host frames [H, W, 3] (numpy or torch; copied into the ring) or whole pinned batches
-        [B, H, W, 3] (read in place).  consumer(frame_index, labels) is called in frame order from the result thread with a
-        numpy view [h, w] of the slot's pinned output; it must copy what it keeps.  A last, partial batch is padded with
+        """source yields uint8 host frames [H, W, 3] (numpy or torch; copied into the ring), whole pinned batches
+        [B, H, W, 3] (read in place) or (pinned batch, valid) pairs for a batch of which only the first `valid` frames count.
+        consumer(frame_index, labels) is called in frame order from the result thread with a numpy view [h, w] of the slot's
+        pinned output; it must copy what it keeps.  A last, partial batch is padded with
         its final frame; padded frames are not reported.  Returns {"frames", "batches", "t_total", "lat_ms"}."""
         if not self.ready:
             raise KfError("VideoPipeline.run before warmup()")
@@ -149,6 +150,9 @@ class VideoPipeline:
                 for item in source:
                     if stop.is_set():
                         break
+                    valid = self.B
+                    if isinstance(item, tuple):
+                        item, valid = item
                     t = torch.as_tensor(item)
                     if t.dim() == 4:                       # a whole batch that already sits in pinned memory
                         if fill:
@@ -157,8 +161,8 @@ class VideoPipeline:
                         if k is None:
                             break
                         self.slots[k].src = t
-                        filled.put((k, idx, self.B, time.perf_counter()))
-                        idx += self.B
+                        filled.put((k, idx, valid, time.perf_counter()))
+                        idx += valid
                         k = None
                         continue
                     if k is None:
