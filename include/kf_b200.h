@@ -158,6 +158,28 @@ KF_API int kf_broadcast_rows(const float* src, float* dst, int R, int d, int B, 
  * Replaces the implicit im2col of patch_gemm_kernel (infer-opt/round11_attn_tier0/impl/patch_embed.cu:76-194). */
 KF_API int kf_im2col_patch16(const void* x, void* out, int B, int S, void* stream);
 
+/* Patch embedding that allocates nothing: x bf16 [B, 3, S, S] -> tokens fp32 [B, tokens_per_image, d], rows
+ * row_offset .. row_offset + (S/16)^2 - 1 of every image = patches * w^T + bias (w bf16 [d, 768], k = c*256 + py*16 + px;
+ * bias fp32 [d] or NULL; flags: 0 or KF_G_ROUND_BF16).  The same result, bit for bit, as kf_im2col_patch16 into a
+ * caller buffer followed by kf_gemm_bs with the output row mapping, but the gathered patch rows go to a fixed array inside
+ * the library instead of a buffer the caller allocates.
+ * For callers that cannot allocate: a plug-in inside another program's frame loop that receives inputs and outputs but no
+ * allocator, or a latency-critical path where cudaMalloc's device-wide synchronisation is not acceptable.
+ * Limits and rules:
+ *   - at most KF_PATCH_STATIC_MAX_ROWS = B * (S/16)^2 patch rows per call (one 1024 x 1024 image, two 640 x 640 images);
+ *     more is refused with KF_ERR_BAD_ARGUMENT and a message.  The array (6 MiB) is part of the library image: every GPU
+ *     that loads the library holds it until the process exits.
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device current) and
+ *     keeps it; make that first call before any stream capture.
+ *   - every call uses the same array, which keeps the previous call's rows: nothing in it needs clearing (a call overwrites
+ *     every row it reads), but two calls that overlap on the GPU (different streams, no ordering) race on it.
+ *   - no cudaMalloc, cudaFree or other allocating routine is called.
+ * No counterpart in the reference (its patch embed, infer-opt/round11_attn_tier0/impl/patch_embed.py:34-53, returns freshly
+ * allocated torch tensors). */
+#define KF_PATCH_STATIC_MAX_ROWS 4096
+KF_API int kf_patch_embed_static(const void* x, const void* w, const float* bias, float* tokens, int B, int S, int d, int tokens_per_image,
+                                 int row_offset, int flags, void* stream);
+
 /* ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] (ConvTranspose2d k2 s2 as a GEMM, column (dy*2+dx)*C + c) -> bias + GELU +
  * pixel shuffle + depthwise 3x3 (dww fp32 [9, C], tap-major, zero padding) + LayerNorm2D -> out bf16 [B, 2Hs, 2Ws, C].
  * pre_act != 0: g already holds bf16(gelu(conv + bias)) (applied by the GEMM epilogue: KF_G_PRE_ROUND_BF16 | KF_G_GELU

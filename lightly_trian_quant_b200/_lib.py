@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
             "kf_ln_tail": [vp, vp, vp, f32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
             "kf_broadcast_rows": [vp, vp, i32, i32, i32, i64, i64, vp],
             "kf_im2col_patch16": [vp, vp, i32, i32, vp],
+            "kf_patch_embed_static": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
             "kf_dw_ln": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, i32, vp],
             "kf_semantic": [vp, vp, i32, i32, i32, i32, vp, vp, vp],
             "kf_resize_norm": [vp, vp, i32, i32, i32, i32, C.POINTER(C.c_float), C.POINTER(C.c_float), vp],

@@ -493,3 +493,76 @@ extern "C" int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, i
                                                                           std3[0], std3[1], std3[2]);
   return cuda_status(cudaGetLastError(), "kf_resize_norm launch");
 }
+
+// ------------------------------------------------------------------------------------------------ patch embed without a caller-provided scratch buffer
+// The patch-embed path is two launches with a scratch tensor between them: the gather kernel writes the patch rows
+// [B*(S/16)^2, 768] bf16 and the tensor-core GEMM reads them as its A operand.  Everywhere else in this library the caller
+// allocates that tensor.  Some callers cannot: a plug-in that runs inside another program's frame loop and is handed its
+// inputs and outputs but no allocator, or a real-time path in which a cudaMalloc (it synchronises the whole device) would
+// stall the copy streams.  For them the rows live in this fixed array inside the library image; every GPU that loads the
+// library carries it until the process exits, so it is kept to what one 1024 x 1024 image (or two 640 x 640 ones) needs.
+static __device__ __align__(256) unsigned char g_patch_rows[(size_t)KF_PATCH_STATIC_MAX_ROWS * 768 * 2];
+
+namespace kf {
+// Device address of the array on the CURRENT device.  On the host the array's name is only a handle: cudaGetSymbolAddress turns
+// it into the pointer kernels and tensor maps can use.  Looked up once per device and kept.
+static int patch_rows_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+  if (dev >= 0 && dev < 64 && cached[dev] != nullptr) {
+    *out = cached[dev];
+    return KF_OK;
+  }
+  void* p = nullptr;
+  e = cudaGetSymbolAddress(&p, g_patch_rows);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetSymbolAddress(patch rows)");
+  if (p == nullptr) {
+    set_error("kf_patch_embed_static: the scratch array has no device address");
+    return KF_ERR_UNSUPPORTED;
+  }
+  if (dev >= 0 && dev < 64) cached[dev] = p;
+  *out = p;
+  return KF_OK;
+}
+}  // namespace kf
+
+extern "C" int kf_patch_embed_static(const void* x, const void* w, const float* bias, float* tokens, int B, int S, int d, int tokens_per_image, int row_offset,
+                                     int flags, void* stream) {
+  KF_REQUIRE(B >= 0 && S > 0 && S % 16 == 0, "kf_patch_embed_static: image side %d must be a positive multiple of 16", S);
+  KF_REQUIRE(d > 0 && d % 128 == 0, "kf_patch_embed_static: d=%d must be a positive multiple of 128", d);
+  const int64_t P = (int64_t)(S / 16) * (S / 16), rows = P * B;
+  KF_REQUIRE(rows <= KF_PATCH_STATIC_MAX_ROWS,
+             "kf_patch_embed_static: %lld patch rows exceed the built-in scratch of %d rows (one 1024 x 1024 image); use kf_im2col_patch16 + kf_gemm_bs with your own buffer",
+             (long long)rows, KF_PATCH_STATIC_MAX_ROWS);
+  KF_REQUIRE(row_offset >= 0 && (int64_t)row_offset + P <= tokens_per_image, "kf_patch_embed_static: %lld patch rows behind %d do not fit %d tokens per image", (long long)P,
+             row_offset, tokens_per_image);
+  KF_REQUIRE((flags & ~KF_G_ROUND_BF16) == 0, "kf_patch_embed_static: only KF_G_ROUND_BF16 is a valid flag");
+  if (B == 0) return KF_OK;
+  KF_REQUIRE(x && w && tokens && al16(x) && al16(w), "kf_patch_embed_static: tensors must be non-null and 16-byte aligned");
+  void* scratch = nullptr;
+  int rc = patch_rows_address(&scratch);
+  if (rc != KF_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * 48;
+  im2col16_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(scratch), B, S);
+  rc = cuda_status(cudaGetLastError(), "kf_patch_embed_static gather launch");
+  if (rc != KF_OK) return rc;
+  kf_gemm_params p = {};
+  p.fmt = KF_FMT_BF16;
+  p.epi = KF_EPI_PLAIN;
+  p.M = (int)rows;
+  p.N = d;
+  p.K = 768;
+  p.out_dtype = KF_F32;
+  p.flags = flags;
+  p.A = scratch;
+  p.W = w;
+  p.bias = bias;
+  p.C = tokens;
+  p.out_row_group = (int)P;
+  p.out_row_stride = tokens_per_image;
+  p.out_row_offset = row_offset;
+  return kf_gemm_bs(&p, stream);
+}

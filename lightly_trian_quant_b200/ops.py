@@ -374,6 +374,25 @@ def gemm_tokens(a: torch.Tensor, W: QWeight, bias, out: torch.Tensor, rows_per_i
     return out
 
 
+PATCH_STATIC_MAX_ROWS = 4096
+
+
+def patch_embed_static(x: torch.Tensor, W: QWeight, bias, out: torch.Tensor, row_offset: int, round_bf16: bool = False) -> torch.Tensor:
+    """Patch embedding for callers that must not allocate: x bf16 [B, 3, S, S] -> rows row_offset.. of every image of the fp32
+    token stream out [B, tokens_per_image, d], through the library's built-in scratch array instead of an im2col tensor
+    (the same bits as gemm_tokens(im2col_patch16(x), ...)).  At most PATCH_STATIC_MAX_ROWS patch rows per call; calls that
+    overlap on the GPU race on the shared array; the first call on a device should come before any stream capture."""
+    _need_cuda(x, W.q, bias, out)
+    if x.dtype != torch.bfloat16 or x.dim() != 4 or x.shape[1] != 3 or x.shape[2] != x.shape[3] or not x.is_contiguous():
+        raise KfError("patch_embed_static: x must be contiguous bf16 [B, 3, S, S]")
+    if W.fmt != "bf16" or W.K != 768 or out.dtype != torch.float32 or not out.is_contiguous() or out.dim() != 3 or out.shape[2] != W.N:
+        raise KfError("patch_embed_static: W must be a bf16 [d, 768] weight and out contiguous fp32 [B, tokens_per_image, d]")
+    B, _, S, _ = x.shape
+    _run("patch_embed_static", lambda: _lib.lib().kf_patch_embed_static(x.data_ptr(), W.q.data_ptr(), _ptr(bias), out.data_ptr(), B, S, W.N, out.shape[1], row_offset,
+                                                                        _lib.KF_G_ROUND_BF16 if round_bf16 else 0, _stream()))
+    return out
+
+
 def im2col_patch16(x: torch.Tensor) -> torch.Tensor:
     """x bf16 [B, 3, S, S] -> bf16 [B*(S/16)^2, 768]."""
     _need_cuda(x)
