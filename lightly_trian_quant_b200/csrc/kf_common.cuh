@@ -166,10 +166,22 @@ __device__ __forceinline__ float2 gelu_erf2(float2 x) {
   return fma2(n, e, relu);
 }
 
-// max(a, b, c) in one instruction
+// max(a, b, c) in one instruction.  NaN-propagating (as are amax_nan / min_nan below): the block maxima of the quantisers
+// must carry a NaN to the scale byte the way torch's amax does in the reference quantiser (a NaN activation gives scale byte
+// 255 / 0x7f and is not silently quantised as a finite value); fmaxf would drop it.
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+__device__ __forceinline__ float amax_nan(float a, float b) {
+  float y;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(y) : "f"(a), "f"(b));
+  return y;
+}
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float y;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(y) : "f"(a), "f"(b));
   return y;
 }
 
@@ -221,8 +233,13 @@ template <int NL>
 __device__ __forceinline__ void quant_mx4(const float (&v)[NL], float amax, bool div_true, uint32_t* out /* NL/8 words */, int& sf_byte) {
   int byte = rceil_byte<6>(amax, 254, div_true);
   float inv = pow2_int(127 - byte);
+  const bool has_nan = amax != amax;            // the conversion instruction would turn a NaN into 6; the reference's comparisons give 0
   if constexpr (NL == 4) {
     float t[4] = {v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv};
+    if (has_nan) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) t[j] = t[j] != t[j] ? 0.f : t[j];
+    }
     out[0] = cvt_e2m1x4(t);                     // 16 bits
   } else {
     float t[8];
@@ -230,6 +247,10 @@ __device__ __forceinline__ void quant_mx4(const float (&v)[NL], float amax, bool
     for (int i = 0; i < NL; i += 8) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) t[j] = v[i + j] * inv;
+      if (has_nan) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = t[j] != t[j] ? 0.f : t[j];
+      }
       out[i / 8] = cvt_e2m1x8(t);
     }
   }
@@ -274,7 +295,7 @@ __device__ __forceinline__ Nv4Block nv4_block(float amax, const Nv4Scale& sc, bo
   const float ts = sc.ts;
   // amax / 6 and (amax / 6) / ts are IEEE divisions; 1/6 as a constant reciprocal (RN(1/6) = 0x3E2AAAAB)
   float a6 = div_true ? div_exact(amax, 6.0f, 0.16666667163372040f, true) : amax * (1.0f / 6.0f);
-  float t = fminf(div_exact(a6, ts, sc.rcp_ts, sc.safe), 448.f);
+  float t = min_nan(div_exact(a6, ts, sc.rcp_ts, sc.safe), 448.f);
   Nv4Block b;
   b.sb = cvt_e4m3x2(t, 0.f) & 0xFF;
   float denom = e4m3_to_float(b.sb) * ts;
@@ -347,7 +368,7 @@ __device__ __forceinline__ bool mant_all_ones(float d) { return (__float_as_uint
 // ones; non-zero scale) the packed route is taken, anything else goes through quant_nv4 itself.
 __device__ __forceinline__ void quant_nv4_pair16(const float (&v0)[16], float am0, const float (&v1)[16], float am1, const Nv4Scale& sc, bool div_true,
                                                  uint32_t* out /* 4 words */, int& by0, int& by1) {
-  const float lo = fminf(am0, am1), hi = fmaxf(am0, am1);
+  const float lo = min_nan(am0, am1), hi = amax_nan(am0, am1);       // a NaN maximum fails both range tests and takes the scalar route
   if (sc.safe && sc.ts > 1e-15f && sc.ts < 1e15f && lo > 1e-15f && hi < 1e15f) {
     const float2 am = make_float2(am0, am1);
     float2 a6;

@@ -144,7 +144,7 @@ __device__ __forceinline__ void quant_chunk(const GemmArgs& g, const uint32_t (&
     return;
   }
   float va[16], vb[16];
-  const float am = fmaxf(quant_values16(g, r, 0, ts, bsm, dbg, va), quant_values16(g, r, 1, ts, bsm, dbg, vb));
+  const float am = amax_nan(quant_values16(g, r, 0, ts, bsm, dbg, va), quant_values16(g, r, 1, ts, bsm, dbg, vb));
   if (g.out_fmt == KF_FMT_MX8) {
     uint32_t o[8];
     quant_mx8<16>(va, am, div_true, o, by0);

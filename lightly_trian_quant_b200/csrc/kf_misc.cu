@@ -340,6 +340,18 @@ __global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __re
 // channels from shared memory.  Spans that do not fit the buffer (extreme down-scaling) take the direct path.
 constexpr int RS_SPAN = 4096;                            // bytes of one input row a CTA can stage (256 outputs at up to 5x down-scaling)
 
+// One aligned 32-bit word of the frame batch; a word that straddles the end of the batch is put together from the bytes
+// that belong to it, one that starts past the end reads as zero (the host checks that the batch starts on a word boundary).
+__device__ __forceinline__ uint32_t rs_load_word(const uint32_t* wp, uintptr_t buf_end) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(wp);
+  if (a + 4 <= buf_end) return __ldg(wp);
+  uint32_t w = 0;
+  const uint8_t* bp = reinterpret_cast<const uint8_t*>(wp);
+  for (int i = 0; i < 3; ++i)
+    if (a + i < buf_end) w |= (uint32_t)__ldg(bp + i) << (8 * i);
+  return w;
+}
+
 __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restrict__ src, __nv_bfloat16* __restrict__ dst, int Hi, int Wi, int So,
                                                           float m0, float m1, float m2, float s0, float s1, float s2) {
   __shared__ float vbuf[RS_SPAN];
@@ -378,8 +390,7 @@ __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restr
         const int64_t off = row0 + (int64_t)y * Wi * 3 + byte_a + j4;
         const uintptr_t ad = reinterpret_cast<uintptr_t>(src) + off;
         const uint32_t* wp = reinterpret_cast<const uint32_t*>(ad & ~(uintptr_t)3);
-        const uint32_t w0 = reinterpret_cast<uintptr_t>(wp) < buf_end ? __ldg(wp) : 0u;
-        const uint32_t w1 = reinterpret_cast<uintptr_t>(wp + 1) < buf_end ? __ldg(wp + 1) : 0u;
+        const uint32_t w0 = rs_load_word(wp, buf_end), w1 = rs_load_word(wp + 1, buf_end);
         const uint32_t four = __funnelshift_r(w0, w1, (uint32_t)(ad & 3) * 8);
         const uint32_t v0 = four & 0xFF, v1 = (four >> 8) & 0xFF, v2 = (four >> 16) & 0xFF, v3 = four >> 24;
         a0 = fmaf(wy, (float)v0, a0);
@@ -488,6 +499,7 @@ extern "C" int kf_resize_norm(const uint8_t* frames, void* out, int B, int Hi, i
   KF_REQUIRE(B >= 0 && Hi > 0 && Wi > 0 && So > 0, "kf_resize_norm: bad shape");
   if (B == 0) return KF_OK;
   KF_REQUIRE(frames && out && mean3 && std3, "kf_resize_norm: null pointer (mean3 / std3 are host arrays of 3 floats)");
+  KF_REQUIRE((reinterpret_cast<uintptr_t>(frames) & 3) == 0, "kf_resize_norm: frames must start on a 4-byte boundary (the kernel reads aligned words)");
   dim3 grid((So + 255) / 256, So, B);
   resize_norm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(frames, static_cast<__nv_bfloat16*>(out), Hi, Wi, So, mean3[0], mean3[1], mean3[2],
                                                                           std3[0], std3[1], std3[2]);

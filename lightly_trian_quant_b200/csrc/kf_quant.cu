@@ -110,16 +110,16 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
   }
   float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  for (int i = 0; i < 16; ++i) amax = amax_nan(amax, fabsf(v[i]));
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   int byte;
   if (FMT == KF_FMT_MX8) {
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = amax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     uint32_t o[4];
     quant_mx8<16>(v, amax, div_true, o, byte);
     if (valid) *reinterpret_cast<uint4*>(q + (int64_t)row * K + c16 * 16) = make_uint4(o[0], o[1], o[2], o[3]);
   } else if (FMT == KF_FMT_MX4) {
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = amax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     uint32_t o[2];
     quant_mx4<16>(v, amax, div_true, o, byte);
     if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * (K >> 1) + c16 * 8) = make_uint2(o[0], o[1]);
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
       float am = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; j += 2) am = max3(am, fabsf(v[i][j]), fabsf(v[i][j + 1]));
-      amax[i] = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      amax[i] = amax_nan(am, __shfl_xor_sync(0xffffffffu, am, 1));
     }
     const int par = lane & 1;
     Nv4Block own[2], oth[2];
@@ -344,8 +344,8 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
     float amax = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j += 2) amax = max3(amax, fabsf(v[i][j]), fabsf(v[i][j + 1]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    if (FMT != KF_FMT_NV4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = amax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if (FMT != KF_FMT_NV4) amax = amax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     int byte;
     const int col = i * 256 + lane * 8;
     if (FMT == KF_FMT_MX8) {

@@ -47,6 +47,7 @@ def f32_to_e4m3_bits(v: np.ndarray) -> np.ndarray:
     sub = np.rint(val * 512.0).astype(np.int64)
     bits = np.where(val < 2.0 ** -6, sub, normal)
     bits = np.where(val == 0, 0, bits)
+    bits = np.where(np.isnan(v), 0x7F, bits)              # e4m3fn has one NaN pattern per sign (the torch cast gives 0x7f)
     return (bits.astype(np.uint8) | sign).astype(np.uint8)
 
 

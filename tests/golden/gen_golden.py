@@ -111,6 +111,19 @@ def main(ref_root: str):
                 assert np.array_equal(fsf.numpy(), ss) and np.array_equal(fts.numpy(), blob[f"{name}/nv4_ts"])
             else:
                 assert np.array_equal(fsf.numpy(), qr.to_blocked(torch.from_numpy(blob[f"{name}/mx4_s"])).numpy())
+    # non-finite inputs (NaN, +Inf, -Inf in different blocks): only the codes and scale bytes, with a given static nv4 scale
+    # (a data-derived per-tensor scale would be NaN itself)
+    gn = torch.Generator().manual_seed(5)
+    xn = torch.randn(4, 128, generator=gn)
+    xn[0, 3], xn[1, 40], xn[2, 100], xn[3, 127] = float("nan"), float("inf"), float("-inf"), float("nan")
+    blob["nonfinite/x"] = xn.numpy()
+    q, b = qr.mx8_quantize(xn)
+    blob["nonfinite/mx8_q"], blob["nonfinite/mx8_s"] = q.view(torch.uint8).numpy(), b.numpy()
+    q, b = qr.mx4_quantize(xn)
+    blob["nonfinite/mx4_q"], blob["nonfinite/mx4_s"] = q.numpy(), b.numpy()
+    tsn = torch.tensor([0.01])
+    q, sf, _ = qr.nv4_quantize(xn, tsn)
+    blob["nonfinite/nv4h_ts"], blob["nonfinite/nv4h_q"], blob["nonfinite/nv4h_s"] = tsn.numpy(), q.numpy(), sf.view(torch.uint8).numpy()
     # config-1 GEMM slice: dequant(X[:96]) @ dequant(W[:128])^T + bias -> fp32 and bf16 (the reference's CPU path)
     gc = torch.Generator().manual_seed(0)
     X = torch.randn(1605, 1024, generator=gc)

@@ -88,3 +88,18 @@ def test_bf16_round():
 
     v = torch.randn(50000) * 37
     assert np.array_equal(qo.bf16_round(v.numpy()), v.to(torch.bfloat16).float().numpy())
+
+
+def test_non_finite_inputs_follow_the_reference(golden):
+    """NaN and +-Inf in different blocks: the scale bytes (255 / 254 / 0x7f) and codes the reference quantisers produce."""
+    import warnings
+
+    x = golden["nonfinite/x"]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        q, s = qo.mx8_quantize(x)
+        assert np.array_equal(q, golden["nonfinite/mx8_q"]) and np.array_equal(s, golden["nonfinite/mx8_s"])
+        q, s = qo.mx4_quantize(x)
+        assert np.array_equal(q, golden["nonfinite/mx4_q"]) and np.array_equal(s, golden["nonfinite/mx4_s"])
+        q, s, _ = qo.nv4_quantize(x, golden["nonfinite/nv4h_ts"])
+        assert np.array_equal(q, golden["nonfinite/nv4h_q"]) and np.array_equal(s, golden["nonfinite/nv4h_s"])

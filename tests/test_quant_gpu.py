@@ -174,3 +174,22 @@ def test_fast_reciprocal_is_correctly_rounded_for_every_significand():
     torch.cuda.synchronize()
     ops.check_device_error()
     assert int(cnt.item()) == 0, f"{int(cnt.item())} significands differ from __frcp_rn"
+
+
+@pytest.mark.parametrize("fmt", ["mx8", "mx4", "nv4"])
+def test_non_finite_inputs_follow_the_reference(golden, fmt):
+    """a NaN or an infinity in a block reaches the scale byte and the codes exactly as in the reference quantiser (its
+    maxima propagate NaN): nothing is silently quantised as a finite value."""
+    from lightly_trian_quant_b200 import ops
+
+    x = torch.from_numpy(golden["nonfinite/x"]).cuda()
+    a = ops.ActBuf(x.shape[0], x.shape[1], fmt, device="cuda")
+    key = "nv4h" if fmt == "nv4" else fmt
+    if fmt == "nv4":
+        a.ts.copy_(torch.from_numpy(golden["nonfinite/nv4h_ts"]))
+    ops.quant_rows(x, a)
+    ops.check_device_error()
+    assert np.array_equal(a.q.cpu().numpy(), golden[f"nonfinite/{key}_q"])
+    nb = x.shape[1] // qo.VEC[fmt]
+    s2 = qo.from_blocked(a.sf.cpu().numpy().reshape(1, -(-nb // 4), 32, 4, 4), x.shape[0], nb)
+    assert np.array_equal(s2, golden[f"nonfinite/{key}_s"])
