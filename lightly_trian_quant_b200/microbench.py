@@ -8,6 +8,7 @@ larger than L2 so operands come from HBM, not from cache).
     python -m lightly_trian_quant_b200.microbench quant_rows --fmt nv4 --batch 8 --k 1024
     python -m lightly_trian_quant_b200.microbench dw_ln --batch 14 --hs 80 --k 1024
     python -m lightly_trian_quant_b200.microbench peak --fmt nv4
+    python -m lightly_trian_quant_b200.microbench sweep --fmt nv4        # quantise + GEMM over every ViT-L linear at 1 / 8 / 32 frames
 
 `kind` selects the GEMM shape AND its fused epilogue: qkv (bias + RoPE + relayout), proj / fc2 (bias, LayerScale,
 fp32 residual in place), fc1 (bias + GELU + quantise-out), plain (bf16 out).  Prints one JSON line.
@@ -188,9 +189,36 @@ def bench_fill(args):
     return out
 
 
+def bench_sweep(args):
+    """The quantise + GEMM sweep over every ViT-L/16 linear shape (qkv, proj, fc1, fc2 with their fused epilogues) at
+    M = 1605 x {1, 8, 32} in one format, plus the row quantiser and the LayerNorm + quantiser at the same sizes: one JSON
+    document with us, TFLOP/s and GB/s per (shape, frames)."""
+    import copy
+
+    out = {"kernel": f"sweep {args.fmt}", "tokens": args.tokens, "rows": {}}
+    for frames in (1, 8, 32):
+        a = copy.copy(args)
+        a.batch = frames
+        a.iters = max(5, min(args.iters, 200 // frames))
+        row = {}
+        for kind in ("qkv", "proj", "fc1", "fc2"):
+            a.kind = kind
+            r = bench_gemm(a)
+            row[kind] = {"us": round(r["us"], 2), "TFLOP/s": round(r["TFLOP/s"], 1)}
+        for k in (1024, 4096):
+            a.k = k
+            r = bench_quant_rows(a)
+            row[f"quant_rows_k{k}"] = {"us": round(r["us"], 2), "GB/s": round(r["GB/s"], 1)}
+        a.k = 1024
+        r = bench_ln_quant(a)
+        row["ln_quant_d1024"] = {"us": round(r["us"], 2), "GB/s": round(r["GB/s"], 1)}
+        out["rows"][f"{frames}_frames_M{frames * args.tokens}"] = row
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "lib_gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak", "fill"])
+    ap.add_argument("what", choices=["gemm", "lib_gemm", "attn", "ln_quant", "quant_rows", "dw_ln", "peak", "fill", "sweep"])
     ap.add_argument("--fmt", default="nv4")
     ap.add_argument("--kind", default="fc1", choices=list(SHAPES))
     ap.add_argument("--batch", type=int, default=8)
@@ -205,7 +233,7 @@ def main():
     ap.add_argument("--general-tables", action="store_true", help="gemm qkv: rotary tables without the repeated-half promise (the slower general path)")
     args = ap.parse_args()
     torch.set_grad_enabled(False)
-    fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak, "fill": bench_fill}[args.what]
+    fn = {"gemm": bench_gemm, "lib_gemm": bench_lib_gemm, "attn": bench_attn, "ln_quant": bench_ln_quant, "quant_rows": bench_quant_rows, "dw_ln": bench_dw_ln, "peak": bench_peak, "fill": bench_fill, "sweep": bench_sweep}[args.what]
     print(json.dumps(fn(args)), flush=True)
 
 
