@@ -33,10 +33,19 @@
 
 namespace kf {
 
-constexpr int STAGES = 3;
+// Depth of the operand ring, chosen per launch.  A fourth stage (54 KB) helps where the main loop is the longer chain
+// (measured at M = 22 470: fc2 K 4096 79 -> 76 us, MXFP8 fc2 116 -> 108 us, PLAIN 73 -> 69 us) and hurts where the epilogue is
+// (proj 51 -> 53 us, fc1 93 -> 98 us: the stage's shared memory comes out of the L1 the epilogue's global accesses use);
+// the ROPE kernel's table slabs leave no room for one.
+constexpr int MAX_STAGES = 4;
+static int gemm_stages(int epi, int k_tiles, int flags) {
+  if (epi == KF_EPI_PLAIN) return (flags & KF_G_GELU) ? 3 : 4;      // PLAIN with GELU (the head's ConvTranspose GEMMs) is epilogue-bound too
+  if (epi == KF_EPI_RES && k_tiles >= 8) return 4;
+  return 3;
+}
 template <int EPI>
-constexpr size_t gemm_smem() {                         // operand ring + scale atoms + bias slices (+ the rotary-table slabs) + barriers
-  return (size_t)STAGES * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * SLICE_FLOATS * 4 + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
+constexpr size_t gemm_smem(int stages) {               // operand ring + scale atoms + bias slices (+ the rotary-table slabs) + barriers
+  return (size_t)stages * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * SLICE_FLOATS * 4 + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -45,6 +54,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
   constexpr int ATOMS = KindTraits<KIND>::ATOMS;
   constexpr bool SCALED = KIND != KIND_BF16;
+  const int STAGES = g.stages;                            // 3 or 4: the ring depth this launch was given shared memory for
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* tiles = smem;
@@ -52,7 +62,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   float* slices = reinterpret_cast<float*>(sfs + (size_t)STAGES * SF_STAGE_BYTES);
   float* slabs = slices + EPI_WARPS * SLICE_FLOATS;                        // ROPE only
   uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS : 0));
-  uint64_t *full = bars, *empty = bars + STAGES, *tfull = bars + 2 * STAGES, *tempty = tfull + 1;
+  uint64_t *full = bars, *empty = bars + MAX_STAGES, *tfull = bars + 2 * MAX_STAGES, *tempty = tfull + 1;
   uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_empty + SF_BUFS);
   volatile uint32_t* abort_flag = tmem_holder + 1;
@@ -314,11 +324,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<EPI>());
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<EPI>(EPI == KF_EPI_ROPE ? 3 : MAX_STAGES));
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), gemm_smem<EPI>(), st, tmA, tmW, g), "kf_gemm_bs launch");
+  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), gemm_smem<EPI>(g.stages), st, tmA, tmW, g), "kf_gemm_bs launch");
 }
 
 template <int KIND>
@@ -388,6 +398,7 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
   g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = (p->N + BN - 1) / BN; g.k_tiles = (int)(kbytes / BKB);
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
+  g.stages = gemm_stages(epi, g.k_tiles, p->flags);
   const bool maps_rows = epi == KF_EPI_PLAIN || epi == KF_EPI_RES;
   g.row_group = maps_rows ? p->out_row_group : 0; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
   g.y_dbg = epi == KF_EPI_QUANT ? p->y_dbg : nullptr;

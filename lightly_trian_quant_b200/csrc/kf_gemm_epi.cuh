@@ -36,7 +36,7 @@ struct GemmArgs {
   int M, N, K;
   int Ntok, prefix, H, d;
   int out_dtype, flags, out_fmt;
-  int m_tiles, n_tiles, k_tiles, nkb4;
+  int m_tiles, n_tiles, k_tiles, nkb4, stages;
   int row_group, row_stride, row_offset;   // PLAIN, RES: output row = (m / group) * stride + offset + m % group (group 0: identity)
   float* y_dbg;                            // QUANT: optional export of the values that were quantised (fp32 [M, N])
   unsigned int* err;

@@ -296,9 +296,9 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
     }
     const int par = lane & 1;
     Nv4Block own[2], oth[2];
+    nv4_block_pair(par ? amax[1] : amax[0], par ? amax[3] : amax[2], ts, div_true, own[0], own[1]);   // the lane's two blocks on packed pairs
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      own[h] = nv4_block(par ? amax[2 * h + 1] : amax[2 * h], ts, div_true);
       oth[h].dd = __shfl_xor_sync(0xffffffffu, own[h].dd, 1);
       oth[h].rcp = __shfl_xor_sync(0xffffffffu, own[h].rcp, 1);
       const uint32_t pk = __shfl_xor_sync(0xffffffffu, own[h].sb | ((uint32_t)own[h].mode << 8), 1);
