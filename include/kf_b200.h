@@ -183,7 +183,8 @@ KF_API int kf_patch_embed_static(const void* x, const void* w, const float* bias
 /* ScaleBlock tail: g bf16 [B*Hs*Ws, 4C] (ConvTranspose2d k2 s2 as a GEMM, column (dy*2+dx)*C + c) -> bias + GELU +
  * pixel shuffle + depthwise 3x3 (dww fp32 [9, C], tap-major, zero padding) + LayerNorm2D -> out bf16 [B, 2Hs, 2Ws, C].
  * pre_act != 0: g already holds bf16(gelu(conv + bias)) (applied by the GEMM epilogue: KF_G_PRE_ROUND_BF16 | KF_G_GELU
- * with the bias repeated 4x), so bias + GELU are skipped here.
+ * with the bias repeated 4x), so bias + GELU are skipped here.  C is a multiple of 128 up to 1024 (a CTA has C/4 threads,
+ * each owning 4 channels); any Hs, Ws.
  * Replaces dw_ln (infer-opt/round11_attn_tier0/impl/head_ext11.cu:72-250) = ScaleBlock.forward after conv1
  * (src/lightly_train/_task_models/dinov3_eomt_semantic_segmentation/scale_block.py:39-44). */
 KF_API int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B,

@@ -29,92 +29,130 @@ __global__ void __launch_bounds__(256) im2col16_kernel(const __nv_bfloat16* __re
 // g [B*Hs*Ws, 4C] bf16 is the ConvTranspose2d(k=2, s=2) GEMM output with column (dy*2+dx)*C + c.  For each output
 // pixel (Y, X) = (2y+dy, 2x+dx):  a = bf16(gelu(g + bias[c]))  (skipped when the GEMM epilogue already applied it:
 // pre_act != 0);  o = bf16(sum over the 3x3 taps of a * dww[tap][c]) with zero padding, fp32 accumulation in tap
-// order;  out = bf16(LayerNorm over c of o) in NHWC.
-// Persistent CTAs, one tile of 4 x 8 output pixels at a time.  The channels go through in slabs of 128: the 6 x 10 halo
-// of a slab (256 contiguous bytes per pixel) is fetched with 16-byte cp.async copies (zero fill outside the image) into
-// a 3-deep shared-memory ring that runs ahead across slabs AND tiles, so two slabs are always in flight while a third is
-// convolved; each thread convolves 8 channels of 2 adjacent pixels (one 3 x 4 window read for both) with the 72 tap weights
-// held in registers; the conv results of all C channels stay in shared memory for the two-pass LayerNorm statistics, which
-// each lane then works out on register-resident values.
-constexpr int DW_TH = 4, DW_TW = 8, DW_HW = (DW_TH + 2) * (DW_TW + 2), DW_CH = 128, DW_RING = 3;
-constexpr int DW_SLAB_BYTES = DW_HW * DW_CH * 2;        // 15 KB
+// order;  out = bf16(LayerNorm over c of o) in NHWC, two-pass statistics on the rounded conv outputs.
+//
+// Channel-stationary threads, rows streamed: a CTA has C/4 threads and thread t owns channels 4t..4t+3 for the whole
+// launch, so its 36 tap weights and 8 LayerNorm parameters are loaded once and stay in registers.  A work item is a
+// strip of 8 output pixels in x and seg_rows rows in y of one image; persistent CTAs take items round-robin.  The
+// halo rows of a strip (10 pixels x C channels, C*20 bytes) stream through a 5-slot shared-memory ring filled by
+// 16-byte cp.async copies (zero fill outside the image) that run two rows ahead, across item boundaries too; every
+// row is fetched once per strip and used for three output rows.  Per output row a thread reads its 4 channels of the
+// 3 x 10 window (30 8-byte shared loads), accumulates the 8 pixels in tap order on packed fp32 pairs, rounds to bf16,
+// and the LayerNorm sums of the 8 pixels are reduced over the CTA (a transposing butterfly inside the warp, then one
+// shared-memory exchange per statistic); the thread normalises and stores its own 8 bytes of each pixel, so no conv
+// result goes through shared memory and a warp's stores are 256 contiguous bytes.
+constexpr int DW_SW = 8, DW_HALO = DW_SW + 2, DW_RING = 5;
 
-__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float (&f)[8]) {
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
-__device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    w[i] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
-}
-__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+__device__ __forceinline__ void cp_async16_zfill(uint32_t smem_dst, const void* gsrc, bool valid) {
   const int n = valid ? 16 : 0;                          // 0 source bytes: the 16 destination bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(n) : "memory");
 }
 
-struct DwTile {
-  int b, Y0, X0;
+// shared-memory accesses by 32-bit address: with a compile-time C the pixel offsets fold into the instruction
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint2 v) { asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory"); }
+
+struct DwItem {
+  int b, X0, Y0, rows;                                   // rows: output rows of the item (its halo has rows + 2)
 };
-__device__ __forceinline__ DwTile dw_tile(int tile, int tiles_x, int tiles_y) {
-  DwTile t;
-  t.X0 = (tile % tiles_x) * DW_TW;
-  const int r = tile / tiles_x;
-  t.Y0 = (r % tiles_y) * DW_TH;
-  t.b = r / tiles_y;
-  return t;
+__device__ __forceinline__ DwItem dw_item(int item, int strips, int segs, int seg_rows, int Ho) {
+  DwItem r;
+  const int seg = item % segs;
+  const int q = item / segs;
+  r.X0 = (q % strips) * DW_SW;
+  r.b = q / strips;
+  r.Y0 = seg * seg_rows;
+  r.rows = min(seg_rows, Ho - r.Y0);
+  return r;
 }
 
+// sums of v[0..7] over all threads of the CTA, returned in v for every thread.  red: 64 floats of shared memory that no
+// other exchange uses between the two barriers around this call.
+__device__ __forceinline__ void dw_block_sum8(float (&v)[8], float* red, int warp, int lane, int nwarps) {
+  // transposing butterfly: after the three halving steps lane l holds the partial sum of pixel l >> 2
+  float a[4], b[2];
+  bool hi = lane & 16;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = hi ? v[j + 4] : v[j], send = hi ? v[j] : v[j + 4];
+    a[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+  }
+  hi = lane & 8;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = hi ? a[j + 2] : a[j], send = hi ? a[j] : a[j + 2];
+    b[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  hi = lane & 4;
+  float c = (hi ? b[1] : b[0]) + __shfl_xor_sync(0xffffffffu, hi ? b[0] : b[1], 4);
+  c += __shfl_xor_sync(0xffffffffu, c, 2);
+  c += __shfl_xor_sync(0xffffffffu, c, 1);
+  if ((lane & 3) == 0) red[warp * 8 + (lane >> 2)] = c;
+  __syncthreads();
+  float tot = 0.f;
+  if (lane < 8) {
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < nwarps) tot += red[w * 8 + lane];
+  }
+#pragma unroll
+  for (int p = 0; p < 8; ++p) v[p] = __shfl_sync(0xffffffffu, tot, p);
+}
+
+// CT: the channel count as a compile-time constant (0 = use the run-time argument)
+template <int CT>
 __global__ void __launch_bounds__(256, 2)
 dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias, const float* __restrict__ dww, const float* __restrict__ lnw,
-             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C, float eps, int pre_act, int tiles_x, int tiles_y,
-             int total_tiles) {
+             const float* __restrict__ lnb, __nv_bfloat16* __restrict__ out, int Hs, int Ws, int C_arg, float eps, int pre_act, int strips, int segs,
+             int seg_rows, int total_items) {
   extern __shared__ __align__(16) uint8_t dsm[];
-  uint4* res = reinterpret_cast<uint4*>(dsm + DW_RING * DW_SLAB_BYTES);     // [32 pixels][C/8]
-  const int t = threadIdx.x;
+  const int C = CT ? CT : C_arg;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31, nwarps = blockDim.x >> 5;
   const int Ho = 2 * Hs, Wo = 2 * Ws;
-  const int C8 = C >> 3, S = C / DW_CH;
-  // conv work item of this thread: 8 channels (grp) of two horizontally adjacent pixels (oy, ox0), (oy, ox0 + 1): the 3 x 4
-  // input window is read and unpacked once for both
-  const int grp = t & 15, strip = t >> 4;
-  const int oy = strip >> 2, ox0 = (strip & 3) * 2;
+  const int row_bytes = DW_HALO * C * 2;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dsm);
+  float* red = reinterpret_cast<float*>(dsm + DW_RING * row_bytes);       // two exchange areas of 64 floats
 
-  // issue cursor (runs two slabs ahead of the consume cursor, across tile boundaries).  The (pixel, 16-byte piece)
-  // pairs a thread copies are the same for every slab of a tile: their source offsets are worked out once per tile.
-  int i_tile = blockIdx.x, i_slab = 0, i_slot = 0;
-  int64_t i_src[4];
-  bool i_in[4];
+  // the thread's channels: tap weights, LayerNorm parameters, bias
+  float2 w[9][2];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(dww + (size_t)k * C) + t);
+    w[k][0] = make_float2(v.x, v.y);
+    w[k][1] = make_float2(v.z, v.w);
+  }
+  const float4 gw = __ldg(reinterpret_cast<const float4*>(lnw) + t), gb = __ldg(reinterpret_cast<const float4*>(lnb) + t);
+  const float2 gw0 = make_float2(gw.x, gw.y), gw1 = make_float2(gw.z, gw.w), gb0 = make_float2(gb.x, gb.y), gb1 = make_float2(gb.z, gb.w);
+  const float invC = 1.0f / (float)C;
+
+  // ---- issue cursor: one halo row per call, two rows ahead of the row being consumed, running on into the next item.
+  // A halo row is 10 pixels x C/8 pieces of 16 bytes; with C/4 threads thread t copies piece q = t mod C/8 of the pixels
+  // 2k + hi (hi = t >= C/8), k = 0..4.  Those pixels have the same x parity, so their sources are 4C elements apart.
+  const int C8 = C >> 3;
+  const int i_hi = t >= C8 ? 1 : 0, i_q = t - i_hi * C8;
+  int i_item = blockIdx.x, i_hr = 0, i_slot = 0;
+  DwItem I = dw_item(i_item < total_items ? i_item : 0, strips, segs, seg_rows, Ho);
   auto issue = [&]() {
-    if (i_tile < total_tiles) {
-      if (i_slab == 0) {
-        const DwTile T = dw_tile(i_tile, tiles_x, tiles_y);
+    if (i_item < total_items) {
+      const int Y = I.Y0 - 1 + i_hr;
+      const bool y_in = Y >= 0 && Y < Ho;
+      const int xs = (I.X0 >> 1) + i_hi - 1;               // source column of k = 0;  X = 2*(xs + k) + (1 - i_hi)
+      const int64_t src0 = ((((int64_t)I.b * Hs + (y_in ? (Y >> 1) : 0)) * Ws + xs) * 4 + (Y & 1) * 2 + (1 - i_hi)) * C + i_q * 8;
+      const uint32_t dst0 = ring + i_slot * row_bytes + i_hi * (C * 2) + i_q * 16;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int idx = t + 256 * k;
-          const int px = idx >> 4, q = idx & 15;
-          const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
-          const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
-          i_in[k] = idx < DW_HW * 16 && Y >= 0 && Y < Ho && X >= 0 && X < Wo;
-          const int64_t row = i_in[k] ? ((int64_t)T.b * Hs + (Y >> 1)) * Ws + (X >> 1) : 0;
-          i_src[k] = row * 4 * C + (i_in[k] ? ((Y & 1) * 2 + (X & 1)) * C : 0) + q * 8;
-        }
+      for (int k = 0; k < 5; ++k) {
+        const int xk = xs + k;
+        const bool valid = y_in && xk >= 0 && xk < Ws;
+        cp_async16_zfill(dst0 + k * (C * 4), g + (valid ? src0 + (int64_t)k * 4 * C : 0), valid);
       }
-      uint4* act = reinterpret_cast<uint4*>(dsm + i_slot * DW_SLAB_BYTES);
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        if (t + 256 * k < DW_HW * 16) cp_async16_zfill(act + t + 256 * k, g + i_src[k] + i_slab * DW_CH, i_in[k]);
-      if (++i_slab == S) {
-        i_slab = 0;
-        i_tile += gridDim.x;
+      if (++i_hr == I.rows + 2) {
+        i_hr = 0;
+        i_item += gridDim.x;
+        if (i_item < total_items) I = dw_item(i_item, strips, segs, seg_rows, Ho);
       }
       if (++i_slot == DW_RING) i_slot = 0;
     }
@@ -123,139 +161,93 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
   issue();
   issue();
 
-  int c_slot = 0;
-  const int warp = t >> 5, lane = t & 31;
-  const float invC = 1.0f / (float)C;
-  const int nk = C8 >> 5;                                    // 256-channel steps of the LayerNorm: lane owns 8 channels in each
-  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-    const DwTile T = dw_tile(tile, tiles_x, tiles_y);
-    for (int sl = 0; sl < S; ++sl) {
-      const int ch = sl * DW_CH;
-      asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of the slab to consume have landed
-      __syncthreads();                                        // ... and everybody's; the previous slab's conv is finished everywhere
-      issue();                                                // refill the slot that conv just left (two slabs stay in flight)
-      uint4* act = reinterpret_cast<uint4*>(dsm + c_slot * DW_SLAB_BYTES);
-      if (!pre_act) {                                         // bias + GELU once per halo element, in place
-        for (int idx = t; idx < DW_HW * 16; idx += 256) {
-          const int px = idx >> 4, q = idx & 15;
-          const int hy = px / (DW_TW + 2), hx = px - hy * (DW_TW + 2);
-          const int Y = T.Y0 + hy - 1, X = T.X0 + hx - 1;
-          if (Y >= 0 && Y < Ho && X >= 0 && X < Wo) {
-            float f[8];
-            bf16x8_to_f32(act[idx], f);
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8)), b1 = __ldg(reinterpret_cast<const float4*>(bias + ch + q * 8) + 1);
-            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  int c_slot = 0;                                            // slot of the halo row consumed by the current step
+  float4 bia = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!pre_act) bia = __ldg(reinterpret_cast<const float4*>(bias) + t);
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const DwItem T = dw_item(item, strips, segs, seg_rows, Ho);
+    for (int hr = 0; hr < T.rows + 2; ++hr) {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");   // this thread's copies of halo row hr have landed
+      __syncthreads();                                        // ... and everybody's; the previous step has left the slot refilled next
+      issue();
+      const uint32_t own = t * 8;                             // the thread's 4 channels inside a pixel
+      if (!pre_act) {                                         // bias + GELU on the new row, in place; only this thread reads these bytes later
+        const int Y = T.Y0 - 1 + hr;
+        if (Y >= 0 && Y < Ho) {
+          const uint32_t rowp = ring + c_slot * row_bytes + own;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k] + bb[k]);
-            act[idx] = f32_to_bf16x8(f);
-          }
-        }
-        __syncthreads();
-      }
-      // ---- depthwise 3x3 of the two pixels: taps accumulate in (ky, kx) order for each of them; the 3 x 8 tap weights of
-      // a kernel row are fetched when that row is due (72 weights at once would not fit the register budget)
-      // (packed pairs: a 16-bit pair unpacks into the two halves of one operand, and one FFMA2 serves two channels)
-      float2 acc0[4], acc1[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc0[k] = acc1[k] = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int ky = 0; ky < 3; ++ky) {
-        float2 w[3][4];
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          const float4* wp = reinterpret_cast<const float4*>(dww + (ky * 3 + k) * C + ch + grp * 8);
-          const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
-          w[k][0] = make_float2(w0.x, w0.y); w[k][1] = make_float2(w0.z, w0.w); w[k][2] = make_float2(w1.x, w1.y); w[k][3] = make_float2(w1.z, w1.w);
-        }
-#pragma unroll
-        for (int cx = 0; cx < 4; ++cx) {
-          const uint4 a = act[((oy + ky) * (DW_TW + 2) + ox0 + cx) * 16 + grp];
-          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-          float2 f[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) f[k] = make_float2(__uint_as_float(aw[k] << 16), __uint_as_float(aw[k] & 0xFFFF0000u));
-          if (cx < 3) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) acc0[k] = fma2(f[k], w[cx][k], acc0[k]);
-          }
-          if (cx > 0) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) acc1[k] = fma2(f[k], w[cx - 1][k], acc1[k]);
+          for (int hx = 0; hx < DW_HALO; ++hx) {
+            const int X = T.X0 - 1 + hx;
+            if (X >= 0 && X < Wo) {
+              const uint2 u = lds64(rowp + hx * (C * 2));
+              float2 f0 = make_float2(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u));
+              float2 f1 = make_float2(__uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
+              f0 = make_float2(gelu_erf(f0.x + bia.x), gelu_erf(f0.y + bia.y));
+              f1 = make_float2(gelu_erf(f1.x + bia.z), gelu_erf(f1.y + bia.w));
+              const __nv_bfloat162 h0 = __float22bfloat162_rn(f0), h1 = __float22bfloat162_rn(f1);
+              sts64(rowp + hx * (C * 2), make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1)));
+            }
           }
         }
       }
-      {
-        const float o0[8] = {acc0[0].x, acc0[0].y, acc0[1].x, acc0[1].y, acc0[2].x, acc0[2].y, acc0[3].x, acc0[3].y};
-        const float o1[8] = {acc1[0].x, acc1[0].y, acc1[1].x, acc1[1].y, acc1[2].x, acc1[2].y, acc1[3].x, acc1[3].y};
-        res[(oy * DW_TW + ox0) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(o0);
-        res[(oy * DW_TW + ox0 + 1) * C8 + (ch >> 3) + grp] = f32_to_bf16x8(o1);
+      if (hr >= 2) {
+        // ---- output row Y of the strip: halo rows hr-2, hr-1, hr sit in the slots c_slot-2, c_slot-1, c_slot
+        const int Y = T.Y0 + hr - 2;
+        float2 acc[DW_SW][2];
+#pragma unroll
+        for (int p = 0; p < DW_SW; ++p) acc[p][0] = acc[p][1] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+          int s = c_slot - 2 + ky;
+          if (s < 0) s += DW_RING;
+          const uint32_t rowp = ring + s * row_bytes + own;
+#pragma unroll
+          for (int hx = 0; hx < DW_HALO; ++hx) {
+            const uint2 u = lds64(rowp + hx * (C * 2));
+            const float2 f0 = make_float2(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u));
+            const float2 f1 = make_float2(__uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
+#pragma unroll
+            for (int kx = 2; kx >= 0; --kx) {                 // pixel hx - kx receives tap (ky, kx): per pixel the taps arrive in (ky, kx) order
+              const int p = hx - kx;
+              if (p >= 0 && p < DW_SW) {
+                acc[p][0] = fma2(f0, w[ky * 3 + kx][0], acc[p][0]);
+                acc[p][1] = fma2(f1, w[ky * 3 + kx][1], acc[p][1]);
+              }
+            }
+          }
+        }
+        // ---- LayerNorm over the channels of each of the 8 pixels, statistics on the bf16-rounded conv outputs
+        float s8[8];
+#pragma unroll
+        for (int p = 0; p < DW_SW; ++p) {
+          acc[p][0] = bf16_round2(acc[p][0]);
+          acc[p][1] = bf16_round2(acc[p][1]);
+          const float2 s2 = add2(acc[p][0], acc[p][1]);
+          s8[p] = s2.x + s2.y;
+        }
+        dw_block_sum8(s8, red, warp, lane, nwarps);
+#pragma unroll
+        for (int p = 0; p < DW_SW; ++p) {
+          const float2 nm = splat2(-s8[p] * invC);
+          acc[p][0] = add2(acc[p][0], nm);
+          acc[p][1] = add2(acc[p][1], nm);
+          const float2 q2 = fma2(acc[p][1], acc[p][1], mul2(acc[p][0], acc[p][0]));
+          s8[p] = q2.x + q2.y;
+        }
+        dw_block_sum8(s8, red + 64, warp, lane, nwarps);
+        __nv_bfloat16* orow = out + (((int64_t)T.b * Ho + Y) * Wo + T.X0) * C + t * 4;
+#pragma unroll
+        for (int p = 0; p < DW_SW; ++p) {
+          if (T.X0 + p < Wo) {
+            const float2 rstd = splat2(rsqrtf(s8[p] * invC + eps));
+            const __nv_bfloat162 h0 = __float22bfloat162_rn(fma2(mul2(acc[p][0], rstd), gw0, gb0));
+            const __nv_bfloat162 h1 = __float22bfloat162_rn(fma2(mul2(acc[p][1], rstd), gw1, gb1));
+            *reinterpret_cast<uint2*>(orow + (int64_t)p * C) = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+          }
+        }
       }
       if (++c_slot == DW_RING) c_slot = 0;
     }
-    __syncthreads();                                          // all conv results of the tile are in res
-
-    // ---- LayerNorm over the channels of each pixel: 8 warps x 4 pixels; the lane's channels stay in registers
-    for (int px = warp; px < DW_TH * DW_TW; px += 8) {
-      const int py = px / DW_TW, pxx = px - py * DW_TW;
-      const int Y = T.Y0 + py, X = T.X0 + pxx;
-      const uint4* r = res + px * C8;
-      float2 v[4][4];                                         // packed pairs: one instruction per two channels
-      float2 s2 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (k < nk) {
-          const uint4 a = r[lane + 32 * k];
-          const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            v[k][e] = make_float2(__uint_as_float(aw[e] << 16), __uint_as_float(aw[e] & 0xFFFF0000u));
-            s2 = add2(s2, v[k][e]);
-          }
-        }
-      }
-      float s = s2.x + s2.y;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      const float mean = s * invC;
-      const float2 nmean = splat2(-mean);
-      float2 q2 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (k < nk) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            v[k][e] = add2(v[k][e], nmean);
-            q2 = fma2(v[k][e], v[k][e], q2);
-          }
-        }
-      }
-      float ss = q2.x + q2.y;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float2 rstd = splat2(rsqrtf(ss * invC + eps));
-      if (Y < Ho && X < Wo) {
-        uint4* dst = reinterpret_cast<uint4*>(out + (((int64_t)T.b * Ho + Y) * Wo + X) * C);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (k < nk) {
-            const int i = lane + 32 * k;
-            const float4 w0 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i), w1 = __ldg(reinterpret_cast<const float4*>(lnw) + 2 * i + 1);
-            const float4 c0 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i), c1 = __ldg(reinterpret_cast<const float4*>(lnb) + 2 * i + 1);
-            const float2 ww[4] = {make_float2(w0.x, w0.y), make_float2(w0.z, w0.w), make_float2(w1.x, w1.y), make_float2(w1.z, w1.w)};
-            const float2 cc[4] = {make_float2(c0.x, c0.y), make_float2(c0.z, c0.w), make_float2(c1.x, c1.y), make_float2(c1.z, c1.w)};
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 y = fma2(mul2(v[k][e], rstd), ww[e], cc[e]);
-              f[2 * e] = y.x;
-              f[2 * e + 1] = y.y;
-            }
-            dst[i] = f32_to_bf16x8(f);
-          }
-        }
-      }
-    }
-    // the next tile's first conv writes res only after the next __syncthreads, which every warp reaches after its LayerNorm
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
@@ -460,28 +452,36 @@ extern "C" int kf_im2col_patch16(const void* x, void* out, int B, int S, void* s
 extern "C" int kf_dw_ln(const void* g, const float* bias, const float* dww, const float* lnw, const float* lnb, void* out, int B, int Hs, int Ws, int C,
                         float eps, int pre_act, void* stream) {
   KF_REQUIRE(B >= 0 && Hs > 0 && Ws > 0, "kf_dw_ln: bad shape B=%d Hs=%d Ws=%d", B, Hs, Ws);
-  KF_REQUIRE(C > 0 && C % 256 == 0 && C <= 1024, "kf_dw_ln: C=%d must be a multiple of 256 up to 1024", C);
+  KF_REQUIRE(C > 0 && C % 128 == 0 && C <= 1024, "kf_dw_ln: C=%d must be a multiple of 128 up to 1024", C);
   if (B == 0) return KF_OK;
   KF_REQUIRE(g && (bias || pre_act) && dww && lnw && lnb && out && al16(g) && al16(out) && al16(lnw) && al16(lnb) && al16(dww) && al16(bias),
              "kf_dw_ln: tensors must be non-null and 16-byte aligned");
-  const size_t smem = (size_t)DW_RING * DW_SLAB_BYTES + (size_t)DW_TH * DW_TW * C * 2;
+  const size_t smem = (size_t)DW_RING * DW_HALO * C * 2 + 2 * 64 * sizeof(float);
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(dw_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)DW_RING * DW_SLAB_BYTES + DW_TH * DW_TW * 1024 * 2));
+    const int big = (int)((size_t)DW_RING * DW_HALO * 1024 * 2 + 2 * 64 * sizeof(float));
+    cudaError_t e = cudaFuncSetAttribute(dw_ln_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dw_ln_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dw_ln_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(dw_ln_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
   int sms = 0;
   int st = device_sm_count(&sms);
   if (st != KF_OK) return st;
-  const int tiles_x = (2 * Ws + DW_TW - 1) / DW_TW, tiles_y = (2 * Hs + DW_TH - 1) / DW_TH;
-  const int64_t total = (int64_t)tiles_x * tiles_y * B;
-  KF_REQUIRE(total < (1ll << 31), "kf_dw_ln: too many tiles");
+  // items: strips of 8 output pixels in x, cut in y into segments of about 40 rows (each segment re-reads two halo rows:
+  // 5 %); fewer, longer segments when the image count alone fills the CTAs several times over
+  const int Ho = 2 * Hs, strips = (2 * Ws + DW_SW - 1) / DW_SW;
+  const int segs = (Ho + 39) / 40, seg_rows = (Ho + segs - 1) / segs;
+  const int64_t total = (int64_t)strips * segs * B;
+  KF_REQUIRE(total < (1ll << 31), "kf_dw_ln: too many strips");
   const int grid = (int)(total < 2 * sms ? total : 2 * sms);
-  dw_ln_kernel<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(g), bias, dww, lnw, lnb,
-                                                                       static_cast<__nv_bfloat16*>(out), Hs, Ws, C, eps, pre_act, tiles_x, tiles_y, (int)total);
+  // the channel counts of the ViT-L and ViT-B heads are compiled in (pixel offsets become instruction immediates)
+  auto kern = C == 1024 ? dw_ln_kernel<1024> : C == 768 ? dw_ln_kernel<768> : dw_ln_kernel<0>;
+  kern<<<grid, C / 4, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(g), bias, dww, lnw, lnb, static_cast<__nv_bfloat16*>(out), Hs,
+                                                                 Ws, C, eps, pre_act, strips, segs, seg_rows, (int)total);
   return cuda_status(cudaGetLastError(), "kf_dw_ln launch");
 }
 

@@ -81,22 +81,32 @@ def test_broadcast_rows_and_residual_into_a_longer_stream():
     assert torch.equal(big[:, Q:].reshape(B * N, d), inplace)
 
 
-@pytest.mark.parametrize("C", [256, 1024])
-def test_dw_ln_scale_block_tail(C):
+def _dw_ln_ref(gm, bias, dww, lw, lb, B, Hs, Ws, C):
+    a = gm.float().reshape(B, Hs, Ws, 2, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(B, 2 * Hs, 2 * Ws, C)
+    a = F.gelu(a + bias).to(BF).float()
+    o = F.conv2d(a.permute(0, 3, 1, 2), dww.reshape(C, 1, 3, 3), padding=1, groups=C).to(BF).float().permute(0, 2, 3, 1)
+    return F.layer_norm(o, (C,), lw, lb, 1e-6), a
+
+
+# (C, B, Hs, Ws): one and several strips, a partial last strip (2*Ws not a multiple of 8), more than one row segment
+# (2*Hs > 40), 128-channel granularity
+@pytest.mark.parametrize("C,B,Hs,Ws", [(256, 2, 6, 8), (1024, 2, 6, 8), (768, 1, 5, 7), (128, 3, 23, 3), (1024, 1, 44, 5)])
+def test_dw_ln_scale_block_tail(C, B, Hs, Ws):
     modeldef, ops, stack = _mods()
     g = torch.Generator().manual_seed(2)
-    B, Hs, Ws = 2, 6, 8
     gm = (torch.randn(B * Hs * Ws, 4 * C, generator=g) * 1.5).to(BF)
     bias = (torch.randn(C, generator=g) * 0.1).to(BF).float()
     dww = (torch.randn(C, 9, generator=g) * 0.3).to(BF).float()
     lw, lb = torch.rand(C, generator=g) + 0.5, torch.randn(C, generator=g) * 0.1
     out = ops.dw_ln(gm.cuda(), bias.cuda(), dww.t().contiguous().cuda(), lw.cuda(), lb.cuda(), B, Hs, Ws, 1e-6)
     assert out.shape == (B, 2 * Hs, 2 * Ws, C)
-    a = gm.float().reshape(B, Hs, Ws, 2, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(B, 2 * Hs, 2 * Ws, C)
-    a = F.gelu(a + bias).to(BF).float()
-    o = F.conv2d(a.permute(0, 3, 1, 2), dww.reshape(C, 1, 3, 3), padding=1, groups=C).to(BF).float().permute(0, 2, 3, 1)
-    ref = F.layer_norm(o, (C,), lw, lb, 1e-6)
+    ref, act = _dw_ln_ref(gm, bias, dww, lw, lb, B, Hs, Ws, C)
     assert go.rel_fro(out.float().cpu().numpy(), ref.numpy()) < 6e-3
+    # the same with the activation applied upstream (what the GEMM epilogue hands over): bit-identical to the fused form
+    pre = act.reshape(B, Hs, 2, Ws, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(B * Hs * Ws, 4 * C).to(BF)
+    out2 = ops.dw_ln(pre.cuda(), None, dww.t().contiguous().cuda(), lw.cuda(), lb.cuda(), B, Hs, Ws, 1e-6, pre_act=True)
+    assert go.rel_fro(out2.float().cpu().numpy(), ref.numpy()) < 6e-3
+    ops.check_device_error()
 
 
 def test_semantic_scores_and_labels():
