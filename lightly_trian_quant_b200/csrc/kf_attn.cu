@@ -7,16 +7,20 @@
 //            items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps every barrier phase running across them
 //   roles    warps 0..3: softmax, one query row per thread (tcgen05.ld of the S row, running max / sum in fp32,
 //            P -> 16 bit -> tensor memory by tcgen05.st); warp 4: TMA producer (Q in two buffers, K / V in a 4-deep
-//            ring, 4-D tensor maps so rows past N read zero); warp 5: MMA issuer (S = Q K^T: 4 MMAs of K=16 from
-//            shared memory; O += P V: 4 MMAs of K=16 with P as the A operand from tensor memory and V as the MN-major
-//            B operand)
-//   pipeline S and P are double buffered in TMEM: S(j+2) is issued as soon as the softmax of tile j has handed P(j)
-//            over, also across the end of an item (the next item's Q and first K tiles are loaded by then), so the
-//            softmax warps - whose dependent chain of S load, exponentials, P store and hand-over is the bound of this
-//            kernel - do not wait for a tensor-core round trip.  O accumulates in TMEM over all key tiles; the running
-//            maximum is raised only when a tile maximum exceeds it by more than 2^8 in the exponent domain, so the
-//            rescale of O (TMEM load, multiply, store) happens on the first tiles and then almost never, and the O
-//            barrier is waited only then and at the end of an item.
+//            ring, 4-D tensor maps so rows past N read zero); warp 5 issues the PV products (O += P V: 4 MMAs of K=16
+//            with P as the A operand from tensor memory and V as the MN-major B operand), warp 6 the S products
+//            (S = Q K^T: 4 MMAs of K=16 from shared memory); warp 7 idles (it completes the second warp group, whose
+//            registers setmaxnreg hands to the softmax warps: 200 against 56).  One thread issuing both products was
+//            busy for about 1450 of the 1670 clk of a step (each MMA costs it ~55 clk, each commit ~80, each barrier
+//            round trip 60-80 even when the phase completed long ago); with two issuers each waits for its operands
+//            first and for the hand-over last.
+//   pipeline S and P are double buffered in TMEM: S(j+2) is issued when PV(j) has completed (so a softmax that sees
+//            S(j+2) knows that P buffer j & 1 has been read), also across the end of an item (the next item's Q and
+//            first K tiles are loaded by then).  O accumulates in TMEM over all key tiles.  The exponentials of a tile
+//            use the running maximum as it is; the tile's own row sum tells whether that was safe (below 2^15 no
+//            element exceeded 2^15), so no maximum is tracked in the common case; only a row whose sum came out larger
+//            finds its maximum, recomputes its P and has its O rescaled (TMEM load, multiply, store), which happens on
+//            the first tiles and then almost never; the O barriers are waited only then and at the end of an item.
 //   numerics softmax scale 1/8 folded into exp2 (fp32, one MUFU operation per element; the exponent arguments and
 //            the row sums as packed fp32 pairs; the packed f16x2 exp2 was measured slower); m, l, O in fp32; P rounded
 //            to the input 16-bit type.  Every mbarrier wait is bounded.
@@ -31,12 +35,14 @@
 namespace kf {
 
 constexpr int AT_BM = 128, AT_BN = 64, AT_D = 64;
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 256;                        // warps 0..3 softmax, 4 TMA, 5 PV issuer, 6 S issuer, 7 idle
+constexpr int AT_REGS_SOFTMAX = 200, AT_REGS_LEAN = 56; // 128 * 200 + 128 * 56 <= 256 * 128, the allocation at launch
 constexpr int AT_KV = 4;                               // K / V ring depth
 constexpr int AT_QTILE = AT_BM * AT_D * 2;             // 16 KB
 constexpr int AT_KTILE = AT_BN * AT_D * 2;             // 8 KB
 constexpr int AT_OFF_Q = 0, AT_OFF_K = 2 * AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_BAR = AT_OFF_V + AT_KV * AT_KTILE;
 constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
+constexpr float AT_SUM_LIMIT = 32768.f;                  // a tile's row sum above this sends the row to the exact-maximum path (the largest finite f16 is 65504)
 constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128, AT_COL_P = 192;   // S buffers at columns 0 and 64, P (16-bit pairs) at 192 and 224
 
 struct AttnArgs {
@@ -66,14 +72,17 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// F16: 16-bit type of q / k / v / P / O (0 = bf16); OUT: -1 = plain 16-bit output, else the KF_FMT_* of the fused
+// output quantisation.  Compile-time so that the softmax loop carries one copy of its code.
+template <int F16, int OUT>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                const AttnArgs a) {
+                const __grid_constant__ AttnArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AT_OFF_BAR);
   uint64_t *q_full = bars, *q_empty = bars + 2, *k_full = bars + 4, *v_full = k_full + AT_KV, *kv_empty = v_full + AT_KV, *s_full = kv_empty + AT_KV,
            *p_full = s_full + 2, *o_full = p_full + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   pdl_launch_dependents();                               // the next kernel of the stream may take the SMs this grid leaves
@@ -113,7 +122,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
     }
-    mbar_init(o_full, 1);
+    mbar_init(&o_full[0], 1);                             // PV(G) completes o_full[G & 1]: a waiter is never more than one phase behind
+    mbar_init(&o_full[1], 1);
     *abort_flag = (smem_u32(smem) & 1023u) ? 1u : 0u;   // the swizzled tiles need a 1024-byte aligned base
     fence_mbar_init();
   }
@@ -133,6 +143,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     a.err[2] = blockIdx.x;
   }
 
+  if (warp >= 4) {
+  setmaxnreg_dec<AT_REGS_LEAN>();
   if (bad_align) {
     // nothing was issued; fall through to the teardown
   } else if (warp == 4) {
@@ -161,18 +173,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     __syncwarp();
   } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ issuer of the PV products
     if (lane == 0) {
-      const uint32_t fmt = a.f16 ? 0u : 1u;
-      const uint32_t idesc_s = idesc_f16(fmt, AT_BN);
-      const uint32_t idesc_o = idesc_f16(fmt, AT_D) | (1u << 16);          // B (= V) is MN-major
+      const uint32_t idesc_o = idesc_f16(F16 ? 0u : 1u, AT_D) | (1u << 16);   // B (= V) is MN-major
       const uint32_t t_o = tmem_base + AT_COL_O;
       const uint32_t total = (uint32_t)n_my * (uint32_t)n_kt;                // key-tile steps of this CTA over all its items
-      bool ok = true;
-      auto issue_s = [&](uint32_t G) {                                    // S(G) = Q K^T into S buffer G & 1
-        const uint32_t it = G / (uint32_t)n_kt, j = G - it * (uint32_t)n_kt;
-        if (j == 0 && !mbar_wait(&q_full[it & 1], (it >> 1) & 1, ctx, 12)) { ok = false; return; }
-        if (!mbar_wait(&k_full[G % AT_KV], (G / AT_KV) & 1, ctx, 13)) { ok = false; return; }
+      uint32_t j = 0;
+      for (uint32_t G = 0; G < total; ++G) {
+        const uint32_t st = G % AT_KV;
+        if (!mbar_wait(&v_full[st], (G / AT_KV) & 1, ctx, 15)) break;      // V lands long before P: its barrier round trip is off the chain P -> PV -> S
+        if (!mbar_wait(&p_full[G & 1], (G >> 1) & 1, ctx, 14)) break;
+        tc_fence_after();
+        const uint32_t t_p = tmem_base + AT_COL_P + (G & 1) * (AT_BN / 2);
+        const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_KTILE));
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 8 TMEM columns of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
+          mma_f16_ta(t_o, t_p + 8 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | (uint32_t)kk) != 0);
+        tc_commit(&o_full[G & 1]);
+        tc_commit(&kv_empty[st]);            // K of this stage was read by S(G), which completed before the softmax of step G began
+        if (++j == (uint32_t)n_kt) j = 0;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ issuer of the S products
+    // A second issuing thread: one thread issuing both products of a step (eight MMAs, three or four commits, three
+    // barrier round trips) was busy for about 1450 of the 1670 clk of a step.  S(G + 2) goes into the S buffer that the
+    // softmax of step G has read, once PV(G) has completed: then a softmax that sees S(G + 2) also knows that P buffer
+    // G & 1 has been read and may be overwritten, as it did when one thread issued S(G + 2) behind PV(G).
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_f16(F16 ? 0u : 1u, AT_BN);
+      const uint32_t total = (uint32_t)n_my * (uint32_t)n_kt;
+      uint32_t it = 0, j = 0;
+      for (uint32_t G = 0; G < total; ++G) {                               // issues S(G)
+        if (j == 0 && !mbar_wait(&q_full[it & 1], (it >> 1) & 1, ctx, 12)) break;   // the operands first: they land long before PV(G - 2) completes
+        if (!mbar_wait(&k_full[G % AT_KV], (G / AT_KV) & 1, ctx, 13)) break;
+        if (G >= 2 && !mbar_wait(&o_full[G & 1], ((G - 2) >> 1) & 1, ctx, 20)) break;   // PV(G - 2); the barrier's next completion, PV(G), needs this S(G)
         tc_fence_after();
         const uint64_t qdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_Q + (it & 1) * AT_QTILE));
         const uint64_t kdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_K + (G % AT_KV) * AT_KTILE));
@@ -180,46 +216,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) mma_f16(t_s, qdesc + 2 * kk, kdesc + 2 * kk, idesc_s, kk != 0);
         tc_commit(&s_full[G & 1]);
-        if (j == (uint32_t)n_kt - 1) tc_commit(&q_empty[it & 1]);        // the item's last S product: its Q buffer is free once it completes
-      };
-      for (uint32_t t = 0; t < 2 && t < total && ok; ++t) issue_s(t);
-      uint32_t j = 0;
-      for (uint32_t G = 0; G < total && ok; ++G) {
-        const uint32_t st = G % AT_KV;
-        if (!mbar_wait(&p_full[G & 1], (G >> 1) & 1, ctx, 14)) break;
-        if (!mbar_wait(&v_full[st], (G / AT_KV) & 1, ctx, 15)) break;
-        tc_fence_after();
-        const uint32_t t_p = tmem_base + AT_COL_P + (G & 1) * (AT_BN / 2);
-        const uint64_t vdesc = smem_desc_sw128(smem_u32(smem + AT_OFF_V + st * AT_KTILE));
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)       // A: 16 keys = 8 TMEM columns of P; B: 16 key rows of V = two 8-row groups of 1024 bytes
-          mma_f16_ta(t_o, t_p + 8 * kk, vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | (uint32_t)kk) != 0);
-        tc_commit(o_full);
-        tc_commit(&kv_empty[st]);
-        // the softmax of step G has consumed S buffer G & 1 (it arrived on p_full): refill it, with the next item's
-        // first tiles when this item is running out
-        if (G + 2 < total) issue_s(G + 2);
-        if (++j == (uint32_t)n_kt) j = 0;
+        if (++j == (uint32_t)n_kt) {
+          tc_commit(&q_empty[it & 1]);                                     // the item's last S product: its Q buffer is free once it completes
+          j = 0;
+          ++it;
+        }
       }
     }
     __syncwarp();
+  }   // warp 7 is idle: it completes the second warp group, whose registers go to the softmax warps
   } else {
+    setmaxnreg_inc<AT_REGS_SOFTMAX>();
+    if (!bad_align) {
     // ------------------------------------------------------------------ softmax: thread = query row
     const int row = warp * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
     const float sc = a.scale_log2;
-    const float thr = 8.0f / sc;
     bool ok = true;
     uint32_t G = 0;                                              // key-tile steps of this CTA so far, over all its items
+    bool s_ready = false;                                        // S(G) already seen complete
     // per-tensor scale of an NVFP4 output, its reciprocal and range check: one L2 round trip per CTA, not per item
-    const Nv4Scale tsc = nv4_scale(a.out_fmt == KF_FMT_NV4 ? __ldg(a.tso) : 1.f);
+    const Nv4Scale tsc = nv4_scale(OUT == KF_FMT_NV4 ? __ldg(a.tso) : 1.f);
     for (int it = 0; it < n_my && ok; ++it) {
     const Item I = item_of(it);
     const int qt = I.qt, h = I.h, b = I.b;
     float m_run = -INFINITY, l_run = 0.f;
     for (int j = 0; j < n_kt; ++j, ++G) {
       const int sb = G & 1;
-      if (!mbar_wait(&s_full[sb], (G >> 1) & 1, ctx, 17)) { ok = false; break; }
+      // the S product of this step was probed during the previous step (a barrier round trip is 60-80 clk even when
+      // the phase has long completed); only a probe that came too early falls back to the wait
+      if (!s_ready && !mbar_wait(&s_full[sb], (G >> 1) & 1, ctx, 17)) { ok = false; break; }
       tc_fence_after();
       const int kbase = j * AT_BN;
       uint32_t r[2][32];
@@ -235,12 +261,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // the P row of this tile goes to tensor memory (the A operand of the PV product): 64 keys = 32 columns of 16-bit pairs
       const uint32_t t_p = t_lane + AT_COL_P + sb * (AT_BN / 2);
-      // P = exp2(s*sc + mneg) into shared memory; returns the row sum.  With TRACK the row maximum is gathered in the
-      // same pass (four independent chains), so the maximum is off the critical path of the exponentials.
-      auto exp_row = [&](auto is_f16, auto track, float mneg, float (&mx4)[4]) -> float {
+      // P = exp2(s*sc + mneg) into tensor memory; returns the row sum.  The exponent arguments and the row sum run as
+      // packed pairs: half the issue slots of the scalar form.
+      auto exp_row = [&](auto is_f16, float mneg) -> float {
         constexpr int F = decltype(is_f16)::value;
-        constexpr bool TRACK = decltype(track)::value != 0;
-        // the exponent arguments and the row sum run as packed pairs: half the issue slots of the scalar form
         const float2 sc2 = splat2(sc), mn2 = splat2(mneg);
         float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
@@ -254,10 +278,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               const float2 t = fma2(make_float2(__uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1])), sc2, mn2);
               p[k] = make_float2(ex2(t.x), ex2(t.y));
             }
-            if (TRACK) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1]));
-            }
             s0 = add2(s0, add2(p[0], p[1]));
             s1 = add2(s1, add2(p[2], p[3]));
 #pragma unroll
@@ -267,43 +287,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         return (s0.x + s0.y) + (s1.x + s1.y);
       };
-      auto run = [&](auto track, float mneg, float (&mx4)[4]) -> float {
-        return a.f16 ? exp_row(std::integral_constant<int, 1>{}, track, mneg, mx4) : exp_row(std::integral_constant<int, 0>{}, track, mneg, mx4);
+      auto run = [&](float mneg) -> float {
+        return exp_row(std::integral_constant<int, F16>{}, mneg);
       };
-      // Lazy maximum: the exponentials of tile j > 0 use the running maximum as it is (valid while the tile maximum
-      // exceeds it by less than 2^8 in the exponent domain: P <= 256, sums and O stay in fp32 range); only a row whose
-      // maximum grew by more than that recomputes its P with the new maximum and has its O rescaled.  The first tile has
-      // no running maximum yet and finds its own first.
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // Lazy maximum without a maximum: the exponentials of tile j > 0 use the running maximum as it is, and the tile's
+      // own row sum tells whether that was safe: while it stays below 2^15 no element exceeded 2^15 (bf16 / f16 P, the
+      // fp32 sums and O have room for that), so the maximum of the tile is not needed at all.  Only a row whose sum came
+      // out larger (or infinite) finds its maximum, raises the running maximum, recomputes its P and has its O rescaled.
+      // The first tile has no running maximum yet and finds its own first.
       float sum = 0.f, alpha = 1.f;
-      bool need;
+      bool need = true;
+      s_ready = mbar_test_wait(&s_full[sb ^ 1], ((G + 1) >> 1) & 1);   // S(G + 1): answered while the exponentials run
       if (j > 0) {
-        sum = run(std::integral_constant<int, 1>{}, -m_run * sc, mx4);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+        sum = run(-m_run * sc);
+        need = sum > AT_SUM_LIMIT;
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      need = j == 0 || mx > m_run + thr;
       const uint32_t any_need = __ballot_sync(0xffffffffu, need);
       if (any_need) {                                            // warp-uniform: the tensor-memory stores need the whole warp
         if (need) {
-          alpha = ex2((m_run - mx) * sc);                        // 0 on the first tile
-          m_run = mx;
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mx4[i & 3] = max3(mx4[i & 3], __uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          if (mx > m_run) {
+            alpha = ex2((m_run - mx) * sc);                      // 0 on the first tile
+            m_run = mx;
+          }
         }
-        sum = run(std::integral_constant<int, 0>{}, -m_run * sc, mx4);
+        sum = run(-m_run * sc);
       }
       const uint32_t any = j > 0 ? any_need : 0u;
       l_run = l_run * alpha + sum;
-      // O is only touched when a row of this warp raised its maximum: PV(G-1) must have landed first.  The parity wait is
-      // unambiguous without consuming every phase of o_full: S(G), which this step began by waiting for, was issued
-      // behind PV(G-2) by the same thread and the tensor pipe completes in order, and PV(G) is not issued before this
-      // thread's arrival below, so the barrier has completed exactly G-1 or G phases here.  (The same argument makes the
-      // P buffer of this step safe to overwrite: PV(G-2) has read it.)  The item's last step always waits, so that the
-      // wait for the last product after the loop is at most one phase behind as well.
-      if ((any || j == n_kt - 1) && j > 0 && !mbar_wait(o_full, (G - 1) & 1, ctx, 18)) { ok = false; break; }
+      // O is only touched when a row of this warp raised its maximum: PV(G-1) must have landed first.  It completes
+      // o_full[(G-1) & 1], whose next completion, PV(G+1), cannot come before this thread's arrivals of steps G and G+1.
+      // The item's last step always waits, so that the epilogue's wait for the last product is covered as well.
+      if ((any || j == n_kt - 1) && j > 0 && !mbar_wait(&o_full[(G - 1) & 1], ((G - 1) >> 1) & 1, ctx, 18)) { ok = false; break; }
       if (any) {                                                 // rescale O in TMEM
         tc_fence_after();
         tmem_ld32(t_lane + AT_COL_O, r[0]);
@@ -322,7 +342,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       mbar_arrive(&p_full[sb]);
     }
-    if (ok) ok = mbar_wait(o_full, (G - 1) & 1, ctx, 19);     // the item's last PV product
+    if (ok) ok = mbar_wait(&o_full[(G - 1) & 1], ((G - 1) >> 1) & 1, ctx, 19);     // the item's last PV product
     const int n = qt * AT_BM + row;
     if (ok) {
       tc_fence_after();
@@ -330,7 +350,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld32(t_lane + AT_COL_O, r0);
       tmem_ld32(t_lane + AT_COL_O + 32, r1);
       tmem_ld_wait();
-      if (n < a.N && a.out_fmt >= 0) {
+      if (n < a.N && OUT >= 0) {
         // O row of this head (64 values) -> rounded to the 16-bit type -> 4 nv4 blocks or 2 mx blocks, written as the
         // codes and scale bytes of row b*N + n, columns h*64.. of the [B*N, H*64] operand
         const float inv = 1.0f / l_run;
@@ -355,11 +375,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             v[33 + i] = y.y;
           }
         };
-        if (a.f16) norm_round(std::integral_constant<int, 1>{});
-        else norm_round(std::integral_constant<int, 0>{});
+        norm_round(std::integral_constant<int, F16>{});
         const size_t m = (size_t)b * a.N + n;
         const int d = a.H * AT_D;
-        if (a.out_fmt == KF_FMT_NV4) {
+        if (OUT == KF_FMT_NV4) {
           uint32_t o[8], word = 0;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -385,7 +404,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < 32; i += 2) am = max3(am, fabsf(v[32 * k + i]), fabsf(v[32 * k + i + 1]));
             int by;
-            if (a.out_fmt == KF_FMT_MX8) {
+            if (OUT == KF_FMT_MX8) {
               uint32_t o[8];
               quant_mx8<16>(va, am, div_true, o, by);
               quant_mx8<16>(vb, am, div_true, o + 4, by);
@@ -407,8 +426,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t w[32];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          w[i] = pack16(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, a.f16);
-          w[16 + i] = pack16(__uint_as_float(r1[2 * i]) * inv, __uint_as_float(r1[2 * i + 1]) * inv, a.f16);
+          w[i] = pack16(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
+          w[16 + i] = pack16(__uint_as_float(r1[2 * i]) * inv, __uint_as_float(r1[2 * i + 1]) * inv, F16);
         }
         uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.O) + (((size_t)b * a.N + n) * a.H + h) * (AT_D * 2));
 #pragma unroll
@@ -416,6 +435,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
     }   // items
+    }
   }
 
   tc_fence_before();
@@ -483,13 +503,20 @@ static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H,
   if (st != KF_OK) return st;
   st = make_tmap_qkv(&tv, base + 2 * plane, B, N, H, AT_BN);
   if (st != KF_OK) return st;
-  static bool attr_set[64] = {false};
+  // one instantiation per 16-bit type and output form
+  using KernelFn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnArgs);
+  static const KernelFn table[2][4] = {
+      {attn_fwd_kernel<0, -1>, attn_fwd_kernel<0, KF_FMT_MX8>, attn_fwd_kernel<0, KF_FMT_NV4>, attn_fwd_kernel<0, KF_FMT_MX4>},
+      {attn_fwd_kernel<1, -1>, attn_fwd_kernel<1, KF_FMT_MX8>, attn_fwd_kernel<1, KF_FMT_NV4>, attn_fwd_kernel<1, KF_FMT_MX4>}};
+  const int oi = out_fmt < 0 ? 0 : out_fmt == KF_FMT_MX8 ? 1 : out_fmt == KF_FMT_NV4 ? 2 : 3;
+  const KernelFn kern = table[dtype == KF_F16 ? 1 : 0][oi];
+  static bool attr_set[64][2][4] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM);
+  if (dev >= 64 || !attr_set[dev][dtype == KF_F16 ? 1 : 0][oi]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AT_SMEM);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(attn_fwd_kernel)");
-    if (dev < 64) attr_set[dev] = true;
+    if (dev < 64) attr_set[dev][dtype == KF_F16 ? 1 : 0][oi] = true;
   }
   AttnArgs a{};
   a.O = O; a.B = B; a.N = N; a.H = H; a.f16 = dtype == KF_F16;
@@ -505,7 +532,7 @@ static int attn_launch(int dtype, const void* qkv, void* O, int B, int N, int H,
   if (sst != KF_OK) return sst;
   const int slots = 2 * sms;                                  // two CTAs are resident per SM
   const int grid = items < slots ? (int)items : slots;
-  return cuda_status(launch_maybe_pdl(attn_fwd_kernel, dim3(grid), dim3(AT_THREADS), (size_t)AT_SMEM, static_cast<cudaStream_t>(stream), tq, tk, tv, a),
+  return cuda_status(launch_maybe_pdl(kern, dim3(grid), dim3(AT_THREADS), (size_t)AT_SMEM, static_cast<cudaStream_t>(stream), tq, tk, tv, a),
                      "kf_attn_fwd launch");
 }
 

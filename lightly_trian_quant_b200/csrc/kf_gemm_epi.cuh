@@ -408,10 +408,6 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
   }
 }
 
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr int REGS_LEAN = 40, REGS_EPI = 104;          // 128 * 40 + 512 * 104 <= 640 * 96, the allocation at launch
 
 }  // namespace kf

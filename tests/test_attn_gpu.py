@@ -49,6 +49,27 @@ def test_attn_massive_activation_rows():
     assert go.rel_fro(out.float().cpu().numpy(), ref) < 6e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attn_logits_growing_along_the_keys(dtype):
+    """the key norm grows with the key index, so for most rows later key tiles hold far larger logits than the running
+    maximum of the earlier ones (by more than 2^15 in the exponent domain for many of them, by less for others): the rows
+    that have to raise their maximum late and rescale O, and the rows that do not, in the same warp."""
+    ops = _ops()
+    B, N, H = 1, 453, 2
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(3, B, N, H, 64, generator=g)
+    qkv[0] *= 1.5
+    qkv[1] *= (0.2 + torch.arange(N).float() / 30.0).view(1, N, 1, 1)
+    qkv[0, :, ::3] *= 0.05                                  # every third query row stays flat: no rescale there
+    qkv = qkv.to(dtype)
+    out = ops.attn_fwd(qkv.cuda())
+    ops.check_device_error()
+    assert torch.isfinite(out).all()
+    ref = ao.attn_ref(qkv.float().numpy())
+    err = go.rel_fro(out.float().cpu().numpy(), ref)
+    assert err < (6e-3 if dtype == torch.bfloat16 else 2e-3), err
+
+
 def test_attn_permutation_of_keys_is_neutral():
     """size-independent property: permuting the keys (and values with them) leaves O unchanged up to rounding."""
     ops = _ops()
