@@ -379,17 +379,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const size_t m = (size_t)b * a.N + n;
         const int d = a.H * AT_D;
         if (OUT == KF_FMT_NV4) {
-          uint32_t o[8], word = 0;
+          uint32_t o[8];
+          float am[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const float(&blk)[16] = *reinterpret_cast<const float(*)[16]>(&v[16 * k]);
-            float am = 0.f;
+            am[k] = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) am = max3(am, fabsf(blk[i]), fabsf(blk[i + 1]));
-            int by;
-            quant_nv4<16>(blk, am, tsc, div_true, o + 2 * k, by);
-            word |= (uint32_t)by << (8 * k);
+            for (int i = 0; i < 16; i += 2) am[k] = max3(am[k], fabsf(v[16 * k + i]), fabsf(v[16 * k + i + 1]));
           }
+          int by[4];
+#pragma unroll
+          for (int k = 0; k < 4; k += 2) {                       // two blocks at a time: their scalars on packed pairs
+            const float(&b0)[16] = *reinterpret_cast<const float(*)[16]>(&v[16 * k]);
+            const float(&b1)[16] = *reinterpret_cast<const float(*)[16]>(&v[16 * k + 16]);
+            quant_nv4_pair16(b0, am[k], b1, am[k + 1], tsc, div_true, o + 2 * k, by[k], by[k + 1]);
+          }
+          const uint32_t word = (uint32_t)by[0] | ((uint32_t)by[1] << 8) | ((uint32_t)by[2] << 16) | ((uint32_t)by[3] << 24);
           uint4* dst = reinterpret_cast<uint4*>(a.Qo + m * (d >> 1) + h * 32);
           dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
           dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
