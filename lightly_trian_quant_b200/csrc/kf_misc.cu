@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __re
 // every input byte of the CTA's horizontal span (threads walk the span four bytes at a time, so the loads are coalesced
 // 32-bit words), result as floats in shared memory.  Pass 2: each thread applies its horizontal taps to the three
 // channels from shared memory.  Spans that do not fit the buffer (extreme down-scaling) take the direct path.
+constexpr int RS_ROWS = 6;                               // window rows whose loads are in flight together
 constexpr int RS_SPAN = 4096;                            // bytes of one input row a CTA can stage (256 outputs at up to 5x down-scaling)
 
 // One aligned 32-bit word of the frame batch; a word that straddles the end of the batch is put together from the bytes
@@ -373,22 +374,49 @@ __global__ void __launch_bounds__(256) resize_norm_kernel(const uint8_t* __restr
   const uintptr_t buf_end = reinterpret_cast<uintptr_t>(src) + (uintptr_t)gridDim.z * Hi * Wi * 3;
   if (staged) {
     const int nbytes = (int)(byte_e - byte_a);
+    // every word this CTA may touch lies inside the batch (all CTAs but the ones on the last rows of the last frame)
+    const bool interior = reinterpret_cast<uintptr_t>(src) + (uintptr_t)(row0 + (int64_t)(y1 - 1) * Wi * 3 + byte_e) + 12 <= buf_end;
     for (int j4 = threadIdx.x * 4; j4 < nbytes + 3; j4 += blockDim.x * 4) {
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      for (int y = y0; y < y1; ++y) {
-        const float wy = fmaxf(0.f, 1.f - fabsf((y + 0.5f - cy) * isy));
-        // four consecutive bytes from two aligned 32-bit words (rows are not word aligned in general); words that start
-        // past the end of the whole batch are not read
-        const int64_t off = row0 + (int64_t)y * Wi * 3 + byte_a + j4;
-        const uintptr_t ad = reinterpret_cast<uintptr_t>(src) + off;
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(ad & ~(uintptr_t)3);
-        const uint32_t w0 = rs_load_word(wp, buf_end), w1 = rs_load_word(wp + 1, buf_end);
-        const uint32_t four = __funnelshift_r(w0, w1, (uint32_t)(ad & 3) * 8);
-        const uint32_t v0 = four & 0xFF, v1 = (four >> 8) & 0xFF, v2 = (four >> 16) & 0xFF, v3 = four >> 24;
-        a0 = fmaf(wy, (float)v0, a0);
-        a1 = fmaf(wy, (float)v1, a1);
-        a2 = fmaf(wy, (float)v2, a2);
-        a3 = fmaf(wy, (float)v3, a3);
+      // four consecutive bytes of every window row from two aligned 32-bit words (rows are not word aligned in
+      // general); words that start past the end of the whole batch are not read.  The rows go six at a time with all
+      // their loads issued before the first use: one L2 round trip per group instead of one per row.
+      for (int yb = y0; yb < y1; yb += RS_ROWS) {
+        uint32_t w0[RS_ROWS], w1[RS_ROWS];
+        const int64_t off0 = row0 + (int64_t)yb * Wi * 3 + byte_a + j4;
+        const uintptr_t ad0 = reinterpret_cast<uintptr_t>(src) + off0;
+#pragma unroll
+        for (int k = 0; k < RS_ROWS; ++k) {
+          if (yb + k < y1) {
+            const uintptr_t ad = ad0 + (uintptr_t)k * Wi * 3;
+            const uint32_t* wp = reinterpret_cast<const uint32_t*>(ad & ~(uintptr_t)3);
+            if (interior) {
+              w0[k] = __ldg(wp);
+              w1[k] = __ldg(wp + 1);
+            } else {
+              w0[k] = rs_load_word(wp, buf_end);
+              w1[k] = rs_load_word(wp + 1, buf_end);
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < RS_ROWS; ++k) {
+          if (yb + k < y1) {
+            const float wy = fmaxf(0.f, 1.f - fabsf((yb + k + 0.5f - cy) * isy));
+            const uintptr_t ad = ad0 + (uintptr_t)k * Wi * 3;
+            const uint32_t four = __funnelshift_r(w0[k], w1[k], (uint32_t)(ad & 3) * 8);
+            // byte -> float without the conversion unit: the byte becomes the low mantissa bits of 2^23 (one byte
+            // permute), and 2^23 is subtracted exactly
+            const float v0 = __uint_as_float(__byte_perm(four, 0x4B000000u, 0x7650)) - 8388608.f;
+            const float v1 = __uint_as_float(__byte_perm(four, 0x4B000000u, 0x7651)) - 8388608.f;
+            const float v2 = __uint_as_float(__byte_perm(four, 0x4B000000u, 0x7652)) - 8388608.f;
+            const float v3 = __uint_as_float(__byte_perm(four, 0x4B000000u, 0x7653)) - 8388608.f;
+            a0 = fmaf(wy, v0, a0);
+            a1 = fmaf(wy, v1, a1);
+            a2 = fmaf(wy, v2, a2);
+            a3 = fmaf(wy, v3, a3);
+          }
+        }
       }
       vbuf[j4] = a0; vbuf[j4 + 1] = a1; vbuf[j4 + 2] = a2; vbuf[j4 + 3] = a3;
     }
