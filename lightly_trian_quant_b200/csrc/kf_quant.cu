@@ -139,14 +139,25 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
 }
 
 // ------------------------------------------------------------------------------------------------ LayerNorm (+ quant)
-// One warp per row; lane l holds the 8 consecutive elements [i*256 + l*8, +8) for i < NV (d = NV*256).
-template <int NV>
+// One warp per row; lane l holds the 8 consecutive elements [i*256 + l*8, +8) for i < NV (d = NV*256), as two pieces of
+// four.  With BLK16 the lane's chunks pair up into runs of 16 consecutive elements (whole NVFP4 blocks): chunks 2h and
+// 2h + 1 are [h*512 + l*16, +16).  The lane then reads the four pieces of a run in the rotated order
+// (k + (l >> 1)) & 3, k = 0..3: with a lane stride of 64 bytes the eight lanes of a 128-bit shared-memory access would
+// otherwise meet in two bank groups (four passes per load); rotated they cover all eight.  LayerNorm does not care about
+// the order, the affine parameters are loaded in the same order, and the quantiser undoes it on its packed output.
+template <bool BLK16>
+__device__ __forceinline__ int ln_piece_offset(int i, int half, int lane) {
+  return BLK16 ? (i >> 1) * 512 + lane * 16 + (((2 * (i & 1) + half) + ((lane >> 1) & 3)) & 3) * 4 : i * 256 + lane * 8 + half * 4;
+}
+
+template <int NV, bool BLK16 = false>
 __device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, const float* __restrict__ b, int lane, float (&ww)[NV][8], float (&bb)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const float4* wp = reinterpret_cast<const float4*>(w + i * 256 + lane * 8);
-    const float4* bp = reinterpret_cast<const float4*>(b + i * 256 + lane * 8);
-    const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1), b0 = __ldg(bp), b1 = __ldg(bp + 1);
+    const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<BLK16>(i, 0, lane)));
+    const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<BLK16>(i, 1, lane)));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<BLK16>(i, 0, lane)));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<BLK16>(i, 1, lane)));
     ww[i][0] = w0.x; ww[i][1] = w0.y; ww[i][2] = w0.z; ww[i][3] = w0.w; ww[i][4] = w1.x; ww[i][5] = w1.y; ww[i][6] = w1.z; ww[i][7] = w1.w;
     bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w; bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
   }
@@ -154,20 +165,21 @@ __device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, cons
 
 // LayerNorm of one row with the affine parameters already in registers (the persistent kernels load them once per
 // warp: re-reading them per row doubles the load instructions of a kernel that is otherwise one pass over x).
-template <int NV, bool FROM_SMEM = false>
+template <int NV, bool FROM_SMEM = false, bool BLK16 = false>
 __device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8], const float (&bb)[NV][8], float eps,
                                        int lane, bool valid, float (&v)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (valid) {
-      const float4* p = reinterpret_cast<const float4*>(xr + i * 256 + lane * 8);
+      const float4* pa = reinterpret_cast<const float4*>(xr + ln_piece_offset<BLK16>(i, 0, lane));
+      const float4* pc = reinterpret_cast<const float4*>(xr + ln_piece_offset<BLK16>(i, 1, lane));
       float4 a, c;
       if (FROM_SMEM) {
-        a = p[0];
-        c = p[1];
+        a = *pa;
+        c = *pc;
       } else {
-        a = __ldg(p);
-        c = __ldg(p + 1);
+        a = __ldg(pa);
+        c = __ldg(pc);
       }
       v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = c.x; v[i][5] = c.y; v[i][6] = c.z; v[i][7] = c.w;
     } else {
@@ -249,8 +261,9 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
   };
   if (lane == 0)
     for (int k = 0; k < LNQ_RING; ++k) issue(k);
+  constexpr bool BLK16 = FMT == KF_FMT_NV4 && NV == 4;   // d = 1024 in NVFP4: a lane owns whole 16-value blocks
   float ww[NV][8], bb[NV][8];
-  ln_affine_load<NV>(w, b, lane, ww, bb);
+  ln_affine_load<NV, BLK16>(w, b, lane, ww, bb);
   const Nv4Scale ts = nv4_scale(FMT == KF_FMT_NV4 ? __ldg(ts_ptr) : 1.f);
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   const bool rb = flags & KF_Q_ROUND_BF16;
@@ -261,70 +274,69 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
   const int slot = k % LNQ_RING;
   if (valid && !mbar_wait(&bars[slot], (k / LNQ_RING) & 1, ctx, 30)) break;
   float v[NV][8];
-  ln_row<NV, true>(ring + (size_t)slot * D, ww, bb, eps, lane, valid, v);
+  ln_row<NV, true, BLK16>(ring + (size_t)slot * D, ww, bb, eps, lane, valid, v);
   __syncwarp();                                   // every lane has its part of the row: the slot can be refilled
   if (lane == 0) {
     fence_proxy_async_smem();
     issue(k + LNQ_RING);
   }
-  if constexpr (FMT == KF_FMT_NV4 && NV == 4) {
-    // d = 1024 in NVFP4 (the block path of the model).  A 16-value block is shared by a lane pair, and each lane meets
-    // four of them (one per 256-column chunk): the even lane works out the block scalars of chunks 0 and 2, the odd
-    // lane those of chunks 1 and 3, and the pair swaps them, instead of both doing all four.  The four scale bytes a
-    // lane ends up with are one byte of four different scale words; a 4 x 4 byte transpose over the lanes
-    // {0, 2, 4, 6} + 8g (two shuffles, two byte permutes) gives every even lane one complete word to store.
-    float amax[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (rb) {
-#pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const float2 t = bf16_round2(make_float2(v[i][j], v[i][j + 1]));
-          v[i][j] = t.x;
-          v[i][j + 1] = t.y;
-        }
-      }
-      if (y_dbg && valid) {
-        float4* yp = reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + i * 256 + lane * 8);
-        yp[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-        yp[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
-      }
-      float am = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; j += 2) am = max3(am, fabsf(v[i][j]), fabsf(v[i][j + 1]));
-      amax[i] = amax_nan(am, __shfl_xor_sync(0xffffffffu, am, 1));
-    }
-    const int par = lane & 1;
-    Nv4Block own[2], oth[2];
-    nv4_block_pair(par ? amax[1] : amax[0], par ? amax[3] : amax[2], ts, div_true, own[0], own[1]);   // the lane's two blocks on packed pairs
+  if constexpr (BLK16) {
+    // d = 1024 in NVFP4 (the block path of the model).  The lane holds two whole blocks: elements [16 l, +16) in chunks
+    // 0 and 1 and [512 + 16 l, +16) in chunks 2 and 3, so the block maxima and scalars need no exchange between lanes.
+    // Both blocks are quantised together, their scalars on packed pairs; the two scale bytes of a lane are the same
+    // byte of two scale words, put together over the four lanes of a word with two shuffles.
+    float am[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      oth[h].dd = __shfl_xor_sync(0xffffffffu, own[h].dd, 1);
-      oth[h].rcp = __shfl_xor_sync(0xffffffffu, own[h].rcp, 1);
-      const uint32_t pk = __shfl_xor_sync(0xffffffffu, own[h].sb | ((uint32_t)own[h].mode << 8), 1);
-      oth[h].sb = pk & 0xFF;
-      oth[h].mode = (int)(pk >> 8);
-    }
-    uint32_t mine = 0;
+      am[h] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const bool is_own = (i & 1) == par;
-      Nv4Block b;
-      b.dd = is_own ? own[i >> 1].dd : oth[i >> 1].dd;
-      b.rcp = is_own ? own[i >> 1].rcp : oth[i >> 1].rcp;
-      b.sb = is_own ? own[i >> 1].sb : oth[i >> 1].sb;
-      b.mode = is_own ? own[i >> 1].mode : oth[i >> 1].mode;
-      uint32_t o[1];
-      nv4_codes<8>(v[i], b, o);
-      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + ((i * 256 + lane * 8) >> 1)) = o[0];
-      mine |= (valid ? b.sb : 0u) << (8 * i);
+      for (int i = 2 * h; i < 2 * h + 2; ++i) {
+        if (rb) {
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const float2 t = bf16_round2(make_float2(v[i][j], v[i][j + 1]));
+            v[i][j] = t.x;
+            v[i][j + 1] = t.y;
+          }
+        }
+        if (y_dbg && valid) {
+          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<true>(i, 0, lane)) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<true>(i, 1, lane)) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) am[h] = max3(am[h], fabsf(v[i][j]), fabsf(v[i][j + 1]));
+      }
     }
-    const int p = (lane >> 1) & 3, grp = lane >> 3;
-    const uint32_t y1 = __shfl_xor_sync(0xffffffffu, mine, 2);
-    const uint32_t n1 = __byte_perm(mine, y1, (p & 1) ? 0x3715 : 0x6240);
-    const uint32_t y2 = __shfl_xor_sync(0xffffffffu, n1, 4);
-    const uint32_t word = __byte_perm(n1, y2, (p & 2) ? 0x3276 : 0x5410);      // chunk p, k-blocks 4 * grp .. + 3 of it
-    if (par == 0) *reinterpret_cast<uint32_t*>(sf + sf_offset(row, 16 * p + 4 * grp, D >> 6)) = word;
+    const float(&blk0)[16] = *reinterpret_cast<const float(*)[16]>(&v[0][0]);
+    const float(&blk1)[16] = *reinterpret_cast<const float(*)[16]>(&v[2][0]);
+    uint32_t o[4];
+    int by0, by1;
+    quant_nv4_pair16(blk0, am[0], blk1, am[1], ts, div_true, o, by0, by1);
+    {
+      // piece k of the registers is piece (k + s) & 3 of the block: rotate the four 16-bit code groups of each block left by s
+      const int sr = (lane >> 1) & 3;
+      const uint32_t sh = (uint32_t)(sr & 1) * 16;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = (sr & 2) ? o[2 * h + 1] : o[2 * h], hi = (sr & 2) ? o[2 * h] : o[2 * h + 1];
+        o[2 * h] = __funnelshift_l(hi, lo, sh);
+        o[2 * h + 1] = __funnelshift_l(lo, hi, sh);
+      }
+    }
+    if (valid) {
+      uint8_t* qr = q + (int64_t)row * (D / 2) + lane * 8;
+      *reinterpret_cast<uint2*>(qr) = make_uint2(o[0], o[1]);
+      *reinterpret_cast<uint2*>(qr + D / 4) = make_uint2(o[2], o[3]);
+    }
+    // lanes 4g .. 4g+3 hold the bytes of k-blocks 4g .. 4g+3 (first half of the row) and 32 + 4g .. (second half)
+    uint32_t pk = valid ? ((uint32_t)by0 | ((uint32_t)by1 << 16)) : 0u;              // byte 0: first word, byte 2: second
+    pk |= __shfl_xor_sync(0xffffffffu, pk, 1) << 8;                                   // on even lanes: the bytes of lanes l, l + 1
+    const uint32_t up = __shfl_xor_sync(0xffffffffu, pk, 2);                          // on lane 4g: the pairs of lanes 4g + 2, 4g + 3
+    if ((lane & 3) == 0) {
+      const uint32_t w0 = __byte_perm(pk, up, 0x5410), w1 = __byte_perm(pk, up, 0x7632);
+      *reinterpret_cast<uint32_t*>(sf + sf_offset(row, lane, D >> 6)) = w0;
+      *reinterpret_cast<uint32_t*>(sf + sf_offset(row, 32 + lane, D >> 6)) = w1;
+    }
   } else {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
