@@ -145,19 +145,24 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const T* __restrict__ x
 // (k + (l >> 1)) & 3, k = 0..3: with a lane stride of 64 bytes the eight lanes of a 128-bit shared-memory access would
 // otherwise meet in two bank groups (four passes per load); rotated they cover all eight.  LayerNorm does not care about
 // the order, the affine parameters are loaded in the same order, and the quantiser undoes it on its packed output.
-template <bool BLK16>
+// LAY_SWAP is the chunk layout read from shared memory: lanes 4..7 of every eight take the two pieces of a chunk in the
+// other order (at a lane stride of 32 bytes lanes l and l + 4 would otherwise share their banks: two passes per load).
+constexpr int LAY_CHUNK = 0, LAY_BLK16 = 1, LAY_SWAP = 2;
+template <int LAY>
 __device__ __forceinline__ int ln_piece_offset(int i, int half, int lane) {
-  return BLK16 ? (i >> 1) * 512 + lane * 16 + (((2 * (i & 1) + half) + ((lane >> 1) & 3)) & 3) * 4 : i * 256 + lane * 8 + half * 4;
+  if (LAY == LAY_BLK16) return (i >> 1) * 512 + lane * 16 + (((2 * (i & 1) + half) + ((lane >> 1) & 3)) & 3) * 4;
+  if (LAY == LAY_SWAP) return i * 256 + lane * 8 + (half ^ ((lane >> 2) & 1)) * 4;
+  return i * 256 + lane * 8 + half * 4;
 }
 
-template <int NV, bool BLK16 = false>
+template <int NV, int LAY = LAY_CHUNK>
 __device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, const float* __restrict__ b, int lane, float (&ww)[NV][8], float (&bb)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<BLK16>(i, 0, lane)));
-    const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<BLK16>(i, 1, lane)));
-    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<BLK16>(i, 0, lane)));
-    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<BLK16>(i, 1, lane)));
+    const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<LAY>(i, 0, lane)));
+    const float4 w1 = __ldg(reinterpret_cast<const float4*>(w + ln_piece_offset<LAY>(i, 1, lane)));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<LAY>(i, 0, lane)));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + ln_piece_offset<LAY>(i, 1, lane)));
     ww[i][0] = w0.x; ww[i][1] = w0.y; ww[i][2] = w0.z; ww[i][3] = w0.w; ww[i][4] = w1.x; ww[i][5] = w1.y; ww[i][6] = w1.z; ww[i][7] = w1.w;
     bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w; bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
   }
@@ -165,14 +170,14 @@ __device__ __forceinline__ void ln_affine_load(const float* __restrict__ w, cons
 
 // LayerNorm of one row with the affine parameters already in registers (the persistent kernels load them once per
 // warp: re-reading them per row doubles the load instructions of a kernel that is otherwise one pass over x).
-template <int NV, bool FROM_SMEM = false, bool BLK16 = false>
+template <int NV, bool FROM_SMEM = false, int LAY = LAY_CHUNK>
 __device__ __forceinline__ void ln_row(const float* xr, const float (&ww)[NV][8], const float (&bb)[NV][8], float eps,
                                        int lane, bool valid, float (&v)[NV][8]) {
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (valid) {
-      const float4* pa = reinterpret_cast<const float4*>(xr + ln_piece_offset<BLK16>(i, 0, lane));
-      const float4* pc = reinterpret_cast<const float4*>(xr + ln_piece_offset<BLK16>(i, 1, lane));
+      const float4* pa = reinterpret_cast<const float4*>(xr + ln_piece_offset<LAY>(i, 0, lane));
+      const float4* pc = reinterpret_cast<const float4*>(xr + ln_piece_offset<LAY>(i, 1, lane));
       float4 a, c;
       if (FROM_SMEM) {
         a = *pa;
@@ -262,8 +267,9 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
   if (lane == 0)
     for (int k = 0; k < LNQ_RING; ++k) issue(k);
   constexpr bool BLK16 = FMT == KF_FMT_NV4 && NV == 4;   // d = 1024 in NVFP4: a lane owns whole 16-value blocks
+  constexpr int LAY = BLK16 ? LAY_BLK16 : LAY_SWAP;
   float ww[NV][8], bb[NV][8];
-  ln_affine_load<NV, BLK16>(w, b, lane, ww, bb);
+  ln_affine_load<NV, LAY>(w, b, lane, ww, bb);
   const Nv4Scale ts = nv4_scale(FMT == KF_FMT_NV4 ? __ldg(ts_ptr) : 1.f);
   const bool div_true = !(flags & KF_Q_RECIP_DIV);
   const bool rb = flags & KF_Q_ROUND_BF16;
@@ -274,7 +280,7 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
   const int slot = k % LNQ_RING;
   if (valid && !mbar_wait(&bars[slot], (k / LNQ_RING) & 1, ctx, 30)) break;
   float v[NV][8];
-  ln_row<NV, true, BLK16>(ring + (size_t)slot * D, ww, bb, eps, lane, valid, v);
+  ln_row<NV, true, LAY>(ring + (size_t)slot * D, ww, bb, eps, lane, valid, v);
   __syncwarp();                                   // every lane has its part of the row: the slot can be refilled
   if (lane == 0) {
     fence_proxy_async_smem();
@@ -300,8 +306,8 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
           }
         }
         if (y_dbg && valid) {
-          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<true>(i, 0, lane)) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<true>(i, 1, lane)) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<LAY_BLK16>(i, 0, lane)) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<LAY_BLK16>(i, 1, lane)) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
         }
 #pragma unroll
         for (int j = 0; j < 8; j += 2) am[h] = max3(am[h], fabsf(v[i][j]), fabsf(v[i][j + 1]));
@@ -349,10 +355,10 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
       }
     }
     if (y_dbg && valid) {
-      float4* yp = reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + i * 256 + lane * 8);
-      yp[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-      yp[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+      *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<LAY_SWAP>(i, 0, lane)) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      *reinterpret_cast<float4*>(y_dbg + (int64_t)row * D + ln_piece_offset<LAY_SWAP>(i, 1, lane)) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
     }
+    const bool swapped = (lane >> 2) & 1;                            // this lane holds the two pieces of the chunk in the other order
     float amax = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j += 2) amax = max3(amax, fabsf(v[i][j]), fabsf(v[i][j + 1]));
@@ -363,15 +369,15 @@ __global__ void __launch_bounds__(128, NV <= 4 ? 4 : 1) ln_quant_kernel(const fl
     if (FMT == KF_FMT_MX8) {
       uint32_t o[2];
       quant_mx8<8>(v[i], amax, div_true, o, byte);
-      if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * D + col) = make_uint2(o[0], o[1]);
+      if (valid) *reinterpret_cast<uint2*>(q + (int64_t)row * D + col) = swapped ? make_uint2(o[1], o[0]) : make_uint2(o[0], o[1]);
     } else if (FMT == KF_FMT_MX4) {
       uint32_t o[1];
       quant_mx4<8>(v[i], amax, div_true, o, byte);
-      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = o[0];
+      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = swapped ? __funnelshift_l(o[0], o[0], 16) : o[0];
     } else {
       uint32_t o[1];
       quant_nv4<8>(v[i], amax, ts, div_true, o, byte);
-      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = o[0];
+      if (valid) *reinterpret_cast<uint32_t*>(q + (int64_t)row * (D / 2) + (col >> 1)) = swapped ? __funnelshift_l(o[0], o[0], 16) : o[0];
     }
     if (!valid) byte = 0;
     constexpr int STEP = (FMT == KF_FMT_NV4) ? 2 : 4;               // lanes per k-block
