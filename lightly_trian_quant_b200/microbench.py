@@ -66,7 +66,7 @@ def bench_gemm(args):
     H = 16
     ang = torch.rand(args.tokens, 32, device="cuda") * 6.28                 # second half of the tables = first half, as in the model
     sin, cos = torch.sin(torch.cat((ang, ang), 1)).contiguous(), torch.cos(torch.cat((ang, ang), 1)).contiguous()    # [tokens, 64]: more rows than any prefix needs
-    res = [torch.randn(M, N, device="cuda") for _ in range(2)] if args.kind in ("proj", "fc2") else None
+    res = [torch.randn(M, N, device="cuda") for _ in range(args.res_copies)] if args.kind in ("proj", "fc2") else None
     outq = ops.ActBuf(M, N, fmt if fmt != "bf16" else "mx8") if args.kind == "fc1" else None
     if outq is not None and outq.fmt == "nv4":
         outq.ts.fill_(0.01)
@@ -77,7 +77,7 @@ def bench_gemm(args):
         if args.kind == "qkv":
             ops.qkv_rope(a, W, bias, sin, cos, args.tokens, args.prefix, H, half_tables=not args.general_tables)
         elif args.kind in ("proj", "fc2"):
-            ops.gemm_res(a, W, bias, gamma, res[i % 2], out=res[i % 2])
+            ops.gemm_res(a, W, bias, gamma, res[i % len(res)], out=res[i % len(res)])
         elif args.kind == "fc1":
             if fmt == "bf16":
                 ops.gemm_plain(a, W, bias, gelu=True)
@@ -224,6 +224,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=1605)
     ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--res-copies", type=int, default=2, help="gemm proj / fc2: residual buffers rotated through (1 = the stream stays where the last launch left it, as far as L2 holds it)")
     ap.add_argument("--hs", type=int, default=80, help="dw_ln: input grid side (output is 2x)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--cold", type=int, default=1)
