@@ -129,6 +129,12 @@ typedef struct kf_gemm_params {
    * gelu(acc*ts + bias) after the optional bf16 rounding.  For parity tests: the written codes and scales are the bit
    * specification's quantisation of exactly these values (mirrors y_dbg of kf_ln_quant). */
   float* y_dbg;
+  /* PLAIN with bf16 operands only, batch > 0: `batch` independent products in one launch, C_b = A_b * W_b^T with
+   * A_b = rows b*a_rows_per_batch .. of A (M = batch * a_rows_per_batch), W_b = rows b*w_rows_per_batch .. of W
+   * (w_rows_per_batch >= N) and C the flat [M, N] matrix (= [batch, a_rows_per_batch, N]).  One launch fills the SMs
+   * where one product alone leaves a partial round of tiles.  Replaces the torch.bmm of the mask product
+   * (infer-opt/round11_attn_tier0/impl/head11.py:95).  batch = 0: off. */
+  int batch, a_rows_per_batch, w_rows_per_batch;
 } kf_gemm_params;
 
 /* Block-scaled GEMM on tcgen05 with a fused epilogue.

@@ -29,7 +29,7 @@ class GemmParams(C.Structure):
                 ("A", C.c_void_p), ("SFA", C.c_void_p), ("W", C.c_void_p), ("SFW", C.c_void_p), ("ts_a", C.c_void_p),
                 ("ts_w", C.c_void_p), ("bias", C.c_void_p), ("gamma", C.c_void_p), ("R", C.c_void_p), ("sin", C.c_void_p),
                 ("cos", C.c_void_p), ("C", C.c_void_p), ("Qo", C.c_void_p), ("SFo", C.c_void_p), ("tso", C.c_void_p),
-                ("out_row_group", C.c_int), ("out_row_stride", C.c_int), ("out_row_offset", C.c_int), ("y_dbg", C.c_void_p)]
+                ("out_row_group", C.c_int), ("out_row_stride", C.c_int), ("out_row_offset", C.c_int), ("y_dbg", C.c_void_p), ("batch", C.c_int), ("a_rows_per_batch", C.c_int), ("w_rows_per_batch", C.c_int)]
 
 
 _lib = None

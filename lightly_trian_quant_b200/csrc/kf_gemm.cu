@@ -114,13 +114,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
           const int m_blk = tile / g.n_tiles, n_blk = tile - m_blk * g.n_tiles;
           const int w_halves = (n_blk * BN + 128 < g.N) ? 2 : 1;              // the last column tile may hold only 128 columns
+          int row_end;
+          const int a_row0 = tile_row0(g, m_blk, row_end), w_row0 = tile_wrow0(g, m_blk, n_blk);
           const uint32_t tx = TILE_BYTES + (SCALED ? (1 + w_halves) * ATOMS * 512 : 0);
           for (int kt = 0; kt < g.k_tiles; ++kt) {
             if (!mbar_wait(&empty[s], ph ^ 1, ctx, 1)) { ok = false; break; }
             mbar_expect_tx(&full[s], tx);
             uint8_t* ta = tiles + (size_t)s * TILE_BYTES;
-            tma_load_2d(ta, &tmA, kt * BKB, m_blk * BM, &full[s]);
-            tma_load_2d(ta + A_BYTES, &tmW, kt * BKB, n_blk * BN, &full[s]);   // rows past N are filled with zeros
+            tma_load_2d(ta, &tmA, kt * BKB, a_row0, &full[s]);
+            tma_load_2d(ta + A_BYTES, &tmW, kt * BKB, w_row0, &full[s]);       // rows past the end of W are filled with zeros
             if (SCALED) {
               uint8_t* sa = sfs + (size_t)s * SF_STAGE_BYTES;
               bulk_load_1d(sa, g.sfa + ((size_t)m_blk * g.nkb4 + (size_t)kt * ATOMS) * 512, ATOMS * 512, &full[s]);
@@ -382,11 +384,19 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
     KF_REQUIRE(p->out_fmt != KF_FMT_NV4 || p->tso, "kf_gemm_bs: nv4 quantise-out needs the per-tensor scale tso");
     KF_REQUIRE(!p->y_dbg || al16(p->y_dbg), "kf_gemm_bs: y_dbg must be 16-byte aligned");
   }
+  KF_REQUIRE(p->batch >= 0, "kf_gemm_bs: negative batch");
+  if (p->batch > 0) {
+    KF_REQUIRE(fmt == KF_FMT_BF16 && epi == KF_EPI_PLAIN && p->out_row_group == 0, "kf_gemm_bs: batched products need bf16 operands, the PLAIN epilogue and no output row mapping");
+    KF_REQUIRE(p->a_rows_per_batch > 0 && (long long)p->batch * p->a_rows_per_batch == p->M && p->w_rows_per_batch >= p->N,
+               "kf_gemm_bs: batched products need M = batch * a_rows_per_batch and w_rows_per_batch >= N (batch=%d, rows=%d, M=%d, w rows=%d, N=%d)",
+               p->batch, p->a_rows_per_batch, p->M, p->w_rows_per_batch, p->N);
+  }
   const uint64_t kbytes = fmt == KF_FMT_MX8 ? (uint64_t)p->K : (fmt == KF_FMT_BF16 ? 2ull * p->K : (uint64_t)p->K / 2);
+  const uint64_t w_rows = p->batch > 0 ? (uint64_t)p->batch * p->w_rows_per_batch : (uint64_t)p->N;
   CUtensorMap tmA, tmW;
   int st = make_tmap_2d_bytes(&tmA, p->A, (uint64_t)p->M, kbytes, kbytes, BM);
   if (st != KF_OK) return st;
-  st = make_tmap_2d_bytes(&tmW, p->W, (uint64_t)p->N, kbytes, kbytes, BN);
+  st = make_tmap_2d_bytes(&tmW, p->W, w_rows, kbytes, kbytes, BN);
   if (st != KF_OK) return st;
   GemmArgs g{};
   g.sfa = static_cast<const uint8_t*>(p->SFA);
@@ -397,6 +407,12 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   g.Ntok = p->Ntok; g.prefix = p->prefix; g.H = p->H; g.d = p->H * 64;
   g.out_dtype = p->out_dtype; g.flags = p->flags; g.out_fmt = p->out_fmt;
   g.m_tiles = (p->M + BM - 1) / BM; g.n_tiles = (p->N + BN - 1) / BN; g.k_tiles = (int)(kbytes / BKB);
+  if (p->batch > 0) {
+    g.m_tiles_pb = (p->a_rows_per_batch + BM - 1) / BM;
+    g.a_rows_pb = p->a_rows_per_batch;
+    g.w_rows_pb = p->w_rows_per_batch;
+    g.m_tiles = p->batch * g.m_tiles_pb;
+  }
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
   g.stages = gemm_stages(epi, g.k_tiles, p->flags);
   const bool maps_rows = epi == KF_EPI_PLAIN || epi == KF_EPI_RES;

@@ -38,6 +38,7 @@ struct GemmArgs {
   int out_dtype, flags, out_fmt;
   int m_tiles, n_tiles, k_tiles, nkb4, stages;
   int row_group, row_stride, row_offset;   // PLAIN, RES: output row = (m / group) * stride + offset + m % group (group 0: identity)
+  int m_tiles_pb, a_rows_pb, w_rows_pb;    // batched products (m_tiles_pb > 0): row tiles, A rows and W rows per product
   float* y_dbg;                            // QUANT: optional export of the values that were quantised (fp32 [M, N])
   unsigned int* err;
 };
@@ -248,7 +249,8 @@ __device__ __forceinline__ void quarter_barrier(int quarter) { asm volatile("bar
 // columns n0..n0+63 (r0 = first 32, r1 = last 32).  `slice` is the warp's bias / LayerScale slice in shared memory.
 template <int EPI>
 __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0,
-                                              const float* slice, const float* slab /* ROPE: the quarter's table rows in shared memory, or null */, int lane) {
+                                              const float* slice, const float* slab /* ROPE: the quarter's table rows in shared memory, or null */, int lane,
+                                              int m_end /* first row past the product: M, or the end of the tile's product in a batched launch */) {
   const int m = rbase + lane;
   if (EPI == KF_EPI_ROPE) {
     // the 64 columns of this warp are one head of q, k or v and the thread's 64 values are one [token, head] row of the
@@ -333,7 +335,7 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     }
   } else if (EPI == KF_EPI_PLAIN) {
     uint8_t* dst_row = nullptr;
-    if (m < g.M) {
+    if (m < m_end) {
       const int64_t orow = g.row_group > 0 ? (int64_t)(m / g.row_group) * g.row_stride + g.row_offset + m % g.row_group : m;
       dst_row = static_cast<uint8_t*>(g.C) + (size_t)orow * g.N * (g.out_dtype == KF_F32 ? 4 : 2);
     }
@@ -343,6 +345,21 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
     quant_chunk(g, r0, ts, sco, m, n0, slice);
     quant_chunk(g, r1, ts, sco, m, n0 + 32, slice + 32);
   }
+}
+
+// First A / C row of row tile m_blk and the first row past its product (batched launches: row tiles never straddle two
+// products, the last tile of a product is cut at the product's end); the first W row of column tile n_blk.
+__device__ __forceinline__ int tile_row0(const GemmArgs& g, int m_blk, int& row_end) {
+  if (g.m_tiles_pb > 0) {
+    const int b = m_blk / g.m_tiles_pb, mt = m_blk - b * g.m_tiles_pb;
+    row_end = (b + 1) * g.a_rows_pb;
+    return b * g.a_rows_pb + mt * BM;
+  }
+  row_end = g.M;
+  return m_blk * BM;
+}
+__device__ __forceinline__ int tile_wrow0(const GemmArgs& g, int m_blk, int n_blk) {
+  return (g.m_tiles_pb > 0 ? (m_blk / g.m_tiles_pb) * g.w_rows_pb : 0) + n_blk * BN;
 }
 
 // ------------------------------------------------------------------------------------------------ tile schedules and the epilogue warps' loop
@@ -380,7 +397,8 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
   const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + cg * 64;
   int m_blk, n_blk;
   for (int lt = 0; sched.get(lt, m_blk, n_blk); ++lt) {
-    const int rbase = m_blk * BM + quarter * 32;
+    int row_end;
+    const int rbase = tile_row0(g, m_blk, row_end) + quarter * 32;
     const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
     uint32_t r0[32], r1[32];
     epilogue_slice_stage<EPI>(g, n0, slice, lane);
@@ -404,7 +422,7 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
       quarter_barrier(quarter);
     }
     if (n0 >= g.N) continue;                                   // column group past N in the last column tile
-    epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, slice, slab, lane);
+    epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, slice, slab, lane, row_end);
   }
 }
 

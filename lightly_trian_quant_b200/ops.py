@@ -259,6 +259,29 @@ def gemm_plain(a, W: QWeight, bias=None, *, gelu: bool = False, out_dtype=torch.
 mm = gemm_plain
 
 
+def bmm_nt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, tag: str = "mask") -> torch.Tensor:
+    """out[b] = a[b] @ w[b]^T for bf16 a [B, Q, K] and w [B, P, K] in one launch (P a multiple of 128): the mask product
+    torch.bmm(h, u.transpose(1, 2)) of the head (infer-opt/round11_attn_tier0/impl/head11.py:95).  Bit-identical to B
+    gemm_plain calls; one launch fills the SMs where a single image leaves a partial round of tiles."""
+    _need_cuda(a, w)
+    if a.dim() != 3 or w.dim() != 3 or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_contiguous() or not w.is_contiguous() \
+            or a.shape[0] != w.shape[0] or a.shape[2] != w.shape[2]:
+        raise KfError("bmm_nt: a [B, Q, K] and w [B, P, K] must be contiguous bf16 with equal B and K")
+    B, Q, K = a.shape
+    P = w.shape[1]
+    if out is None:
+        out = torch.empty(B, Q, P, dtype=torch.bfloat16, device=a.device)
+    elif out.shape != (B, Q, P) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise KfError(f"bmm_nt: out must be contiguous bf16 [{B}, {Q}, {P}]")
+    p = GemmParams()
+    p.fmt, p.epi, p.M, p.N, p.K = KF_FMT["bf16"], KF_EPI["plain"], B * Q, P, K
+    p.A, p.W, p.C = a.data_ptr(), w.data_ptr(), out.data_ptr()
+    p.out_dtype = _DT[torch.bfloat16]
+    p.batch, p.a_rows_per_batch, p.w_rows_per_batch = B, Q, P
+    _run(f"gemm_{tag}_bf16", lambda: _lib.lib().kf_gemm_bs(p, _stream()))
+    return out
+
+
 def gemm_res(a, W: QWeight, bias, gamma, res: torch.Tensor, out: Optional[torch.Tensor] = None, row_map=None) -> torch.Tensor:
     """fp32 [M, N] = res + gamma * (a @ W^T (* ts) + bias)   (proj / fc2; gemm_res, fwd_res).
     row_map = (group, stride, offset): row m of the result goes to row (m // group) * stride + offset + m % group of `out`

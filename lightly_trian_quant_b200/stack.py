@@ -225,10 +225,7 @@ class Head:
         h = qb
         for i, (W, b) in enumerate(self.mh):
             h = ops.gemm_plain(h, W, b, gelu=i < len(self.mh) - 1, tag="head")
-        ml = torch.empty(B, Q, Hs * Ws, dtype=BF, device=t.device)
-        uv = u.view(B, Hs * Ws, C)
-        for i in range(B):
-            ops.gemm_plain(h[i * Q:(i + 1) * Q], ops.QWeight(uv[i], "bf16"), out=ml[i], tag="mask")
+        ml = ops.bmm_nt(h.view(B, Q, C), u.view(B, Hs * Ws, C))          # all images in one launch
         return ml.view(B, Q, Hs, Ws), cl
 
 

@@ -289,3 +289,21 @@ def test_rate_probes_run_and_report_work():
     gbs = ops.smem_fill_rate_gbs(8 << 20, 49152, iters=256, reps=1)
     assert 500.0 < gbs < 100000.0, gbs
     ops.check_device_error()
+
+
+@pytest.mark.parametrize("B,Q,P,K", [(3, 200, 1024, 256), (2, 77, 384, 128), (1, 130, 128, 64)])
+def test_batched_products_match_one_launch_per_product(B, Q, P, K):
+    """kf_gemm_bs with batch > 0 (ops.bmm_nt): every product bit-identical to its own PLAIN launch, rows of one product never
+    written by the tiles of another (Q is not a multiple of the 128-row tile), and against the fp32 product."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(B * 1000 + Q)
+    a = torch.randn(B, Q, K, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(B, P, K, generator=g).to(torch.bfloat16).cuda()
+    out = torch.full((B, Q, P), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.bmm_nt(a, w, out=out)
+    ops.check_device_error()
+    for b in range(B):
+        one = ops.gemm_plain(a[b], ops.QWeight(w[b], "bf16"))
+        assert torch.equal(out[b], one)
+    ref = torch.bmm(a.float(), w.float().transpose(1, 2))
+    assert go.rel_fro(out.float().cpu().numpy(), ref.cpu().numpy()) < 4e-3
