@@ -254,68 +254,82 @@ dw_ln_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ bias
 
 // ------------------------------------------------------------------------------------------------ semantic scores
 // scores[b, c, p] = sum_q sigmoid(mask_logits[b, q, p]) * softmax(class_logits[b, q, :])[c]   (all ncls+1 classes kept),
-// labels[b, p] = argmax over the ncls real classes.  One thread per pixel; the class probabilities sit in shared memory.
-__global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __restrict__ ml, const __nv_bfloat16* __restrict__ cl, int Q, int ncls1,
-                                                       int HW, float* __restrict__ scores, uint8_t* __restrict__ labels) {
-  extern __shared__ float prob[];                     // [Q][ncls1]
+// labels[b, p] = argmax over the ncls real classes.  One thread per pixel pair; the class probabilities sit in shared
+// memory.  NC1 = ncls + 1 is a compile-time constant, and the mask logits of eight queries are requested before the
+// first is used (the loop is otherwise one dependent L2 / HBM round trip per query).
+template <int NC1>
+__global__ void __launch_bounds__(256) semantic_kernel(const __nv_bfloat16* __restrict__ ml, const __nv_bfloat16* __restrict__ cl, int Q, int HW,
+                                                       float* __restrict__ scores, uint8_t* __restrict__ labels) {
+  extern __shared__ float prob[];                     // [Q][NC1]
   const int b = blockIdx.y;
   for (int q = threadIdx.x; q < Q; q += blockDim.x) {
-    float v[8], mx = -INFINITY, s = 0.f;
-    for (int c = 0; c < ncls1; ++c) {
-      v[c] = __bfloat162float(cl[((int64_t)b * Q + q) * ncls1 + c]);
+    float v[NC1], mx = -INFINITY, s = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC1; ++c) {
+      v[c] = __bfloat162float(cl[((int64_t)b * Q + q) * NC1 + c]);
       mx = fmaxf(mx, v[c]);
     }
-    for (int c = 0; c < ncls1; ++c) {
+#pragma unroll
+    for (int c = 0; c < NC1; ++c) {
       v[c] = expf(v[c] - mx);
       s += v[c];
     }
-    for (int c = 0; c < ncls1; ++c) prob[q * ncls1 + c] = v[c] / s;
+#pragma unroll
+    for (int c = 0; c < NC1; ++c) prob[q * NC1 + c] = v[c] / s;
   }
   __syncthreads();
   // two adjacent pixels per thread (one 32-bit load per query when HW is even); sigmoid by exp2 / reciprocal approximations
   const int p = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
   if (p >= HW) return;
   const bool two = p + 1 < HW, vec = two && (HW & 1) == 0;
-  float acc0[8], acc1[8];                      // static indices only (loops over 8 with a guard) so that they stay in registers
+  float acc0[NC1], acc1[NC1];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc0[c] = acc1[c] = 0.f;
+  for (int c = 0; c < NC1; ++c) acc0[c] = acc1[c] = 0.f;
   const __nv_bfloat16* m = ml + (int64_t)b * Q * HW + p;
-  for (int q = 0; q < Q; ++q) {
-    float x0, x1 = 0.f;
-    if (vec) {
-      const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(m + (int64_t)q * HW));
-      x0 = __uint_as_float(u << 16);
-      x1 = __uint_as_float(u & 0xFFFF0000u);
-    } else {
-      x0 = __bfloat162float(m[(int64_t)q * HW]);
-      if (two) x1 = __bfloat162float(m[(int64_t)q * HW + 1]);
-    }
-    float e0, e1, s0, s1;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 * -1.4426950408889634f));
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 * -1.4426950408889634f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s0) : "f"(1.0f + e0));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s1) : "f"(1.0f + e1));
+  constexpr int QB = 8;
+  for (int q0 = 0; q0 < Q; q0 += QB) {
+    uint32_t u[QB];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      if (c < ncls1) {
-        const float pr = prob[q * ncls1 + c];
-        acc0[c] = fmaf(s0, pr, acc0[c]);
-        acc1[c] = fmaf(s1, pr, acc1[c]);
+    for (int k = 0; k < QB; ++k) {
+      u[k] = 0;
+      if (q0 + k < Q) {
+        const __nv_bfloat16* mq = m + (int64_t)(q0 + k) * HW;
+        if (vec) {
+          u[k] = __ldg(reinterpret_cast<const uint32_t*>(mq));
+        } else {
+          u[k] = (uint32_t)__bfloat16_as_ushort(mq[0]);
+          if (two) u[k] |= (uint32_t)__bfloat16_as_ushort(mq[1]) << 16;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < QB; ++k) {
+      if (q0 + k < Q) {
+        const float x0 = __uint_as_float(u[k] << 16), x1 = __uint_as_float(u[k] & 0xFFFF0000u);
+        float e0, e1, s0, s1;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(x0 * -1.4426950408889634f));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(x1 * -1.4426950408889634f));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s0) : "f"(1.0f + e0));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(s1) : "f"(1.0f + e1));
+#pragma unroll
+        for (int c = 0; c < NC1; ++c) {
+          const float pr = prob[(q0 + k) * NC1 + c];
+          acc0[c] = fmaf(s0, pr, acc0[c]);
+          acc1[c] = fmaf(s1, pr, acc1[c]);
+        }
       }
     }
   }
   int best0 = 0, best1 = 0;
   float bv0 = acc0[0], bv1 = acc1[0];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    if (c < ncls1) {
-      if (scores) {
-        scores[((int64_t)b * ncls1 + c) * HW + p] = acc0[c];
-        if (two) scores[((int64_t)b * ncls1 + c) * HW + p + 1] = acc1[c];
-      }
-      if (c < ncls1 - 1 && acc0[c] > bv0) { bv0 = acc0[c]; best0 = c; }      // first maximum wins, as torch.argmax
-      if (c < ncls1 - 1 && acc1[c] > bv1) { bv1 = acc1[c]; best1 = c; }
+  for (int c = 0; c < NC1; ++c) {
+    if (scores) {
+      scores[((int64_t)b * NC1 + c) * HW + p] = acc0[c];
+      if (two) scores[((int64_t)b * NC1 + c) * HW + p + 1] = acc1[c];
     }
+    if (c < NC1 - 1 && acc0[c] > bv0) { bv0 = acc0[c]; best0 = c; }      // first maximum wins, as torch.argmax
+    if (c < NC1 - 1 && acc1[c] > bv1) { bv1 = acc1[c]; best1 = c; }
   }
   if (labels) {
     labels[(int64_t)b * HW + p] = (uint8_t)best0;
@@ -518,8 +532,19 @@ extern "C" int kf_semantic(const void* mask_logits, const void* class_logits, in
   if (B == 0) return KF_OK;
   KF_REQUIRE(mask_logits && class_logits && (scores || labels), "kf_semantic: null tensor pointer");
   dim3 grid((HW + 511) / 512, B);
-  semantic_kernel<<<grid, 256, (size_t)Q * (ncls + 1) * 4, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(mask_logits), static_cast<const __nv_bfloat16*>(class_logits), Q, ncls + 1, HW, scores, labels);
+  const __nv_bfloat16* mlp = static_cast<const __nv_bfloat16*>(mask_logits);
+  const __nv_bfloat16* clp = static_cast<const __nv_bfloat16*>(class_logits);
+  const size_t smem = (size_t)Q * (ncls + 1) * 4;
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  switch (ncls + 1) {                                   // one instantiation per class count (ncls real classes + the void class)
+    case 2: semantic_kernel<2><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    case 3: semantic_kernel<3><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    case 4: semantic_kernel<4><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    case 5: semantic_kernel<5><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    case 6: semantic_kernel<6><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    case 7: semantic_kernel<7><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+    default: semantic_kernel<8><<<grid, 256, smem, cs>>>(mlp, clp, Q, HW, scores, labels); break;
+  }
   return cuda_status(cudaGetLastError(), "kf_semantic launch");
 }
 
