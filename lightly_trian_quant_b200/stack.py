@@ -176,7 +176,7 @@ class PatchEmbed:
 
 class Head:
     """EoMT prediction head: final LN + gather, class head, mask MLP, two ScaleBlocks (ConvTranspose as a GEMM in the
-    block-scaled format + fused bias/GELU/pixel-shuffle/depthwise/LayerNorm2D), mask einsum as per-image bf16 GEMMs
+    block-scaled format + fused bias/GELU/pixel-shuffle/depthwise/LayerNorm2D), mask product of all images as one batched bf16 GEMM launch
     (task_model.py:636-651; infer-opt/round11_attn_tier0/impl/head11.py:42-96; stack13.py:124-148)."""
 
     def __init__(self, model, fmt: str, calib: Calib):
