@@ -57,3 +57,42 @@ def test_set_pdl_switch(built_lib):
 
     ops.set_pdl(True)
     ops.set_pdl(False)
+
+
+def test_gemm_params_mirror_matches_the_header(built_lib, tmp_path):
+    """the ctypes mirror of kf_gemm_params has the size and the field offsets the C compiler gives the header's struct."""
+    import ctypes as C
+    import subprocess
+    from pathlib import Path
+
+    from lightly_trian_quant_b200 import _lib
+
+    inc = Path(__file__).resolve().parents[1] / "include"
+    fields = [name for name, _ in _lib.GemmParams._fields_]
+    src = tmp_path / "layout.c"
+    body = "".join(f'  printf("{f} %zu\\n", offsetof(kf_gemm_params, {f}));\n' for f in fields)
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "kf_b200.h"\nint main(void) {\n  printf("sizeof %zu\\n", sizeof(kf_gemm_params));\n'
+                   + body + "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(inc), str(src), "-o", str(exe)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    assert int(out["sizeof"]) == C.sizeof(_lib.GemmParams)
+    for f in fields:
+        assert int(out[f]) == getattr(_lib.GemmParams, f).offset, f
+
+
+def test_batched_products_are_checked_on_the_host(built_lib):
+    """kf_gemm_bs with batch > 0 only takes bf16 operands with the PLAIN epilogue and consistent row counts."""
+    from lightly_trian_quant_b200 import _lib
+
+    L = _lib.lib()
+    p = _lib.GemmParams()
+    p.fmt, p.epi, p.M, p.N, p.K = _lib.KF_FMT["nv4"], _lib.KF_EPI["plain"], 400, 256, 256
+    p.batch, p.a_rows_per_batch, p.w_rows_per_batch = 2, 200, 256
+    p.A = p.W = p.SFA = p.SFW = p.C = 4096                    # never dereferenced: the call is rejected on the host
+    assert L.kf_gemm_bs(p, None) == -1 and "batched" in L.kf_last_error_string().decode()
+    p.fmt = _lib.KF_FMT["bf16"]
+    p.a_rows_per_batch = 199                                   # M != batch * rows
+    assert L.kf_gemm_bs(p, None) == -1 and "batched" in L.kf_last_error_string().decode()
+    p.a_rows_per_batch, p.w_rows_per_batch = 200, 128          # fewer W rows per product than columns
+    assert L.kf_gemm_bs(p, None) == -1 and "batched" in L.kf_last_error_string().decode()
