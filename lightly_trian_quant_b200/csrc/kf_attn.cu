@@ -234,7 +234,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float sc = a.scale_log2;
     bool ok = true;
     uint32_t G = 0;                                              // key-tile steps of this CTA so far, over all its items
-    bool s_ready = false;                                        // S(G) already seen complete
     // per-tensor scale of an NVFP4 output, its reciprocal and range check: one L2 round trip per CTA, not per item
     const Nv4Scale tsc = nv4_scale(OUT == KF_FMT_NV4 ? __ldg(a.tso) : 1.f);
     for (int it = 0; it < n_my && ok; ++it) {
@@ -243,9 +242,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m_run = -INFINITY, l_run = 0.f;
     for (int j = 0; j < n_kt; ++j, ++G) {
       const int sb = G & 1;
-      // the S product of this step was probed during the previous step (a barrier round trip is 60-80 clk even when
-      // the phase has long completed); only a probe that came too early falls back to the wait
-      if (!s_ready && !mbar_wait(&s_full[sb], (G >> 1) & 1, ctx, 17)) { ok = false; break; }
+      if (!mbar_wait(&s_full[sb], (G >> 1) & 1, ctx, 17)) { ok = false; break; }
       tc_fence_after();
       const int kbase = j * AT_BN;
       uint32_t r[2][32];
@@ -297,7 +294,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // The first tile has no running maximum yet and finds its own first.
       float sum = 0.f, alpha = 1.f;
       bool need = true;
-      s_ready = mbar_test_wait(&s_full[sb ^ 1], ((G + 1) >> 1) & 1);   // S(G + 1): answered while the exponentials run
       if (j > 0) {
         sum = run(-m_run * sc);
         need = sum > AT_SUM_LIMIT;
