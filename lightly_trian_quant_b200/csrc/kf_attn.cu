@@ -21,9 +21,11 @@
 //            element exceeded 2^15), so no maximum is tracked in the common case; only a row whose sum came out larger
 //            finds its maximum, recomputes its P and has its O rescaled (TMEM load, multiply, store), which happens on
 //            the first tiles and then almost never; the O barriers are waited only then and at the end of an item.
-//   numerics softmax scale 1/8 folded into exp2 (fp32, one MUFU operation per element; the exponent arguments and
-//            the row sums as packed fp32 pairs; the packed f16x2 exp2 was measured slower); m, l, O in fp32; P rounded
-//            to the input 16-bit type.  Every mbarrier wait is bounded.
+//   numerics softmax scale 1/8 folded into exp2 (fp32; three of every four element pairs by the special-function unit,
+//            the fourth by a cubic on the FMA pipe: the unit is shared by the softmax warps of both CTAs and is the
+//            busiest pipe of the step; more than a quarter costs more issue slots than it frees); the exponent
+//            arguments and the row sums as packed fp32 pairs; m, l, O in fp32; P rounded to the input 16-bit type.
+//            Every mbarrier wait is bounded.
 //
 // Replaces a16::fwd_kernel / attn16_fwd (infer-opt/round12_lowp_stack/impl/attn16o.cu:126-404; mma.sync m16n8k16 +
 // TMA on sm_120).  The power-of-two Q pre-scale `pre` of the reference protects its fp16 accumulators
@@ -43,6 +45,7 @@ constexpr int AT_KTILE = AT_BN * AT_D * 2;             // 8 KB
 constexpr int AT_OFF_Q = 0, AT_OFF_K = 2 * AT_QTILE, AT_OFF_V = AT_OFF_K + AT_KV * AT_KTILE, AT_OFF_BAR = AT_OFF_V + AT_KV * AT_KTILE;
 constexpr size_t AT_SMEM = (size_t)AT_OFF_BAR + 256;
 constexpr float AT_SUM_LIMIT = 32768.f;                  // a tile's row sum above this sends the row to the exact-maximum path (the largest finite f16 is 65504)
+constexpr int AT_POLY_K = 3;                             // which of every four element pairs takes the polynomial exponential
 constexpr int AT_TMEM_COLS = 256, AT_COL_S = 0, AT_COL_O = 128, AT_COL_P = 192;   // S buffers at columns 0 and 64, P (16-bit pairs) at 192 and 224
 
 struct AttnArgs {
@@ -61,6 +64,23 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^t for a pair without the special-function unit: t = n + f with n = round(t) taken from the low mantissa bits of
+// t + 1.5 * 2^23 and f in [-0.5, 0.5]; 2^f by a cubic (minimax for the relative error on that interval: 7.6e-5, far
+// below the rounding of the 16-bit P it feeds); n goes into the exponent field by an integer add.  t is clamped at -126
+// (the result is then 2^-126 instead of 0: it vanishes in the 16-bit P and in the row sum alike).  All of it runs on the
+// FMA and integer pipes, as packed pairs where the operation exists.
+__device__ __forceinline__ float2 ex2_poly2(float2 t) {
+  t.x = fmaxf(t.x, -126.f);
+  t.y = fmaxf(t.y, -126.f);
+  const float2 r = add2(t, splat2(12582912.f));
+  const float2 n = add2(r, splat2(-12582912.f));
+  const float2 f = fma2(n, splat2(-1.f), t);
+  float2 p = fma2(f, splat2(0x1.c43e56p-5f), splat2(0x1.f0df98p-3f));
+  p = fma2(p, f, splat2(0x1.62f24ap-1f));
+  p = fma2(p, f, splat2(0x1.fff686p-1f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23)), __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23)));
 }
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int f16) {
@@ -273,7 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const float2 t = fma2(make_float2(__uint_as_float(r[c][8 * i + 2 * k]), __uint_as_float(r[c][8 * i + 2 * k + 1])), sc2, mn2);
-              p[k] = make_float2(ex2(t.x), ex2(t.y));
+              p[k] = k == AT_POLY_K ? ex2_poly2(t) : make_float2(ex2(t.x), ex2(t.y));   // one pair in four off the special-function unit
             }
             s0 = add2(s0, add2(p[0], p[1]));
             s1 = add2(s1, add2(p[2], p[3]));
