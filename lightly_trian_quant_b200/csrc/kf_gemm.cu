@@ -43,9 +43,11 @@ static int gemm_stages(int epi, int k_tiles, int flags) {
   if (epi == KF_EPI_RES && k_tiles >= 8) return 4;
   return 3;
 }
+constexpr size_t GEMM_SMEM_MAX = 227 * 1024;
 template <int EPI>
-constexpr size_t gemm_smem(int stages) {               // operand ring + scale atoms + bias slices (+ the rotary-table slabs) + barriers
-  return (size_t)stages * (TILE_BYTES + SF_STAGE_BYTES) + EPI_WARPS * SLICE_FLOATS * 4 + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
+constexpr size_t gemm_smem(int stages, int vec_floats = 0) {   // operand ring + scale atoms + bias slices or vectors (+ the rotary-table slabs) + barriers
+  const size_t sl = (size_t)(vec_floats > EPI_WARPS * SLICE_FLOATS ? vec_floats : EPI_WARPS * SLICE_FLOATS) * 4;
+  return (size_t)stages * (TILE_BYTES + SF_STAGE_BYTES) + sl + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
 }
 
 // ------------------------------------------------------------------------------------------------ the kernel
@@ -60,7 +62,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* tiles = smem;
   uint8_t* sfs = smem + (size_t)STAGES * TILE_BYTES;
   float* slices = reinterpret_cast<float*>(sfs + (size_t)STAGES * SF_STAGE_BYTES);
-  float* slabs = slices + EPI_WARPS * SLICE_FLOATS;                        // ROPE only
+  float* slabs = slices + (g.vec_floats > EPI_WARPS * SLICE_FLOATS ? g.vec_floats : EPI_WARPS * SLICE_FLOATS);   // ROPE only
   uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + (EPI == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS : 0));
   uint64_t *full = bars, *empty = bars + MAX_STAGES, *tfull = bars + 2 * MAX_STAGES, *tempty = tfull + 1;
   uint64_t *sf_full = tempty + 1, *sf_empty = sf_full + SF_BUFS;
@@ -326,11 +328,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmW, const Gem
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<EPI>(EPI == KF_EPI_ROPE ? 3 : MAX_STAGES));
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_MAX);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(gemm_kernel)");
     if (dev < 64) attr_set[dev] = true;
   }
-  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), gemm_smem<EPI>(g.stages), st, tmA, tmW, g), "kf_gemm_bs launch");
+  return cuda_status(launch_maybe_pdl(gemm_kernel<KIND, EPI>, dim3(grid), dim3(GEMM_THREADS), gemm_smem<EPI>(g.stages, g.vec_floats), st, tmA, tmW, g), "kf_gemm_bs launch");
 }
 
 template <int KIND>
@@ -415,6 +417,13 @@ extern "C" int kf_gemm_bs(const kf_gemm_params* p, void* stream) {
   }
   g.nkb4 = fmt == KF_FMT_BF16 ? 0 : p->K / (4 * fmt_vec(fmt));
   g.stages = gemm_stages(epi, g.k_tiles, p->flags);
+  {
+    // the whole bias (+ LayerScale) vector in shared memory where the ring depth of this launch leaves room for it
+    const int want = (p->bias || epi == KF_EPI_RES) ? p->N * (epi == KF_EPI_RES ? 2 : 1) : 0;
+    const size_t rest = (size_t)g.stages * (TILE_BYTES + SF_STAGE_BYTES) + (epi == KF_EPI_ROPE ? 4 * ROPE_SLAB_FLOATS * 4 : 0) + 256;
+    const size_t vec_bytes = (size_t)(want > EPI_WARPS * SLICE_FLOATS ? want : EPI_WARPS * SLICE_FLOATS) * 4;
+    g.vec_floats = (want > 0 && rest + vec_bytes <= GEMM_SMEM_MAX) ? want : 0;
+  }
   const bool maps_rows = epi == KF_EPI_PLAIN || epi == KF_EPI_RES;
   g.row_group = maps_rows ? p->out_row_group : 0; g.row_stride = p->out_row_stride; g.row_offset = p->out_row_offset;
   g.y_dbg = epi == KF_EPI_QUANT ? p->y_dbg : nullptr;

@@ -39,6 +39,7 @@ struct GemmArgs {
   int m_tiles, n_tiles, k_tiles, nkb4, stages;
   int row_group, row_stride, row_offset;   // PLAIN, RES: output row = (m / group) * stride + offset + m % group (group 0: identity)
   int m_tiles_pb, a_rows_pb, w_rows_pb;    // batched products (m_tiles_pb > 0): row tiles, A rows and W rows per product
+  int vec_floats;                          // > 0: the whole bias vector (and for RES the LayerScale vector behind it) sits in shared memory for the launch
   float* y_dbg;                            // QUANT: optional export of the values that were quantised (fp32 [M, N])
   unsigned int* err;
 };
@@ -249,7 +250,8 @@ __device__ __forceinline__ void quarter_barrier(int quarter) { asm volatile("bar
 // columns n0..n0+63 (r0 = first 32, r1 = last 32).  `slice` is the warp's bias / LayerScale slice in shared memory.
 template <int EPI>
 __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0,
-                                              const float* slice, const float* slab /* ROPE: the quarter's table rows in shared memory, or null */, int lane,
+                                              const float* slice, const float* gslice /* RES: the LayerScale values of the warp's 64 columns */,
+                                              const float* slab /* ROPE: the quarter's table rows in shared memory, or null */, int lane,
                                               int m_end /* first row past the product: M, or the end of the tile's product in a batched launch */) {
   const int m = rbase + lane;
   if (EPI == KF_EPI_ROPE) {
@@ -325,7 +327,7 @@ __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[
       float o[8];
 #pragma unroll
       for (int e = 0; e < 8; e += 2) {
-        const float2 bb = *reinterpret_cast<const float2*>(slice + 8 * c + e), gg = *reinterpret_cast<const float2*>(slice + 64 + 8 * c + e);
+        const float2 bb = *reinterpret_cast<const float2*>(slice + 8 * c + e), gg = *reinterpret_cast<const float2*>(gslice + 8 * c + e);
         const float2 v = fma2(make_float2(__uint_as_float(acc[e]), __uint_as_float(acc[e + 1])), ts2, bb);
         const float2 w = fma2(gg, v, make_float2(cur.v[e], cur.v[e + 1]));
         o[e] = w.x;
@@ -390,6 +392,18 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
   const int quarter = warp & 3;                 // TMEM lanes 32*quarter .. +31 are the ones this warp may read
   const int cg = (warp - EPI_WARP0) >> 2;       // which 64-column group of the 256-column tile
   float* slice = slices + (warp - EPI_WARP0) * SLICE_FLOATS;
+  // Where the launch left room for it, the bias vector (and the LayerScale vector) is brought into shared memory once per
+  // CTA instead of 64 values per warp and tile: that load was an L2 round trip (400-700 clk) at the head of every tile of
+  // warps that are the busy role of these kernels.
+  const bool vec = g.vec_floats > 0;
+  if (vec) {
+    const int tid = (warp - EPI_WARP0) * 32 + lane;
+    for (int i = tid; i < g.N; i += EPI_WARPS * 32) {
+      slices[i] = g.bias ? __ldg(g.bias + i) : 0.f;
+      if (EPI == KF_EPI_RES) slices[g.N + i] = __ldg(g.gamma + i);
+    }
+    asm volatile("bar.sync 5, %0;" ::"r"(EPI_WARPS * 32) : "memory");
+  }
   float ts = 1.f;
   if (g.ts_a) ts *= __ldg(g.ts_a);
   if (g.ts_w) ts *= __ldg(g.ts_w);
@@ -401,7 +415,9 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
     const int rbase = tile_row0(g, m_blk, row_end) + quarter * 32;
     const int n0 = n_blk * BN + cg * 64;        // first column of this warp's group
     uint32_t r0[32], r1[32];
-    epilogue_slice_stage<EPI>(g, n0, slice, lane);
+    if (!vec) epilogue_slice_stage<EPI>(g, n0, slice, lane);
+    const float* bsl = vec ? slices + n0 : slice;
+    const float* gsl = vec ? slices + g.N + n0 : slice + 64;
     // ROPE with half tables: the quarter's table rows are fetched now and parked in shared memory after the wait
     const bool use_slab = EPI == KF_EPI_ROPE && (g.flags & KF_G_ROPE_HALF) != 0 && n_blk * BN < 2 * g.d;   // the tile holds q or k columns
     RopeSlabRegs tab;
@@ -422,7 +438,7 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
       quarter_barrier(quarter);
     }
     if (n0 >= g.N) continue;                                   // column group past N in the last column tile
-    epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, slice, slab, lane, row_end);
+    epilogue_math<EPI>(g, r0, r1, ts, sco, rbase, n0, bsl, gsl, slab, lane, row_end);
   }
 }
 
