@@ -6,8 +6,9 @@
 // Every epilogue works in the layout tcgen05.ld delivers: thread `lane` of a warp owns 64 consecutive columns of ONE
 // output row.  That is 128 contiguous bytes of a 16-bit output (exactly one [token, head] row of the q/k/v layout) or
 // 256 contiguous bytes of an fp32 one, which the thread moves with 256-bit global loads / stores (ld/st.global.v8): every
-// access is a whole 32-byte sector, so nothing is restaged through shared memory and the only shared memory an epilogue
-// warp uses is a small slice with the bias (and LayerScale) values of its 64 columns.
+// access is a whole 32-byte sector, so nothing is restaged through shared memory; the only shared memory the epilogue
+// warps use holds the bias (and LayerScale) values: the whole vector of the launch, loaded once per CTA, or a 64-value
+// slice per warp and tile where the operand ring leaves no room for the vector.
 #pragma once
 #include "kf_sm100.cuh"
 
@@ -196,10 +197,10 @@ __device__ __forceinline__ void plain_chunk(const GemmArgs& g, const uint32_t (&
   }
 }
 
-// The bias values (and for RES the LayerScale values) of the warp's 64 columns go to its shared-memory slice with one
-// coalesced load per tile, issued before the wait for the accumulator so that its L2 latency runs under that wait (the
-// kernel's shared memory leaves little L1: a load inside the chunk loops would be an L2 round trip); the chunk loops then
-// read them as broadcast float4s.
+// Fallback when the launch has no room for the whole vectors: the bias values (and for RES the LayerScale values) of the
+// warp's 64 columns go to its shared-memory slice with one coalesced load per tile (the kernel's shared memory leaves
+// little L1: a load inside the chunk loops would be an L2 round trip); the chunk loops then read them as broadcast
+// float4s.  The store into the slice waits for the load, an L2 round trip at the head of the tile.
 template <int EPI>
 __device__ __forceinline__ void epilogue_slice_stage(const GemmArgs& g, int n0, float* slice, int lane) {
   if (n0 >= g.N) return;
@@ -247,7 +248,7 @@ __device__ __forceinline__ void quarter_barrier(int quarter) { asm volatile("bar
 
 // ------------------------------------------------------------------------------------------------ the fused epilogues
 // One epilogue warp's share of a tile: rows rbase..rbase+31 (thread `lane` holds row rbase + lane of the accumulator),
-// columns n0..n0+63 (r0 = first 32, r1 = last 32).  `slice` is the warp's bias / LayerScale slice in shared memory.
+// columns n0..n0+63 (r0 = first 32, r1 = last 32).  `slice` / `gslice` point at the bias / LayerScale values of these 64 columns in shared memory.
 template <int EPI>
 __device__ __forceinline__ void epilogue_math(const GemmArgs& g, uint32_t (&r0)[32], uint32_t (&r1)[32], float ts, const Nv4Scale& sco, int rbase, int n0,
                                               const float* slice, const float* gslice /* RES: the LayerScale values of the warp's 64 columns */,
