@@ -105,7 +105,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 
   if (warp < EPI_WARP0) {
-    setmaxnreg_dec<REGS_LEAN>();
+    setmaxnreg_dec<EPI == KF_EPI_ROPE ? REGS_LEAN_ROPE : REGS_LEAN>();
     if (bad_align) {
       // nothing is issued; fall through to the teardown
     } else if (warp == 0) {
@@ -220,7 +220,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else {
     // ------------------------------------------------------------------ epilogue: 16 warps, warp = (TMEM lane quarter, 64-column group)
-    setmaxnreg_inc<REGS_EPI>();
+    setmaxnreg_inc<EPI == KF_EPI_ROPE ? REGS_EPI_ROPE : REGS_EPI>();
     if (!bad_align) {
       const TileSched sched{(int)blockIdx.x, (int)gridDim.x, total_tiles, g.n_tiles, -1};
       epilogue_warps<EPI>(g, sched, tmem_base, tfull, tempty, slices, slabs, ctx, warp, lane);

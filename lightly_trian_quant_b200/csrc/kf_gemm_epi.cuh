@@ -444,5 +444,6 @@ __device__ __forceinline__ void epilogue_warps(const GemmArgs& g, const TileSche
 }
 
 constexpr int REGS_LEAN = 40, REGS_EPI = 104;          // 128 * 40 + 512 * 104 <= 640 * 96, the allocation at launch
+constexpr int REGS_LEAN_ROPE = 32, REGS_EPI_ROPE = 112; // the ROPE epilogue spills at 104 registers (64 accumulators + packed outputs + table values)
 
 }  // namespace kf
