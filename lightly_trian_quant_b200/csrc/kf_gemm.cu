@@ -11,7 +11,7 @@
 //   pipeline   20 warps.  Warp group 0: warp 0 = TMA producer (operand tiles by tensor map, scale atoms by 1-D bulk copy),
 //              warp 1 = MMA issuer (4 MMAs per stage), warp 2 = scale-factor copier (tcgen05.cp atoms smem -> TMEM; the
 //              copies take tensor-pipe time but overlap the MMAs when another warp issues them), warp 3 idle.  Warp groups
-//              1..4 = 16 epilogue warps.  Registers are re-balanced between the roles (setmaxnreg): the three single-thread
+//              1..4 = 16 epilogue warps.  Registers are re-balanced between the roles (setmaxnreg, per epilogue kind): the three single-thread
 //              roles give theirs up and every epilogue thread holds its 64 accumulator values plus loads in flight
 //              without spilling.
 //              One 256-column accumulator in TMEM: each epilogue warp takes (32-row TMEM quarter, 64 columns) into
