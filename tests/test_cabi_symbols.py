@@ -96,3 +96,22 @@ def test_batched_products_are_checked_on_the_host(built_lib):
     assert L.kf_gemm_bs(p, None) == -1 and "batched" in L.kf_last_error_string().decode()
     p.a_rows_per_batch, p.w_rows_per_batch = 200, 128          # fewer W rows per product than columns
     assert L.kf_gemm_bs(p, None) == -1 and "batched" in L.kf_last_error_string().decode()
+
+
+def test_host_checks_of_the_head_kernels(built_lib):
+    """kf_dw_ln takes channel counts in steps of 128 up to 1024; ops.bmm_nt refuses anything but matching contiguous bf16 batches."""
+    import torch
+
+    from lightly_trian_quant_b200 import _lib, ops
+    from lightly_trian_quant_b200._lib import KfError
+
+    L = _lib.lib()
+    assert L.kf_dw_ln(4096, None, 4096, 4096, 4096, 4096, 1, 4, 4, 192, 1e-6, 1, None) == -1
+    assert "multiple of 128" in L.kf_last_error_string().decode()
+    assert L.kf_dw_ln(4096, None, 4096, 4096, 4096, 4096, 1, 4, 4, 1152, 1e-6, 1, None) == -1
+    a = torch.zeros(2, 8, 64, dtype=torch.bfloat16)
+    w = torch.zeros(2, 128, 64, dtype=torch.bfloat16)
+    with pytest.raises(KfError):
+        ops.bmm_nt(a, w)                                     # CPU tensors
+    with pytest.raises(KfError):
+        ops.bmm_nt(a.float(), w)                             # wrong dtype (checked before the device)
